@@ -1,0 +1,149 @@
+/*
+ * sparsedrop.h — C ABI of libsparsedrop.so, the sm_100a SparseDrop engine.
+ *
+ * Every entry point is plain C: raw device pointers, sizes, element strides and a
+ * CUDA stream handle passed as void*.  No torch types, no exceptions.  All functions
+ * that launch work are asynchronous on the given stream, allocate nothing on the
+ * device, and return SD_OK (0) or a negative sd_status code; sd_last_error() gives the
+ * message of the most recent failure on the calling thread.
+ *
+ * Each declaration cites the interface of andylolu2/sparse-dropout that it replaces
+ * (paths are relative to that project's root).
+ *
+ * Matrix convention (same as the reference extension):  A is [M, K], B is [N, K],
+ * C = scale * (A . B^T) is [M, N].  A matrix is described by its pointer plus the element
+ * strides of its two logical dimensions (row stride, column stride); exactly one of the
+ * two strides must be 1 ("row-major" when the column stride is 1, "column-major" when the
+ * row stride is 1), which is the operand rule of flash_dropout/cuda/src/gemm_binding.cu:18-22.
+ * The non-unit stride must be a multiple of 8 elements and the pointer 16-byte aligned
+ * (TMA requirement).  M, N, K need not be multiples of the block size: blocks at the ragged
+ * edge are zero-padded logically (the reference asserts divisibility instead,
+ * flash_dropout/cuda/src/matmul_dsd.cuh:87-95).
+ */
+#ifndef SPARSEDROP_H_
+#define SPARSEDROP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum sd_status {
+    SD_OK = 0,
+    SD_ERR_INVALID_ARG = -1,   /* null pointer, bad size, p outside [0,1), bad dtype ... */
+    SD_ERR_LAYOUT = -2,        /* neither stride is 1, or stride / pointer not TMA-aligned */
+    SD_ERR_CUDA = -3,          /* a CUDA runtime / driver call failed */
+    SD_ERR_TIMEOUT = -4,       /* a device-side bounded wait expired (read by sd_check_status) */
+    SD_ERR_TOO_LARGE = -5      /* size beyond a documented maximum */
+} sd_status;
+
+typedef enum sd_dtype {
+    SD_F16 = 0,                /* IEEE half   (the only dtype of gemm_binding.cu:49-50) */
+    SD_BF16 = 1                /* bfloat16    (extension: the reference is fp16-only)   */
+} sd_dtype;
+
+/* Side of the block plan a DSD product reduces over. */
+typedef enum sd_plan_side {
+    SD_PLAN_ROWS = 0,          /* A's row-blocks are the plan's rows  (forward,  mask)   */
+    SD_PLAN_COLS = 1           /* A's row-blocks are the plan's columns (dW, i.e. mask.T) */
+} sd_plan_side;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int sd_version(void);
+
+/* Message of the last error raised on this thread ("" if none). */
+const char* sd_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Block plan = the drop mask plus every compacted kept-block index list the kernels walk.
+ *
+ * A plan describes an R x C grid of 128x128 tiles (R = ceil(M/128), C = ceil(K/128)).  The
+ * logical dropout blocks may be larger: block_size = 128*rep, and tile (r, c) inherits the
+ * decision of logical block (r / rep, c / rep).  True / 1 = dropped, as in
+ * flash_dropout/functional/utils.py:11-16.
+ *
+ * The plan lives in ONE caller-allocated device buffer of sd_plan_bytes(R, C) bytes, laid out
+ * as int32 arrays at the offsets reported by sd_plan_offsets():
+ *   header[16]   : [0] nnz kept tiles, [1] number of SDD work items, [2] number of dropped
+ *                  tiles, [3] R, [4] C, [5] max kept per row, [6] max kept per column
+ *   row_ptr[R+1], col_idx[R*C]   : CSR of kept tiles (kept column indices per row, ascending)
+ *   col_ptr[C+1], row_idx[R*C]   : CSC of kept tiles (kept row indices per column, ascending)
+ *   kept_pairs[2*R*C]            : (row, col) of kept tiles in row-major order — the order of
+ *                                  torch.nonzero(~mask) used by
+ *                                  flash_dropout/functional/blockwise_dropout_matmul_triton.py:48
+ *   drop_pairs[2*R*C]            : (row, col) of dropped tiles in row-major order
+ *   row_order[R], col_order[C]   : permutations, most kept tiles first (scheduling hint)
+ *   sdd_items[3*R*ceil(C/2)]     : (row, col0, col1 or -1): kept tiles of one row paired up
+ *   mask[R*C] (uint8)            : 1 = dropped, row-major, tile granularity
+ * ------------------------------------------------------------------------------------------ */
+typedef struct sd_plan_layout {
+    int64_t header, row_ptr, col_idx, col_ptr, row_idx, kept_pairs, drop_pairs,
+            row_order, col_order, sdd_items, mask, total_bytes;   /* byte offsets */
+} sd_plan_layout;
+
+size_t sd_plan_bytes(int R, int C);
+int sd_plan_offsets(int R, int C, sd_plan_layout* out);
+
+/*
+ * Draw the Bernoulli(p) drop mask on the device and build the plan in one launch.
+ * Replaces blockwise_dropout_mask (flash_dropout/functional/utils.py:11-16: torch.rand(...) < p)
+ * and the index-list builders (utils.py:19-69 mask_to_increment_table;
+ * blockwise_dropout_matmul_triton.py:48 torch.nonzero(~mask)).
+ * Logical block (i, j) of the ceil(R/rep) x ceil(C/rep) grid is dropped iff
+ *   u < p,  u = float(philox4x32_10(key = seed, counter = (i*Cm + j, 0, offset_lo, offset_hi)).x >> 8) * 2^-24
+ * compared in fp32.  mask_out (optional, may be NULL) receives the logical mask as
+ * ceil(R/rep) x ceil(C/rep) bytes, row-major.
+ */
+int sd_plan_from_seed(void* plan, int R, int C, int rep, uint64_t seed, uint64_t offset, float p,
+                      uint8_t* mask_out, void* stream);
+
+/*
+ * Build the plan from a caller-supplied bool mask (1 byte per logical block, any two strides),
+ * the form in which the reference passes masks to gemm_dsd / gemm_sdd
+ * (flash_dropout/cuda/binding_gemm.py:29-47).  mask is ceil(R/rep) x ceil(C/rep).
+ */
+int sd_plan_from_mask(void* plan, int R, int C, int rep, const uint8_t* mask,
+                      int64_t mask_row_stride, int64_t mask_col_stride, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * GEMMs.  `status` is an optional device int32 (may be NULL) that a kernel sets to a non-zero
+ * code if one of its bounded waits expires; sd_check_status() copies it back and translates.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Dense C = scale * A . B^T.  Replaces GEMM.gemm (flash_dropout/cuda/binding_gemm.py:26-27,
+ * flash_dropout/cuda/src/gemm.cuh:143-167). */
+int sd_gemm(const void* A, int64_t a_rs, int64_t a_cs,
+            const void* B, int64_t b_rs, int64_t b_cs,
+            void* C, int64_t c_rs, int64_t c_cs,
+            int M, int N, int K, float scale, int dtype, int* status, void* stream);
+
+/* DSD: C = scale * (keep o A) . B^T, skipping dropped 128-wide K tiles of each 128-row block
+ * of A.  Replaces GEMM.gemm_dsd (flash_dropout/cuda/binding_gemm.py:29-37,
+ * flash_dropout/cuda/src/matmul_dsd.cuh:70-106).  With side = SD_PLAN_ROWS the plan is
+ * R = ceil(M/128) x C = ceil(K/128) (forward); with SD_PLAN_COLS it is ceil(K/128) x ceil(M/128)
+ * (A = x^T, the dW product of flash_dropout/functional/blockwise_dropout_matmul_cuda.py:47-51).
+ * Row-blocks with no kept tile produce zeros. */
+int sd_gemm_dsd(const void* A, int64_t a_rs, int64_t a_cs,
+                const void* B, int64_t b_rs, int64_t b_cs,
+                void* C, int64_t c_rs, int64_t c_cs,
+                int M, int N, int K, const void* plan, int plan_side,
+                float scale, int dtype, int* status, void* stream);
+
+/* SDD: C = scale * keep o (A . B^T): only kept 128x128 output tiles are computed, dropped tiles
+ * are written as zeros.  The plan is ceil(M/128) x ceil(N/128).  Replaces GEMM.gemm_sdd
+ * (flash_dropout/cuda/binding_gemm.py:39-47, flash_dropout/cuda/src/matmul_sdd.cuh:69-105). */
+int sd_gemm_sdd(const void* A, int64_t a_rs, int64_t a_cs,
+                const void* B, int64_t b_rs, int64_t b_cs,
+                void* C, int64_t c_rs, int64_t c_cs,
+                int M, int N, int K, const void* plan,
+                float scale, int dtype, int* status, void* stream);
+
+/* Synchronises the stream, reads *status and returns SD_OK or SD_ERR_TIMEOUT. */
+int sd_check_status(const int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSEDROP_H_ */

@@ -1,0 +1,44 @@
+// Library-level pieces of the C ABI: version, thread-local error text, cached device facts.
+#include <string.h>
+
+#include "sd_common.h"
+
+namespace sd {
+
+char* error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int sm_count_current_device(int* out) {
+    static int cached[64] = {0};
+    int dev = 0;
+    SD_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && cached[dev] > 0) {
+        *out = cached[dev];
+        return SD_OK;
+    }
+    int n = 0;
+    SD_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    if (dev < 64) cached[dev] = n;
+    *out = n;
+    return SD_OK;
+}
+
+}  // namespace sd
+
+extern "C" {
+
+int sd_version(void) { return 100; }
+
+const char* sd_last_error(void) { return sd::error_buffer(); }
+
+}  // extern "C"

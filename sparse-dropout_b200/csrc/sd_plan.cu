@@ -1,0 +1,280 @@
+// Block-plan kernel: draws (or reads) the drop mask of an R x C grid of 128x128 tiles and
+// compacts it, in one single-CTA launch, into every index list the GEMM kernels walk
+// (CSR, CSC, kept/dropped pair lists, heaviest-first orders, paired SDD work items).
+//
+// Replaces, device-side and without any host synchronisation:
+//   blockwise_dropout_mask        flash_dropout/functional/utils.py:11-16
+//   mask_to_increment_table       flash_dropout/functional/utils.py:19-69   (CSR form)
+//   torch.nonzero(~mask)          flash_dropout/functional/blockwise_dropout_matmul_triton.py:48
+//   mask.T                        flash_dropout/functional/blockwise_dropout_matmul_cuda.py:50 (CSC form)
+//
+// The work is a few KB of integer traffic: the launch is latency-bound, not HBM-bound.
+#include "sd_common.h"
+#include "sd_plan.cuh"
+
+namespace sd {
+
+constexpr int kPlanThreads = 1024;
+constexpr int kSmemMaskBytes = 32768;
+
+// Exclusive scan of one value per thread over the whole CTA (kPlanThreads threads).
+// `total` receives the sum.  warp_sums is 32 ints of shared memory.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+    }
+    __syncthreads();   // protects warp_sums against a previous call's readers
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_sums[lane];
+        int wi = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, wi, d);
+            if (lane >= d) wi += n;
+        }
+        warp_sums[lane] = wi - w;   // exclusive warp offsets
+        if (lane == 31) warp_sums[32] = wi;
+    }
+    __syncthreads();
+    total = warp_sums[32];
+    return warp_sums[warp] + incl - v;
+}
+
+struct PlanArgs {
+    unsigned char* plan;
+    int R, C, rep;
+    int from_seed;
+    unsigned long long seed, offset;
+    float p;
+    const unsigned char* mask_in;
+    long long mask_rs, mask_cs;
+    unsigned char* mask_out;
+};
+
+__global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
+    __shared__ unsigned char smask[kSmemMaskBytes];
+    __shared__ int warp_sums[33];
+    __shared__ int bins[kPlanThreads];
+    __shared__ int s_max_row, s_max_col;
+
+    const int R = a.R, C = a.C, rep = a.rep;
+    const int RC = R * C;
+    const int Cm = (C + rep - 1) / rep;
+    const sd_plan_layout L = plan_layout(R, C);
+    int* header = reinterpret_cast<int*>(a.plan + L.header);
+    int* row_ptr = reinterpret_cast<int*>(a.plan + L.row_ptr);
+    int* col_idx = reinterpret_cast<int*>(a.plan + L.col_idx);
+    int* col_ptr = reinterpret_cast<int*>(a.plan + L.col_ptr);
+    int* row_idx = reinterpret_cast<int*>(a.plan + L.row_idx);
+    int* kept_pairs = reinterpret_cast<int*>(a.plan + L.kept_pairs);
+    int* drop_pairs = reinterpret_cast<int*>(a.plan + L.drop_pairs);
+    int* row_order = reinterpret_cast<int*>(a.plan + L.row_order);
+    int* col_order = reinterpret_cast<int*>(a.plan + L.col_order);
+    int* sdd_items = reinterpret_cast<int*>(a.plan + L.sdd_items);
+    unsigned char* gmask = a.plan + L.mask;
+    const bool in_smem = RC <= kSmemMaskBytes;
+    unsigned char* m = in_smem ? smask : gmask;
+
+    if (threadIdx.x == 0) { s_max_row = 0; s_max_col = 0; }
+
+    // ---- phase 0: the drop decision of every tile (1 = dropped)
+    for (int i = threadIdx.x; i < RC; i += kPlanThreads) {
+        const int r = i / C, c = i - r * C;
+        const int lr = r / rep, lc = c / rep;
+        bool drop;
+        if (a.from_seed) {
+            drop = philox_drop(a.seed, a.offset, (unsigned long long)lr * Cm + lc, a.p);
+            if (a.mask_out && r == lr * rep && c == lc * rep) a.mask_out[(long long)lr * Cm + lc] = drop;
+        } else {
+            drop = a.mask_in[lr * a.mask_rs + lc * a.mask_cs] != 0;
+        }
+        gmask[i] = drop;
+        if (in_smem) smask[i] = drop;
+    }
+    __syncthreads();
+
+    // ---- phase 1: rows.  Thread t owns rows [t*rpt, (t+1)*rpt).
+    {
+        const int rpt = (R + kPlanThreads - 1) / kPlanThreads;
+        const int r0 = min(R, int(threadIdx.x) * rpt), r1 = min(R, r0 + rpt);
+        int kept = 0, items = 0, mx = 0;
+        for (int r = r0; r < r1; ++r) {
+            int cnt = 0;
+            for (int c = 0; c < C; ++c) cnt += (m[r * C + c] == 0);
+            kept += cnt;
+            items += (cnt + 1) >> 1;
+            mx = max(mx, cnt);
+        }
+        int nnz, n_items, dummy;
+        int kept_off = block_exclusive_scan(kept, warp_sums, nnz);
+        int item_off = block_exclusive_scan(items, warp_sums, n_items);
+        (void)dummy;
+        if (mx) atomicMax(&s_max_row, mx);
+        for (int r = r0; r < r1; ++r) {
+            row_ptr[r] = kept_off;
+            int drop_off = r * C - kept_off;   // dropped tiles before row r
+            int first = -1;
+            for (int c = 0; c < C; ++c) {
+                if (m[r * C + c] == 0) {
+                    col_idx[kept_off] = c;
+                    kept_pairs[2 * kept_off] = r;
+                    kept_pairs[2 * kept_off + 1] = c;
+                    ++kept_off;
+                    if (first < 0) {
+                        first = c;
+                    } else {
+                        sdd_items[3 * item_off] = r;
+                        sdd_items[3 * item_off + 1] = first;
+                        sdd_items[3 * item_off + 2] = c;
+                        ++item_off;
+                        first = -1;
+                    }
+                } else {
+                    drop_pairs[2 * drop_off] = r;
+                    drop_pairs[2 * drop_off + 1] = c;
+                    ++drop_off;
+                }
+            }
+            if (first >= 0) {
+                sdd_items[3 * item_off] = r;
+                sdd_items[3 * item_off + 1] = first;
+                sdd_items[3 * item_off + 2] = -1;
+                ++item_off;
+            }
+        }
+        if (threadIdx.x == 0) {
+            row_ptr[R] = nnz;
+            header[H_NNZ] = nnz;
+            header[H_SDD_ITEMS] = n_items;
+            header[H_NDROP] = RC - nnz;
+            header[H_R] = R;
+            header[H_C] = C;
+        }
+    }
+
+    // ---- phase 2: columns.  Thread t owns columns [t*cpt, (t+1)*cpt).
+    {
+        const int cpt = (C + kPlanThreads - 1) / kPlanThreads;
+        const int c0 = min(C, int(threadIdx.x) * cpt), c1 = min(C, c0 + cpt);
+        int kept = 0, mx = 0;
+        for (int c = c0; c < c1; ++c) {
+            int cnt = 0;
+            for (int r = 0; r < R; ++r) cnt += (m[r * C + c] == 0);
+            kept += cnt;
+            mx = max(mx, cnt);
+        }
+        int nnz;
+        int off = block_exclusive_scan(kept, warp_sums, nnz);
+        if (mx) atomicMax(&s_max_col, mx);
+        for (int c = c0; c < c1; ++c) {
+            col_ptr[c] = off;
+            for (int r = 0; r < R; ++r)
+                if (m[r * C + c] == 0) row_idx[off++] = r;
+        }
+        if (threadIdx.x == 0) col_ptr[C] = nnz;
+    }
+    __syncthreads();   // row_ptr / col_ptr visible to the whole CTA
+
+    // ---- phase 3: heaviest-first orders (a scheduling hint: any permutation is valid).
+    //   n <= 1024 : stable rank sort, exact and deterministic
+    //   n  > 1024 : counting sort; keys are exact while the largest count fits the 1024 bins,
+    //               otherwise scaled (monotone, so the order is still non-increasing per bin)
+    for (int pass = 0; pass < 2; ++pass) {
+        const int n = pass == 0 ? R : C;
+        const int full = pass == 0 ? C : R;   // largest possible count
+        const int* ptr = pass == 0 ? row_ptr : col_ptr;
+        int* order = pass == 0 ? row_order : col_order;
+        if (n <= kPlanThreads) {
+            if (int(threadIdx.x) < n) bins[threadIdx.x] = ptr[threadIdx.x + 1] - ptr[threadIdx.x];
+            __syncthreads();
+            if (int(threadIdx.x) < n) {
+                const int mine = bins[threadIdx.x];
+                int rank = 0;
+                for (int j = 0; j < n; ++j) {
+                    const int other = bins[j];
+                    rank += (other > mine) || (other == mine && j < int(threadIdx.x));
+                }
+                order[rank] = threadIdx.x;
+            }
+            __syncthreads();
+            continue;
+        }
+        auto key_of = [&](int i) {
+            const int k = full - (ptr[i + 1] - ptr[i]);
+            return full < kPlanThreads ? k : int((long long)k * (kPlanThreads - 1) / full);
+        };
+        bins[threadIdx.x] = 0;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += kPlanThreads) atomicAdd(&bins[key_of(i)], 1);
+        __syncthreads();
+        int total;
+        const int mine = bins[threadIdx.x];
+        const int start = block_exclusive_scan(mine, warp_sums, total);
+        bins[threadIdx.x] = start;
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += kPlanThreads) order[atomicAdd(&bins[key_of(i)], 1)] = i;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        header[H_MAX_ROW] = s_max_row;
+        header[H_MAX_COL] = s_max_col;
+    }
+}
+
+static int launch_plan(const PlanArgs& a, void* stream) {
+    if (!a.plan) return fail(SD_ERR_INVALID_ARG, "plan buffer is null");
+    if (a.R <= 0 || a.C <= 0) return fail(SD_ERR_INVALID_ARG, "plan grid must be positive (R=%d, C=%d)", a.R, a.C);
+    if (a.rep <= 0) return fail(SD_ERR_INVALID_ARG, "block_size must be a positive multiple of 128");
+    if (int64_t(a.R) * a.C > (int64_t(1) << 26))
+        return fail(SD_ERR_TOO_LARGE, "plan grid %d x %d exceeds 2^26 tiles", a.R, a.C);
+    plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    SD_CUDA_TRY(cudaGetLastError());
+    return SD_OK;
+}
+
+}  // namespace sd
+
+extern "C" {
+
+size_t sd_plan_bytes(int R, int C) {
+    if (R <= 0 || C <= 0) return 0;
+    return size_t(sd::plan_layout(R, C).total_bytes);
+}
+
+int sd_plan_offsets(int R, int C, sd_plan_layout* out) {
+    if (!out || R <= 0 || C <= 0) return sd::fail(SD_ERR_INVALID_ARG, "sd_plan_offsets: bad arguments");
+    *out = sd::plan_layout(R, C);
+    return SD_OK;
+}
+
+int sd_plan_from_seed(void* plan, int R, int C, int rep, uint64_t seed, uint64_t offset, float p,
+                      uint8_t* mask_out, void* stream) {
+    if (!(p >= 0.0f && p < 1.0f)) return sd::fail(SD_ERR_INVALID_ARG, "Dropout probability must be in [0, 1)");
+    sd::PlanArgs a{};
+    a.plan = static_cast<unsigned char*>(plan);
+    a.R = R; a.C = C; a.rep = rep;
+    a.from_seed = 1;
+    a.seed = seed; a.offset = offset; a.p = p;
+    a.mask_out = mask_out;
+    return sd::launch_plan(a, stream);
+}
+
+int sd_plan_from_mask(void* plan, int R, int C, int rep, const uint8_t* mask, int64_t mask_row_stride,
+                      int64_t mask_col_stride, void* stream) {
+    if (!mask) return sd::fail(SD_ERR_INVALID_ARG, "mask is null");
+    sd::PlanArgs a{};
+    a.plan = static_cast<unsigned char*>(plan);
+    a.R = R; a.C = C; a.rep = rep;
+    a.from_seed = 0;
+    a.mask_in = mask;
+    a.mask_rs = mask_row_stride; a.mask_cs = mask_col_stride;
+    return sd::launch_plan(a, stream);
+}
+
+}  // extern "C"

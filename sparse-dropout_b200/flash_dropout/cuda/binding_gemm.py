@@ -1,0 +1,206 @@
+"""Python face of the sm_100a SparseDrop kernels.
+
+``GEMM`` keeps the interface of the reference's JIT-loaded extension wrapper
+(flash_dropout/cuda/binding_gemm.py:7-47: ``gemm``, ``gemm_dsd``, ``gemm_sdd`` on 2-D CUDA
+tensors that are row- or column-major, bool mask with True = dropped) but calls the C ABI of
+libsparsedrop.so through ctypes instead of a pybind/libtorch module, on the current torch
+stream and device (the reference launches on the legacy default stream of device 0,
+flash_dropout/cuda/src/matmul_dsd.cuh:101-105).
+
+``BlockPlan`` is the device-resident mask + compacted kept-tile lists the kernels walk.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from functools import cache
+from math import ceil
+
+import torch
+
+from flash_dropout import _lib
+
+TILE = 128
+
+
+def _check_operand(x: torch.Tensor, name: str) -> None:
+    # flash_dropout/cuda/src/gemm_binding.cu:18-22
+    if not x.is_cuda:
+        raise RuntimeError(f"{name} must be CUDA")
+    if x.dim() != 2:
+        raise RuntimeError(f"{name} must be 2D")
+    if not (x.stride(0) == 1 or x.stride(1) == 1):
+        raise RuntimeError(f"{name} must be row or column major")
+
+
+def _rep(block_size: int) -> int:
+    if isinstance(block_size, (tuple, list)):
+        if len(block_size) != 2 or block_size[0] != block_size[1]:
+            raise ValueError(f"block_size must be an int or an (m, k) pair with equal entries, got {block_size}")
+        block_size = block_size[0]
+    if block_size <= 0 or block_size % TILE:
+        # flash_dropout/cuda/src/matmul_dsd.cuh:92-93
+        raise ValueError(f"block_size must be a positive multiple of {TILE}, got {block_size}")
+    return block_size // TILE
+
+
+class BlockPlan:
+    """Drop mask of an ``R x C`` grid of 128x128 tiles plus its compacted index lists, on the device.
+
+    Built by one kernel launch, either from ``(seed, offset, p)`` (Philox4x32-10, see
+    ``sd_plan_from_seed``) or from a caller-supplied bool mask.  Never synchronises with the host.
+    """
+
+    def __init__(self, R: int, Cc: int, device: torch.device):
+        self.R, self.C = int(R), int(Cc)
+        self.layout = _lib.plan_layout(self.R, self.C)
+        self.buf = torch.empty(self.layout.total_bytes, dtype=torch.uint8, device=device)
+        self.mask: torch.Tensor | None = None   # logical bool mask, True = dropped
+
+    # ---- construction -------------------------------------------------------------------
+    @classmethod
+    def from_seed(cls, M: int, K: int, block_size: int, p: float, seed: int, offset: int,
+                  device: torch.device) -> "BlockPlan":
+        assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
+        rep = _rep(block_size)
+        plan = cls(ceil(M / TILE), ceil(K / TILE), device)
+        mask = torch.empty((ceil(plan.R / rep), ceil(plan.C / rep)), dtype=torch.bool, device=device)
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib().sd_plan_from_seed(
+                plan.buf.data_ptr(), plan.R, plan.C, rep, seed & (2**64 - 1), offset & (2**64 - 1), float(p),
+                mask.data_ptr(), _lib.stream_ptr(device)))
+        plan.mask = mask
+        return plan
+
+    @classmethod
+    def from_mask(cls, mask: torch.Tensor, M: int, K: int, block_size: int) -> "BlockPlan":
+        if mask.dtype != torch.bool:
+            raise RuntimeError("Mask must be bool")
+        if not mask.is_cuda or mask.dim() != 2:
+            raise RuntimeError("Mask must be a 2D CUDA tensor")
+        rep = _rep(block_size)
+        plan = cls(ceil(M / TILE), ceil(K / TILE), mask.device)
+        want = (ceil(plan.R / rep), ceil(plan.C / rep))
+        if tuple(mask.shape) != want:
+            raise RuntimeError(f"mask shape {tuple(mask.shape)} does not match {want} blocks of {block_size}")
+        with torch.cuda.device(mask.device):
+            _lib.check(_lib.lib().sd_plan_from_mask(
+                plan.buf.data_ptr(), plan.R, plan.C, rep, mask.data_ptr(), mask.stride(0), mask.stride(1),
+                _lib.stream_ptr(mask.device)))
+        plan.mask = mask
+        return plan
+
+    # ---- views (no copies) ---------------------------------------------------------------
+    def _ints(self, off: int, n: int) -> torch.Tensor:
+        return self.buf[off:off + 4 * n].view(torch.int32)
+
+    @property
+    def header(self): return self._ints(self.layout.header, 16)
+    @property
+    def row_ptr(self): return self._ints(self.layout.row_ptr, self.R + 1)
+    @property
+    def col_idx(self): return self._ints(self.layout.col_idx, self.R * self.C)
+    @property
+    def col_ptr(self): return self._ints(self.layout.col_ptr, self.C + 1)
+    @property
+    def row_idx(self): return self._ints(self.layout.row_idx, self.R * self.C)
+    @property
+    def kept_pairs(self): return self._ints(self.layout.kept_pairs, 2 * self.R * self.C).view(-1, 2)
+    @property
+    def drop_pairs(self): return self._ints(self.layout.drop_pairs, 2 * self.R * self.C).view(-1, 2)
+    @property
+    def row_order(self): return self._ints(self.layout.row_order, self.R)
+    @property
+    def col_order(self): return self._ints(self.layout.col_order, self.C)
+    @property
+    def sdd_items(self): return self._ints(self.layout.sdd_items, 3 * self.R * ((self.C + 1) // 2)).view(-1, 3)
+    @property
+    def tile_mask(self): return self.buf[self.layout.mask:self.layout.mask + self.R * self.C].view(self.R, self.C)
+
+
+def _mat(x: torch.Tensor):
+    return (x.data_ptr(), x.stride(0), x.stride(1))
+
+
+def _out(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None) -> torch.Tensor:
+    if out is None:
+        return torch.empty((A.size(0), B.size(0)), dtype=A.dtype, device=A.device)
+    if tuple(out.shape) != (A.size(0), B.size(0)) or out.dtype != A.dtype or out.device != A.device:
+        raise RuntimeError("out has the wrong shape, dtype or device")
+    return out
+
+
+def _check_pair(A: torch.Tensor, B: torch.Tensor) -> int:
+    _check_operand(A, "A")
+    _check_operand(B, "B")
+    if A.dtype != B.dtype:
+        raise RuntimeError("A and B must have the same dtype")
+    if A.size(1) != B.size(1):
+        raise RuntimeError(f"reduction dimensions differ: A is {tuple(A.shape)}, B is {tuple(B.shape)}")
+    if A.device != B.device:
+        raise RuntimeError("A and B must be on the same device")
+    return _lib.dtype_code(A.dtype)
+
+
+def dense(A: torch.Tensor, B: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``scale * A @ B.T`` on the tcgen05 kernel with every tile kept."""
+    dt = _check_pair(A, B)
+    Cm = _out(A, B, out)
+    with torch.cuda.device(A.device):
+        _lib.check(_lib.lib().sd_gemm(*_mat(A), *_mat(B), *_mat(Cm), A.size(0), B.size(0), A.size(1),
+                                      float(scale), dt, None, _lib.stream_ptr(A.device)))
+    return Cm
+
+
+def dsd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, side: int, scale: float,
+        out: torch.Tensor | None = None) -> torch.Tensor:
+    """``scale * (keep o A) @ B.T``; ``side`` says whether A's row blocks are the plan's rows or columns."""
+    dt = _check_pair(A, B)
+    M, K = A.shape
+    want = (ceil(M / TILE), ceil(K / TILE)) if side == _lib.SD_PLAN_ROWS else (ceil(K / TILE), ceil(M / TILE))
+    if (plan.R, plan.C) != want:
+        raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match operand A {tuple(A.shape)} (need {want})")
+    Cm = _out(A, B, out)
+    with torch.cuda.device(A.device):
+        _lib.check(_lib.lib().sd_gemm_dsd(*_mat(A), *_mat(B), *_mat(Cm), M, B.size(0), K, plan.buf.data_ptr(),
+                                          side, float(scale), dt, None, _lib.stream_ptr(A.device)))
+    return Cm
+
+
+def sdd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float,
+        out: torch.Tensor | None = None) -> torch.Tensor:
+    """``scale * keep o (A @ B.T)``: kept output tiles computed, dropped tiles written as zeros."""
+    dt = _check_pair(A, B)
+    M, N = A.size(0), B.size(0)
+    if (plan.R, plan.C) != (ceil(M / TILE), ceil(N / TILE)):
+        raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the output {(M, N)}")
+    Cm = _out(A, B, out)
+    with torch.cuda.device(A.device):
+        _lib.check(_lib.lib().sd_gemm_sdd(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),
+                                          float(scale), dt, None, _lib.stream_ptr(A.device)))
+    return Cm
+
+
+@cache
+class GEMM:
+    """Drop-in for the reference's ``GEMM`` wrapper (flash_dropout/cuda/binding_gemm.py:7-47)."""
+
+    def __init__(self, verbose: bool = False):
+        self.lib = _lib.lib()   # raises if libsparsedrop.so has not been built
+        if verbose:
+            print(f"libsparsedrop {self.lib.sd_version()} loaded from {_lib.LIB_PATH}")
+
+    def gemm(self, A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+        return dense(A, B)
+
+    def gemm_dsd(self, A: torch.Tensor, B: torch.Tensor, mask: torch.Tensor, block_size: int,
+                 scale: float) -> torch.Tensor:
+        _check_operand(A, "A")
+        plan = BlockPlan.from_mask(mask, A.size(0), A.size(1), block_size)
+        return dsd(A, B, plan, _lib.SD_PLAN_ROWS, scale)
+
+    def gemm_sdd(self, A: torch.Tensor, B: torch.Tensor, mask: torch.Tensor, block_size: int,
+                 scale: float) -> torch.Tensor:
+        _check_operand(A, "A")
+        _check_operand(B, "B")
+        plan = BlockPlan.from_mask(mask, A.size(0), B.size(0), block_size)
+        return sdd(A, B, plan, scale)
