@@ -1,0 +1,359 @@
+#!/usr/bin/env python
+"""Benchmark of the SparseDrop hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): one SparseDrop linear at M = N = K = 4096, fp16 inputs, fp32
+accumulation, 128 x 128 blocks, p = 0.5, inputs N(0, K^-1/2).  One "step" is the whole hot path for one
+batch: the Philox block-plan kernel (mask + kept-block lists), the DSD forward, the SDD dX and the DSD dW.
+The metric is useful TFLOP/s: 3 * 2 * 128^2 * N * (kept blocks of that step's mask) / time.
+
+* `value`  — inputs resident in HBM, kernels launched through the C ABI, CUDA-event time over K steps.
+             Four rotating input/output sets (768 MB) are used so no step finds its operands in L2.
+* `e2e`    — same metric through the public operator API (flash_dropout.functional + autograd) from
+             pinned HOST buffers: H2D of x, W, dy and D2H of y, dx, dW inside the timed region.
+* roofline — the GEMM kernel (3 launches per step), timed per launch with CUDA events inside the same
+             timed region, against the measured dense bf16 peak in MEASURED_PEAKS.json.
+* cpu_baseline / --impl reference — the reference's CPU path (oracle/cpu_path.py) on the host cores.
+* N > 1    — one process per GPU (torchrun), data parallel: every rank runs the step on its own batch
+             shard and the weight gradient is all-reduced over NCCL; weak scaling.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+for _p in (os.path.join(REPO, "sparse-dropout_b200"), REPO):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+M = N = K = 4096
+BLOCK = 128
+P_DROP = 0.5
+SEED = 0
+N_SETS = 4
+METRIC = "DSD/SDD useful TFLOP/s (DSD fwd + SDD dX + DSD dW on kept 128x128 blocks) at 4096^3 fp16, p=0.5"
+WORKLOAD = ("BASELINE configs[1]: SparseDrop linear fwd+bwd, M=N=K=4096, fp16 in / fp32 acc, 128x128 blocks, "
+            "p=0.5, x,W,dy~N(0,K^-1/2), per-step Philox mask (seed 0, offset=step)")
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch at this workload, from the ncu capture
+# summarised in profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured burst bf16 (MEASURED_PEAKS.json)"
+    except (OSError, KeyError, ValueError):
+        return 1590.0, "fallback 1.59 PFLOP/s (MEASURED_PEAKS.json absent)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period, self.samples, self._stop = index, period_s, [], threading.Event()
+        self._thread = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if not self.nv:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        self._stop.set()
+        self._thread.join()
+        nv = self.nv
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-3:]
+        mhz = sorted(s[1] for s in inside)
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": self.max_mhz,
+                "reasons": [k for k, v in names.items() if bits & v], "samples": len(inside)}
+
+
+def useful_flops(kept_tiles: int) -> float:
+    return 3 * 2.0 * BLOCK * BLOCK * N * kept_tiles
+
+
+# ------------------------------------------------------------------------------------------ reference arm
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cpu_path
+    info = cpu_path.host_info()
+    budget = 20.0
+    r = cpu_path.time_linear_fwd_bwd(M, N, K, BLOCK, P_DROP, seed=SEED, budget_s=budget,
+                                     max_passes=max(1, min(args.steps, 5)))
+    tflops = useful_flops(r["kept_tiles"]) / r["seconds_per_pass"] / 1e12
+    sample = (f"{r['passes']} full passes of the 4096^3 fwd+dX+dW masked-dense path in fp32 "
+              f"(dense work: dropped blocks are not skipped on the CPU), median; {info['cpu_model']}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": r["passes"], "warmup": 1, "ms_per_step": r["seconds_per_pass"] * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "host": info["cpu_model"]},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": r["threads"], "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------ our arm
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import flash_dropout.functional as F
+    from flash_dropout import _lib
+    from flash_dropout import random as sd_random
+    from flash_dropout.cuda.binding_gemm import BlockPlan, dsd, sdd
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the SparseDrop kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    scale = 1.0 / (1.0 - P_DROP)
+    g = torch.Generator().manual_seed(SEED + 1000 * rank)
+    sets = []
+    for _ in range(N_SETS):
+        x = (torch.randn(M, K, generator=g) * K ** -0.25).half().to(dev)
+        w = (torch.randn(N, K, generator=g) * K ** -0.25).half().to(dev)
+        dy = (torch.randn(M, N, generator=g) * N ** -0.25).half().to(dev)
+        sets.append((x, w, dy, torch.empty(M, N, device=dev, dtype=torch.float16),
+                     torch.empty(M, K, device=dev, dtype=torch.float16),
+                     torch.empty(N, K, device=dev, dtype=torch.float16)))
+    plans = [BlockPlan(M // BLOCK, K // BLOCK, dev) for _ in range(N_SETS)]
+    L = _lib.lib()
+    stream = torch.cuda.current_stream(dev)
+
+    def step(i: int, events=None):
+        x, w, dy, y, dx, dw = sets[i % N_SETS]
+        plan = plans[i % N_SETS]
+        # mask + kept-block lists for this step: one launch, offset = step index, rank = Philox subsequence
+        _lib.check(L.sd_plan_from_seed(plan.buf.data_ptr(), plan.R, plan.C, 1, SEED, (rank << 40) + i,
+                                       P_DROP, None, stream.cuda_stream))
+        if events is not None:
+            events[0].record()
+        dsd(x, w, plan, _lib.SD_PLAN_ROWS, scale, out=y)
+        if events is not None:
+            events[1].record()
+        sdd(dy, w.T, plan, scale, out=dx)
+        if events is not None:
+            events[2].record()
+        dsd(x.T, dy.T, plan, _lib.SD_PLAN_COLS, scale, out=dw.T)
+        if events is not None:
+            events[3].record()
+        if world > 1:
+            dist.all_reduce(dw)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(steps):
+        step(warmup + i, evs[i])
+    e1.record()
+    barrier()
+    t1 = time.perf_counter()
+    clocks = sampler.stop(t0, t1)
+    ms_total = e0.elapsed_time(e1)
+    # kept blocks of every timed step's mask, recomputed after the timed region (same seed / offsets)
+    kept_dev = torch.zeros(1, dtype=torch.int64, device=dev)
+    for i in range(steps):
+        _lib.check(L.sd_plan_from_seed(plans[0].buf.data_ptr(), plans[0].R, plans[0].C, 1, SEED,
+                                       (rank << 40) + warmup + i, P_DROP, None, stream.cuda_stream))
+        kept_dev += plans[0].header[0]
+    kept = kept_dev.item()
+    gemm_ms = sum(ev[0].elapsed_time(ev[3]) for ev in evs)
+    per_kernel_ms = [sum(ev[j].elapsed_time(ev[j + 1]) for ev in evs) / steps for j in range(3)]
+
+    # ---- end to end through the operator API from pinned host memory
+    e2e_steps = max(3, min(steps, 20))
+    hx, hw, hdy = (torch.empty(M, K, dtype=torch.float16).pin_memory() for _ in range(3))
+    hx.copy_(sets[0][0].cpu()); hw.copy_(sets[0][1].cpu()); hdy.copy_(sets[0][2].cpu())
+    hy, hdx, hdw = (torch.empty(M, K, dtype=torch.float16).pin_memory() for _ in range(3))
+    dxs, dws, ddy = (torch.empty(M, K, device=dev, dtype=torch.float16) for _ in range(3))
+    sd_random.manual_seed(SEED, subsequence=rank)
+    e2e_masks = []
+
+    def e2e_step():
+        dxs.copy_(hx, non_blocking=True); dws.copy_(hw, non_blocking=True); ddy.copy_(hdy, non_blocking=True)
+        xa, wa = dxs.detach().requires_grad_(), dws.detach().requires_grad_()
+        seed, off = sd_random.next_seed_offset()
+        plan = BlockPlan.from_seed(M, K, BLOCK, P_DROP, seed, off, dev)
+        y = F.cuda_blockwise_dropout_matmul(xa, wa, BLOCK, P_DROP, plan)
+        y.backward(ddy)
+        if world > 1:
+            dist.all_reduce(wa.grad)
+        hy.copy_(y.detach(), non_blocking=True); hdx.copy_(xa.grad, non_blocking=True)
+        hdw.copy_(wa.grad, non_blocking=True)
+        return plan
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_masks.append(e2e_step())
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    e2e_kept = sum(int(pl.header[0].item()) for pl in e2e_masks)
+
+    # ---- speed-up over the same kernels at p = 0 (the other half of the headline metric), rank 0 only
+    extra = {}
+    if rank == 0:
+        def time_three(plan, sc, reps=10):
+            x, w, dy, y, dx, dw = sets[0]
+            out = []
+            for fn in (lambda: dsd(x, w, plan, _lib.SD_PLAN_ROWS, sc, out=y), lambda: sdd(dy, w.T, plan, sc, out=dx),
+                       lambda: dsd(x.T, dy.T, plan, _lib.SD_PLAN_COLS, sc, out=dw.T)):
+                ts = []
+                for r in range(reps + 2):
+                    for s in sets[1:]:
+                        s[3].zero_()     # push set 0 out of L2 between timed launches
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(); fn(); b.record(); torch.cuda.synchronize()
+                    if r >= 2:
+                        ts.append(a.elapsed_time(b))
+                ts.sort()
+                out.append(ts[len(ts) // 2])
+            return out
+        sweep = {}
+        for p in (0.0, 0.5):
+            plan = BlockPlan.from_seed(M, K, BLOCK, p, SEED, 0, dev)
+            t = time_three(plan, 1.0 / (1.0 - p))
+            nk = int(plan.header[0].item())
+            sweep[p] = (t, nk)
+        t0s, t5s = sweep[0.0][0], sweep[0.5][0]
+        extra["speedup_vs_p0"] = {"fwd_dsd": t0s[0] / t5s[0], "dx_sdd": t0s[1] / t5s[1], "dw_dsd": t0s[2] / t5s[2],
+                                  "fwd_bwd": sum(t0s) / sum(t5s), "ms_p0": t0s, "ms_p0.5": t5s,
+                                  "kept_p0.5": sweep[0.5][1],
+                                  "method": "median of 10 single launches, L2 flushed between launches"}
+
+    # ---- aggregate over ranks: max time, summed work
+    stats = torch.tensor([ms_total, e2e_ms, gemm_ms], device=dev, dtype=torch.float64)
+    work = torch.tensor([float(kept), float(e2e_kept)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms, gemm_ms_max = stats.tolist()
+    kept_all, e2e_kept_all = work.tolist()
+
+    if rank == 0:
+        value = useful_flops(kept_all) / (ms_total * 1e-3) / 1e12
+        e2e_value = useful_flops(e2e_kept_all) / (e2e_ms * 1e-3) / 1e12
+        peak, peak_src = measured_peaks()
+        achieved = useful_flops(kept) / (gemm_ms * 1e-3) / 1e12      # this rank's GEMM launches only
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_total / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": f"dp{world}" if world > 1 else "single GPU",
+                       "l2": f"{N_SETS} rotating operand/result sets (768 MB > 126 MB L2), no flush kernel",
+                       "step": "plan kernel + DSD fwd + SDD dX + DSD dW" + (" + NCCL allreduce(dW)" if world > 1 else "")},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "kernel": "sparsedrop_gemm_kernel (3 launches per step: DSD fwd, SDD dX, DSD dW)",
+                         "peak_source": peak_src, "frac_of_nominal_2250": achieved / 2250.0,
+                         "avg_launch_ms": {"dsd_fwd": per_kernel_ms[0], "sdd_dx": per_kernel_ms[1], "dsd_dw": per_kernel_ms[2]},
+                         "flops_per_launch": useful_flops(kept) / 3 / steps},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * M * K * 2,
+                    "d2h_bytes_per_step": 3 * M * K * 2, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "api": "flash_dropout.functional.cuda_blockwise_dropout_matmul + backward, pinned host buffers"},
+            "gpu_launches": 4 * steps, "clocks": clocks,
+        }
+        line.update(extra)
+        if world == 1:
+            from oracle import cpu_path
+            info = cpu_path.host_info()
+            r = cpu_path.time_linear_fwd_bwd(M, N, K, BLOCK, P_DROP, seed=SEED, budget_s=12.0, max_passes=4)
+            line["cpu_baseline"] = {
+                "value": useful_flops(r["kept_tiles"]) / r["seconds_per_pass"] / 1e12, "unit": "TFLOP/s",
+                "cores": r["threads"], "kind": "port",
+                "sample": f"{r['passes']} full 4096^3 fwd+dX+dW passes, fp32 masked-dense (no block skipping), "
+                          f"median {r['seconds_per_pass']:.3f} s; {info['cpu_model']}"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world == 1:
+        # convenience: relaunch under torchrun, one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__),
+               "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup)]
+        raise SystemExit(subprocess.call(cmd))
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -427,6 +427,13 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     if (mode == MODE_DSD && plan_side != SD_PLAN_ROWS && plan_side != SD_PLAN_COLS)
         return fail(SD_ERR_INVALID_ARG, "plan_side must be SD_PLAN_ROWS or SD_PLAN_COLS");
 
+    // Bind the device's primary context to this thread before the first driver-API call: a thread that
+    // has made no runtime call yet (e.g. an autograd worker) has no current context and
+    // cuTensorMapEncodeTiled would fail with CUDA_ERROR_INVALID_CONTEXT.
+    int dev = 0;
+    SD_CUDA_TRY(cudaGetDevice(&dev));
+    SD_CUDA_TRY(cudaSetDevice(dev));
+
     CUtensorMap ta, tb;
     bool a_mn = false, b_mn = false;
     int rc = make_operand_map(&ta, &a_mn, "A", A, a_rs, a_cs, M, K, dtype);

@@ -1,0 +1,81 @@
+"""SparseDrop linear on the sm_100a kernels: the autograd glue of the operator API.
+
+Same contract as the reference's ``BlockwiseDropoutMatmulCUDA``
+(flash_dropout/functional/blockwise_dropout_matmul_cuda.py:7-59): forward ``y = (keep o x) W^T / (1-p)``
+by a DSD product, backward ``dx`` by an SDD product and ``dW`` by a DSD product over the transposed
+operands.  Differences: the mask comes from the device-side Philox plan kernel instead of
+``torch.rand`` (one launch, no host sync, and the same plan object is reused by all three products);
+bf16 is accepted as well as fp16; launches go to the current stream of the tensors' device.
+"""
+from __future__ import annotations
+
+import torch
+
+from flash_dropout import _lib
+from flash_dropout import random as sd_random
+from flash_dropout.cuda.binding_gemm import BlockPlan, dsd, sdd
+
+
+def _operand(x: torch.Tensor) -> torch.Tensor:
+    """Row- or column-major with a TMA-compatible leading stride, else a contiguous copy."""
+    if x.dim() == 2 and x.data_ptr() % 16 == 0:
+        if x.stride(1) == 1 and (x.stride(0) % 8 == 0 or x.size(0) == 1) and x.stride(0) >= x.size(1):
+            return x
+        if x.stride(0) == 1 and (x.stride(1) % 8 == 0 or x.size(1) == 1) and x.stride(1) >= x.size(0):
+            return x
+    return x.contiguous()
+
+
+class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
+                plan: BlockPlan | None = None):
+        assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
+        if not (input.is_cuda and weight.is_cuda):
+            # no CPU path: flash_dropout/cuda/src/gemm_binding.cu:19 raises the same way
+            raise RuntimeError("input and weight must be CUDA")
+        if input.dim() != 2 or weight.dim() != 2:
+            raise RuntimeError("input and weight must be 2D")
+        if input.dtype != weight.dtype:
+            raise RuntimeError(f"input ({input.dtype}) and weight ({weight.dtype}) must have the same dtype")
+        M, K = input.shape
+        if K % 8 or weight.size(0) % 8:
+            raise RuntimeError("in_features and out_features must be multiples of 8 (16-byte TMA rows)")
+        input, weight = _operand(input), _operand(weight)
+        if plan is None:
+            seed, offset = sd_random.next_seed_offset()
+            plan = BlockPlan.from_seed(M, K, block_size, p, seed, offset, input.device)
+        out = dsd(input, weight, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))
+        ctx.save_for_backward(input, weight)
+        ctx.plan = plan
+        ctx.p = p
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        input, weight = ctx.saved_tensors
+        plan, scale = ctx.plan, 1.0 / (1.0 - ctx.p)
+        dy = _operand(grad_output.to(input.dtype))
+        grad_input = grad_weight = None
+        if ctx.needs_input_grad[0]:
+            # dx (M, K) = keep o (dy (M, N) . W (N, K)) * scale: B operand is W^T, a column-major view
+            grad_input = sdd(dy, weight.T, plan, scale)
+        if ctx.needs_input_grad[1]:
+            # dW^T (K, N) = (keep o x)^T (K, M) . dy (M, N) * scale, stored straight into dW (N, K)
+            grad_weight = torch.empty_like(weight, memory_format=torch.contiguous_format)
+            dsd(input.T, dy.T, plan, _lib.SD_PLAN_COLS, scale, out=grad_weight.T)
+        return grad_input, grad_weight, None, None, None
+
+
+def blockwise_dropout_matmul(input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
+                             plan: BlockPlan | None = None) -> torch.Tensor:
+    """``y = (mask o input) . weight^T / (1 - p)`` with a fresh block mask (or the given plan).
+
+    Under CUDA autocast both operands are cast to the autocast dtype (the reference casts to fp16,
+    blockwise_dropout_matmul_cuda.py:9); otherwise they must already be fp16 or bf16.
+    """
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.get_autocast_dtype("cuda")
+        input, weight = input.to(dt), weight.to(dt)
+    with torch.autocast("cuda", enabled=False):
+        return BlockwiseDropoutMatmulCUDA.apply(input, weight, block_size, p, plan)

@@ -1,0 +1,43 @@
+"""Mask and index-list helpers of the operator API (reference: flash_dropout/functional/utils.py)."""
+from __future__ import annotations
+
+from math import ceil
+
+import torch
+
+from flash_dropout import random as sd_random
+
+
+def blockwise_dropout_mask(x: torch.Tensor, block_size: int, p: float) -> torch.Tensor:
+    """Bernoulli(p) drop mask (True = dropped) per ``block_size`` x ``block_size`` block of the last two dims.
+
+    Same shape rule and polarity as flash_dropout/functional/utils.py:11-16.  For a 2-D CUDA tensor the
+    mask is drawn on the device by the Philox plan kernel; otherwise by ``torch.rand`` as in the reference.
+    """
+    *b, m, k = x.shape
+    if x.is_cuda and not b and block_size % 128 == 0:
+        from flash_dropout.cuda.binding_gemm import BlockPlan
+        seed, offset = sd_random.next_seed_offset()
+        return BlockPlan.from_seed(m, k, block_size, p, seed, offset, x.device).mask
+    shape = (*b, ceil(m / block_size), ceil(k / block_size))
+    return torch.rand(shape, device=x.device) < p
+
+
+def mask_to_increment_table(mask: torch.Tensor, BLOCK_K: int):
+    """CSR-style pointer-increment table of the kept blocks (flash_dropout/functional/utils.py:19-69).
+
+    Returns ``(table, row_indices, row_widths)``: ``row_widths[r]`` kept blocks in row r,
+    ``row_indices[r]`` where row r starts in ``table``, and ``table`` the element offset of each kept
+    block relative to the previous kept block of its row (absolute for the first one of a row).
+    """
+    keep = ~mask
+    row_widths = keep.sum(dim=1)
+    row_indices = torch.cumsum(row_widths, dim=0) - row_widths
+    cols = torch.nonzero(keep, as_tuple=True)[1]
+    offsets = cols * BLOCK_K
+    table = offsets.clone()
+    if table.numel() > 1:
+        table[1:] = offsets[1:] - offsets[:-1]
+    starts = row_indices[row_indices < table.numel()]
+    table[starts] = offsets[starts]
+    return table, row_indices, row_widths

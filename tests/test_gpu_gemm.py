@@ -1,0 +1,189 @@
+"""DSD / SDD / dense kernels through the C ABI vs the CPU oracle.
+
+Structure follows the reference's test/test_cuda.py:13-57 — one mask handed to both implementations,
+forward + dX + dW in one test, its (m, n, k) x p grid including the degenerate ends — with the tolerance
+of this build's contract: rtol 1e-2 / atol 1e-2 for 16-bit inputs with fp32 accumulation (the reference
+accepts atol 0.2 on unscaled inputs).  Inputs are N(0, K^-1/2) so outputs are O(1).
+"""
+from itertools import product
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import masked_dense as md
+from oracle import philox_mask as pm
+
+pytestmark = pytest.mark.gpu
+
+RTOL = ATOL = 1e-2
+DEV = torch.device("cuda:0")
+
+
+def _inputs(M, N, K, seed, dtype=torch.float16):
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(M, K, generator=g) * K ** -0.25).to(dtype)
+    w = (torch.randn(N, K, generator=g) * K ** -0.25).to(dtype)
+    dy = (torch.randn(M, N, generator=g) * N ** -0.25).to(dtype)
+    return x, w, dy
+
+
+def _close(got, want, what):
+    torch.testing.assert_close(got.float().cpu(), want, rtol=RTOL, atol=ATOL, msg=lambda m: f"{what}: {m}")
+
+
+mnks = [(128, 128, 128), (512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048)]
+ps = [0.0, 0.1, 0.2, 0.5, 0.9, 0.99, 0.999]
+
+
+@pytest.mark.parametrize("mnk,p", list(product(mnks, ps)))
+def test_blockwise_dropout_matmul_reference_grid(built_lib, mnk, p):
+    from flash_dropout.cuda.binding_gemm import GEMM
+    M, N, K = mnk
+    x, w, dy = _inputs(M, N, K, seed=0)
+    mask_np = pm.block_mask(M, K, 128, p, seed=0, offset=int(p * 1000))
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, 128, p, w, dy)
+    ext = GEMM()
+    mask = torch.from_numpy(mask_np).to(DEV)
+    A, B, dC = x.to(DEV), w.to(DEV), dy.to(DEV)
+    s = 1 / (1 - p)
+    C = ext.gemm_dsd(A, B, mask, 128, s)
+    dA = ext.gemm_sdd(dC, B.T, mask, 128, s)
+    dB = ext.gemm_dsd(A.T, dC.T, mask.T, 128, s).T
+    _close(C, y_ref, "C")
+    _close(dB, dw_ref, "dB")
+    _close(dA, dx_ref, "dA")
+    # dropped blocks of dA are exact zeros (matmul_sdd.cuh:64-65 writes them too)
+    keep = md._keep_matrix(mask_np, M, K, 128)
+    assert (dA.float().cpu()[keep == 0] == 0).all()
+
+
+def test_golden_cases_from_the_reference(built_lib, golden):
+    """fp16 kernels on the very inputs the reference saw, against the reference's own fp32 outputs."""
+    from flash_dropout.cuda.binding_gemm import GEMM
+    ext = GEMM()
+    ran = 0
+    for i in range(int(golden["mm_count"])):
+        M, N, K, bs, _ = (int(v) for v in golden[f"mm{i}_cfg"])
+        if bs % 128:
+            continue
+        p = float(golden[f"mm{i}_p"])
+        x, w, dy = (torch.from_numpy(golden[f"mm{i}_{n}"]).to(DEV) for n in ("x", "w", "dy"))
+        mask = torch.from_numpy(golden[f"mm{i}_mask"]).to(DEV)
+        s = 1 / (1 - p)
+        _close(ext.gemm_dsd(x, w, mask, bs, s), torch.from_numpy(golden[f"mm{i}_y"]), f"y[{i}]")
+        _close(ext.gemm_sdd(dy, w.T, mask, bs, s), torch.from_numpy(golden[f"mm{i}_dx"]), f"dx[{i}]")
+        _close(ext.gemm_dsd(x.T, dy.T, mask.T, bs, s).T, torch.from_numpy(golden[f"mm{i}_dw"]), f"dw[{i}]")
+        ran += 1
+    assert ran >= 3
+
+
+@pytest.mark.parametrize("la,lb", list(product(("row", "col"), repeat=2)))
+def test_all_operand_layouts(built_lib, la, lb):
+    """The 4 (row|col)-major operand combinations of flash_dropout/cuda/binding_gemm.py:98-133 (2048^3, p=0.2)."""
+    from flash_dropout.cuda.binding_gemm import GEMM
+    M = N = K = 2048
+    p = 0.2
+    x, w, _ = _inputs(M, N, K, seed=1)
+    A, B = x.to(DEV), w.to(DEV)
+    if la == "col":
+        A = A.T.contiguous().T
+    if lb == "col":
+        B = B.T.contiguous().T
+    ext = GEMM()
+    _close(ext.gemm(A, B), x.float() @ w.float().T, "gemm")
+    mk = pm.block_mask(M, K, 128, p, seed=2)
+    _close(ext.gemm_dsd(A, B, torch.from_numpy(mk).to(DEV), 128, 1 / (1 - p)), md.forward(x, mk, 128, p, w), "dsd")
+    mn = pm.block_mask(M, N, 128, p, seed=3)
+    want = (x.float() @ w.float().T) * md._keep_matrix(mn, M, N, 128) / (1 - p)
+    _close(ext.gemm_sdd(A, B, torch.from_numpy(mn).to(DEV), 128, 1 / (1 - p)), want, "sdd")
+
+
+@pytest.mark.parametrize("M,N,K,p", [(300, 264, 392, 0.4), (512, 1024, 784, 0.5), (129, 8, 136, 0.3),
+                                      (1000, 136, 576, 0.5), (64, 64, 64, 0.0), (2048, 128, 640, 0.5)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_ragged_shapes_and_bf16(built_lib, M, N, K, p, dtype):
+    """Shapes that are not multiples of 128 (the reference asserts divisibility, matmul_dsd.cuh:87-95)."""
+    from flash_dropout import _lib
+    from flash_dropout.cuda.binding_gemm import BlockPlan, dsd, sdd
+    x, w, dy = _inputs(M, N, K, seed=5, dtype=dtype)
+    mask_np = pm.block_mask(M, K, 128, p, seed=6)
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, 128, p, w, dy)
+    plan = BlockPlan.from_mask(torch.from_numpy(mask_np).to(DEV), M, K, 128)
+    A, B, dC = x.to(DEV), w.to(DEV), dy.to(DEV)
+    s = 1 / (1 - p)
+    tol = dict(rtol=RTOL, atol=ATOL) if dtype == torch.float16 else dict(rtol=2e-2, atol=4e-2)   # bf16: 8-bit mantissa
+    torch.testing.assert_close(dsd(A, B, plan, _lib.SD_PLAN_ROWS, s).float().cpu(), y_ref, **tol)
+    torch.testing.assert_close(sdd(dC, B.T, plan, s).float().cpu(), dx_ref, **tol)
+    dW = torch.full((N, K), float("nan"), device=DEV, dtype=dtype)
+    dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, s, out=dW.T)          # transposed store straight into dW[N, K]
+    torch.testing.assert_close(dW.float().cpu(), dw_ref, **tol)
+
+
+def test_block_size_larger_than_tile(built_lib):
+    from flash_dropout.cuda.binding_gemm import GEMM
+    M, N, K, bs, p = 1024, 256, 1536, 256, 0.5
+    x, w, dy = _inputs(M, N, K, seed=7)
+    mask_np = pm.block_mask(M, K, bs, p, seed=8)
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, bs, p, w, dy)
+    mask = torch.from_numpy(mask_np).to(DEV)
+    ext = GEMM()
+    _close(ext.gemm_dsd(x.to(DEV), w.to(DEV), mask, bs, 2.0), y_ref, "y")
+    _close(ext.gemm_sdd(dy.to(DEV), w.to(DEV).T, mask, bs, 2.0), dx_ref, "dx")
+    _close(ext.gemm_dsd(x.to(DEV).T, dy.to(DEV).T, mask.T, bs, 2.0).T, dw_ref, "dw")
+
+
+def test_full_size_properties_4096(built_lib):
+    """BASELINE config 2 (4096^3, p = 0.5): size-independent properties instead of a CPU oracle pass.
+
+    * skipping a dropped tile == multiplying by an explicitly zeroed tile, bit for bit (zeros add nothing
+      to an fp32 accumulator), for all three products;
+    * p = 0 plan == the dense kernel, bit for bit;
+    * dropped tiles of dx are exact zeros; linearity in the scale.
+    """
+    from flash_dropout import _lib
+    from flash_dropout.cuda.binding_gemm import BlockPlan, dense, dsd, sdd
+    M = N = K = 4096
+    p = 0.5
+    x, w, dy = (t.to(DEV) for t in _inputs(M, N, K, seed=9))
+    plan = BlockPlan.from_seed(M, K, 128, p, 0, 0, DEV)
+    assert np.array_equal(plan.mask.cpu().numpy(), pm.block_mask(M, K, 128, p, 0, 0))
+    keep = (~plan.mask).repeat_interleave(128, 0).repeat_interleave(128, 1)
+    xz = x * keep
+    s = 1 / (1 - p)
+    y = dsd(x, w, plan, _lib.SD_PLAN_ROWS, s)
+    assert torch.equal(y, dense(xz, w, scale=s))
+    dx = sdd(dy, w.T, plan, s)
+    assert torch.equal(dx, dense(dy, w.T, scale=s) * keep)
+    dw = torch.empty(N, K, device=DEV, dtype=torch.float16)
+    dsd(x.T, dy.T, plan, _lib.SD_PLAN_COLS, s, out=dw.T)
+    assert torch.equal(dw.T, dense(xz.T, dy.T, scale=s))
+    full = BlockPlan.from_seed(M, K, 128, 0.0, 0, 0, DEV)
+    assert torch.equal(dsd(x, w, full, _lib.SD_PLAN_ROWS, 1.0), dense(x, w))
+    assert torch.equal(sdd(dy, w.T, full, 1.0), dense(dy, w.T))
+    # against cuBLAS on the masked input (fp32 accumulate both sides)
+    torch.testing.assert_close(y.float(), s * (xz.float() @ w.float().T), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(dsd(x, w, plan, _lib.SD_PLAN_ROWS, 2 * s).float(), 2 * y.float(), rtol=2e-3, atol=2e-3)
+
+
+def test_errors_mirror_the_reference(built_lib):
+    """gemm_binding.cu:18-22,49-50,87-89 raise RuntimeError for device / rank / stride / dtype problems."""
+    from flash_dropout.cuda.binding_gemm import GEMM
+    ext = GEMM()
+    a = torch.zeros(256, 256, device=DEV, dtype=torch.float16)
+    mask = torch.zeros(2, 2, device=DEV, dtype=torch.bool)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ext.gemm_dsd(a.cpu(), a, mask, 128, 1.0)
+    with pytest.raises(RuntimeError, match="2D"):
+        ext.gemm_dsd(a[None], a, mask, 128, 1.0)
+    with pytest.raises(RuntimeError, match="row or column major"):
+        ext.gemm_dsd(a[:, ::2], a[:, ::2], mask[:, :1], 128, 1.0)
+    with pytest.raises(RuntimeError, match="half"):
+        ext.gemm_dsd(a.float(), a.float(), mask, 128, 1.0)
+    with pytest.raises(RuntimeError, match="bool"):
+        ext.gemm_dsd(a, a, mask.to(torch.uint8), 128, 1.0)
+    with pytest.raises(RuntimeError, match="mask shape"):
+        ext.gemm_dsd(a, a, mask[:1], 128, 1.0)
+    with pytest.raises(ValueError, match="multiple of 128"):
+        ext.gemm_dsd(a, a, mask, 64, 1.0)
+    assert ext.gemm(a, a).abs().sum().item() == 0     # the context is still healthy

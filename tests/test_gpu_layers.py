@@ -1,0 +1,100 @@
+"""Autograd op and modules on the GPU vs the CPU oracle (forward, dX, dW), plus the conv composition."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import masked_dense as md
+from oracle import philox_mask as pm
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+RTOL = ATOL = 1e-2
+
+
+def test_autograd_op_matches_oracle(built_lib):
+    import flash_dropout.functional as F
+    from flash_dropout import random as sd_random
+    M, N, K, p = 512, 384, 1024, 0.5
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(M, K, generator=g) * K ** -0.25).half()
+    w = (torch.randn(N, K, generator=g) * K ** -0.25).half()
+    dy = (torch.randn(M, N, generator=g) * N ** -0.25).half()
+    sd_random.manual_seed(77, subsequence=0)
+    xa, wa = x.to(DEV).requires_grad_(), w.to(DEV).requires_grad_()
+    y = F.cuda_blockwise_dropout_matmul(xa, wa, 128, p)
+    y.backward(dy.to(DEV))
+    mask = pm.block_mask(M, K, 128, p, seed=77, offset=0)        # first mask after manual_seed(77)
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask, 128, p, w, dy)
+    torch.testing.assert_close(y.float().cpu(), y_ref, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(xa.grad.float().cpu(), dx_ref, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(wa.grad.float().cpu(), dw_ref, rtol=RTOL, atol=ATOL)
+    assert wa.grad.is_contiguous() and xa.grad.dtype == torch.float16
+    # the next call draws the next mask of the stream
+    y2 = F.cuda_blockwise_dropout_matmul(xa, wa, 128, p)
+    mask2 = pm.block_mask(M, K, 128, p, seed=77, offset=1)
+    torch.testing.assert_close(y2.float().cpu(), md.forward(x, mask2, 128, p, w), rtol=RTOL, atol=ATOL)
+    with pytest.raises(AssertionError):
+        F.cuda_blockwise_dropout_matmul(xa, wa, 128, 1.0)
+    with pytest.raises(RuntimeError):
+        F.cuda_blockwise_dropout_matmul(xa.float(), wa, 128, 0.5)
+    sd_random.follow_torch_seed()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_dropout_mm_under_autocast(built_lib, dtype):
+    from flash_dropout import random as sd_random
+    from flash_dropout.layers import DropoutMM
+    torch.manual_seed(0)
+    layer = DropoutMM(768, 256, p=0.5, variant="blockwise[cuda]", block_size=(128, 128)).to(DEV)
+    x = torch.randn(4, 96, 768, device=DEV, requires_grad=True)
+    sd_random.manual_seed(5, subsequence=1)
+    with torch.autocast("cuda", dtype=dtype):
+        y = layer(x)
+    assert y.dtype == dtype and tuple(y.shape) == (4, 96, 256)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert layer.weight.grad.dtype == torch.float32 and x.grad.dtype == torch.float32
+    mask = pm.block_mask(384, 768, 128, 0.5, seed=5, offset=(1 << 40))
+    xq, wq, dyq = x.detach().to(dtype).cpu().view(384, 768), layer.weight.detach().to(dtype).cpu(), dy.cpu().view(384, 256)
+    y_ref, dx_ref, dw_ref = md.forward_backward(xq, mask, 128, 0.5, wq, dyq)
+    tol = dict(rtol=1e-2, atol=1e-2) if dtype == torch.float16 else dict(rtol=2e-2, atol=4e-2)
+    torch.testing.assert_close(y.float().cpu().view(384, 256), y_ref, **tol)
+    torch.testing.assert_close(x.grad.cpu().view(384, 768), dx_ref, **tol)
+    torch.testing.assert_close(layer.weight.grad.cpu(), dw_ref, **tol)
+    layer.eval()
+    torch.testing.assert_close(layer(x), torch.nn.functional.linear(x, layer.weight))
+    sd_random.follow_torch_seed()
+
+
+def test_dropout_conv2d_blockwise(built_lib):
+    """Blockwise dropout on the im2col matrix: forward, dX (through fold) and dW vs the oracle."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.layers import DropoutConv2d
+    torch.manual_seed(1)
+    N, C, H, W, Ko, p = 8, 64, 16, 16, 128, 0.5
+    conv = DropoutConv2d(C, Ko, (3, 3), padding=(1, 1), p=p, variant="blockwise[cuda]", block_size=128).to(DEV).half()
+    x = torch.randn(N, C, H, W, device=DEV, dtype=torch.float16, requires_grad=True)
+    sd_random.manual_seed(9, subsequence=0)
+    y = conv(x)
+    assert tuple(y.shape) == (N, Ko, H, W)
+    dy = (torch.randn_like(y) * 0.1)
+    y.backward(dy)
+    M, K = N * H * W, C * 9
+    mask = pm.block_mask(M, K, 128, p, seed=9, offset=0)
+    assert mask.shape == (16, 5)
+    xc, kc = x.detach().cpu(), conv.weight.detach().cpu()
+    y_ref = md.conv_forward(xc, kc, mask, 128, p, padding=(1, 1))
+    dx_ref, dw_ref = md.conv_backward(xc, kc, mask, 128, p, dy.cpu(), padding=(1, 1))
+    torch.testing.assert_close(y.float().cpu(), y_ref, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(conv.weight.grad.float().cpu(), dw_ref, rtol=RTOL, atol=2e-2)
+    torch.testing.assert_close(x.grad.float().cpu(), dx_ref, rtol=RTOL, atol=2e-2)
+    sd_random.follow_torch_seed()
+
+
+def test_non_contiguous_grad_output(built_lib):
+    import flash_dropout.functional as F
+    x = torch.randn(256, 256, device=DEV, dtype=torch.float16, requires_grad=True)
+    w = torch.randn(256, 256, device=DEV, dtype=torch.float16, requires_grad=True)
+    y = F.cuda_blockwise_dropout_matmul(x, w, 128, 0.0)
+    y.sum().backward()                                   # expanded (stride-0) upstream gradient
+    torch.testing.assert_close(x.grad.float(), w.float().sum(0).expand(256, 256), rtol=1e-2, atol=1e-2)
