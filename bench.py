@@ -259,7 +259,7 @@ def run_ours(args) -> None:
 
     # ---- speed-up over the same kernels at p = 0 (the other half of the headline metric), rank 0 only
     extra = {}
-    if rank == 0:
+    if rank == 0 and not args.no_extras:
         def time_three(plan, sc, reps=10):
             x, w, dy, y, dx, dw = sets[0]
             out = []
@@ -321,7 +321,7 @@ def run_ours(args) -> None:
             "gpu_launches": 4 * steps, "clocks": clocks,
         }
         line.update(extra)
-        if world == 1:
+        if world == 1 and not args.no_extras:
             from oracle import cpu_path
             info = cpu_path.host_info()
             r = cpu_path.time_linear_fwd_bwd(M, N, K, BLOCK, P_DROP, seed=SEED, budget_s=12.0, max_passes=4)
@@ -341,6 +341,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the p=0 comparison and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -351,6 +353,8 @@ def main() -> None:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__),
                "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup)]
+        if args.no_extras:
+            cmd.append("--no-extras")
         raise SystemExit(subprocess.call(cmd))
     run_ours(args)
 
