@@ -74,7 +74,7 @@ const char* sd_last_error(void);
  *                                  torch.nonzero(~mask) used by
  *                                  flash_dropout/functional/blockwise_dropout_matmul_triton.py:48
  *   drop_pairs[2*R*C]            : (row, col) of dropped tiles in row-major order
- *   row_order[R], col_order[C]   : permutations, most kept tiles first (scheduling hint)
+ *   row_order[R], col_order[C]   : permutations, most kept tiles first
  *   sdd_items[3*R*ceil(C/2)]     : (row, col0, col1 or -1): kept tiles of one row paired up
  *   mask[R*C] (uint8)            : 1 = dropped, row-major, tile granularity
  * ------------------------------------------------------------------------------------------ */
@@ -110,14 +110,29 @@ int sd_plan_from_mask(void* plan, int R, int C, int rep, const uint8_t* mask,
 /* ------------------------------------------------------------------------------------------
  * GEMMs.  `status` is an optional device int32 (may be NULL) that a kernel sets to a non-zero
  * code if one of its bounded waits expires; sd_check_status() copies it back and translates.
+ *
+ * `workspace` is optional device scratch (may be NULL).  A launch with fewer 128x256 output tiles
+ * than SMs (small layers; the dW product of a conv, whose reduction runs over all N*P*Q rows) would
+ * leave SMs idle if tiles were handed out whole, so with a workspace it cuts its stream of kept K
+ * tiles into equal shares per SM instead: a CTA whose share begins inside an output tile parks one
+ * fp32 partial tile in the workspace and the tile's owner adds the partials (in CTA order, so
+ * results are reproducible) before finishing the tile.  Launches with at least one tile per SM
+ * never touch the workspace.  It is sd_workspace_bytes() bytes for the current device (4 KiB of
+ * flags + 128 KiB per SM, 18.5 MiB on a B200), 16-byte aligned, and must be passed through
+ * sd_workspace_init() once before its first use (and again after a launch that reported
+ * SD_ERR_TIMEOUT).  A launch leaves the flags cleared.  Launches that may overlap on the GPU
+ * (different streams) need different workspaces.  No counterpart in the reference, whose kernels
+ * use a fixed one-CTA-per-tile grid (flash_dropout/cuda/src/matmul_dsd.cuh:99-105).
  * ------------------------------------------------------------------------------------------ */
+size_t sd_workspace_bytes(void);
+int sd_workspace_init(void* workspace, void* stream);
 
 /* Dense C = scale * A . B^T.  Replaces GEMM.gemm (flash_dropout/cuda/binding_gemm.py:26-27,
  * flash_dropout/cuda/src/gemm.cuh:143-167). */
 int sd_gemm(const void* A, int64_t a_rs, int64_t a_cs,
             const void* B, int64_t b_rs, int64_t b_cs,
             void* C, int64_t c_rs, int64_t c_cs,
-            int M, int N, int K, float scale, int dtype, int* status, void* stream);
+            int M, int N, int K, float scale, int dtype, void* workspace, int* status, void* stream);
 
 /* DSD: C = scale * (keep o A) . B^T, skipping dropped 128-wide K tiles of each 128-row block
  * of A.  Replaces GEMM.gemm_dsd (flash_dropout/cuda/binding_gemm.py:29-37,
@@ -129,7 +144,7 @@ int sd_gemm_dsd(const void* A, int64_t a_rs, int64_t a_cs,
                 const void* B, int64_t b_rs, int64_t b_cs,
                 void* C, int64_t c_rs, int64_t c_cs,
                 int M, int N, int K, const void* plan, int plan_side,
-                float scale, int dtype, int* status, void* stream);
+                float scale, int dtype, void* workspace, int* status, void* stream);
 
 /* SDD: C = scale * keep o (A . B^T): only kept 128x128 output tiles are computed, dropped tiles
  * are written as zeros.  The plan is ceil(M/128) x ceil(N/128).  Replaces GEMM.gemm_sdd
@@ -138,7 +153,7 @@ int sd_gemm_sdd(const void* A, int64_t a_rs, int64_t a_cs,
                 const void* B, int64_t b_rs, int64_t b_cs,
                 void* C, int64_t c_rs, int64_t c_cs,
                 int M, int N, int K, const void* plan,
-                float scale, int dtype, int* status, void* stream);
+                float scale, int dtype, void* workspace, int* status, void* stream);
 
 /* Synchronises the stream, reads *status and returns SD_OK or SD_ERR_TIMEOUT. */
 int sd_check_status(const int* status, void* stream);

@@ -21,6 +21,22 @@
 // Both operands may be K-major (reduction dimension contiguous) or MN-major; that is the
 // (row|col)-major x (row|col)-major operand matrix of flash_dropout/cuda/src/gemm_binding.cu:51-53.
 //
+// Scheduling.  With several output tiles per SM, whole tiles are dealt round-robin from a list sorted
+// heaviest row block first.  With fewer tiles than SMs (small layers, or the dW product of a conv whose
+// reduction runs over hundreds of thousands of rows) the unit of work becomes one kept 128-wide K tile of
+// one output tile: all units of the launch form one sequence (tiles in row-block order, kept K tiles
+// ascending) that is cut into gridDim.x equal contiguous ranges, one per CTA, so every SM gets the same
+// number of MMA steps.  A range may then begin or end inside an output tile:
+//   * the CTA that owns the first unit of a tile is its finisher and writes the result;
+//   * a CTA that starts in the middle of a tile computes its part first thing, stores the fp32
+//     partial accumulator in its own workspace slot and raises its flag;
+//   * the finisher (for which that tile is the last thing it does) waits, bounded, for the flags
+//     two segments ahead of time, adds the partials in CTA order (deterministic) straight into the
+//     TMEM accumulator the tile will use (tcgen05.st) and clears the flags; its MMAs then
+//     accumulate on top, so the tile ends with an ordinary epilogue and the fix-up is hidden
+//     behind the main loop of the segment in between.
+// The second schedule needs the caller's workspace; without one, whole tiles are used throughout.
+//
 // Every wait is bounded (sd_ptx.cuh: mbar_wait); on expiry the CTA records a code in the status
 // word, every role leaves its loop, TMEM is freed and the kernel returns normally.
 #include <cuda_bf16.h>
@@ -39,12 +55,19 @@ constexpr int B_HALF_BYTES = B_BYTES / 2;   // one 128-row half of the B tile
 constexpr int MN_ATOM_BYTES = 64 * BK * 2;  // 64 MN-elements x 64 K-rows, one MN-major TMA box
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TILE_SMEM = STAGES * STAGE_BYTES;          // 192 KiB
-constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int XPOSE_BYTES = 32 * 128 * 2;                // one 32-column chunk of a tile, transposed (fp16/bf16)
+constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/ + 2 * XPOSE_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
+// Workspace of the split schedule: flags first, then one fp32 partial tile per CTA.
+constexpr int WS_MAX_CTAS = 1024;
+constexpr size_t WS_FLAG_BYTES = WS_MAX_CTAS * sizeof(int);
+constexpr size_t WS_SLOT_FLOATS = size_t(BM) * BN;
+constexpr size_t WS_SLOT_BYTES = WS_SLOT_FLOATS * sizeof(float);   // 128 KiB
+
 enum GemmMode { MODE_DENSE = 0, MODE_DSD = 1, MODE_SDD = 2 };
-enum StatusCode { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_ACC = 3, ST_EPILOGUE = 4 };
+enum StatusCode { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_ACC = 3, ST_EPILOGUE = 4, ST_FIXUP = 5 };
 
 struct GemmArgs {
     int mode;
@@ -56,51 +79,143 @@ struct GemmArgs {
     int n_row_blocks, n_col_tiles;   // dense / DSD tile grid (128 x 256 tiles)
     const int* list_ptr;             // DSD: kept K-tile list of row block rb = list_idx[list_ptr[rb] .. list_ptr[rb+1])
     const int* list_idx;
-    const int* order;                // DSD: row blocks, heaviest first (may be null)
+    const int* order;                // DSD: row blocks sorted by kept count, heaviest first
     const int* items;                // SDD: (row block, col tile 0, col tile 1 or -1)
     const int* n_items;
     const int* zero_pairs;           // SDD: dropped (row block, col tile) pairs
     const int* n_zero;
     int* status;
     uint32_t idesc256, idesc128;
+    int split;                       // 1: equal unit ranges with fix-up (needs the workspace); 0: whole tiles
+    float* ws_slots;
+    int* ws_flags;
 };
 
-struct Work {
+// The part [i0, i1) of one output tile's kept K-tile list that this CTA computes.
+struct Seg {
     int a_row, b_row0, b_row1;   // element coordinates along the operands' MN dimension; b_row1 < 0: absent
-    int nk;                      // number of 128-wide K tiles
-    const int* klist;            // their indices, or null for 0..nk-1
+    const int* klist;            // kept K-tile indices of the whole tile, or null for 0..nk-1
+    int nk, i0, i1;
+    long long tile_end;          // unit index one past the tile's last unit
 };
 
-__device__ __forceinline__ int num_work(const GemmArgs& g) {
-    return g.mode == MODE_SDD ? __ldg(g.n_items) : g.n_row_blocks * g.n_col_tiles;
-}
+// Walks this CTA's share of the launch.  Every role of the CTA runs its own copy and sees the same
+// segments in the same order.  Two schedules:
+//   split == 0 : whole output tiles, dealt round-robin from a list sorted heaviest row block first
+//                (longest-processing-time order); the choice when there are several tiles per SM;
+//   split == 1 : the unit sequence cut into gridDim.x equal ranges (see the file header); the choice
+//                when there are fewer tiles than SMs, so that every SM still gets work.
+struct WorkIter {
+    long long u, u_end, total;   // split: current unit, end of this CTA's range, all units
+    int t, n_tiles, stride;      // whole tiles: next tile, tile count, gridDim.x
+    int nk_uniform;              // dense / SDD: K tiles per output tile
+    int rb, nt, i0;              // split position: row block (SDD: work item), n tile, offset inside the tile
+    bool split;
 
-__device__ __forceinline__ Work get_work(const GemmArgs& g, int t) {
-    Work w;
-    if (g.mode == MODE_SDD) {
-        const int mb = __ldg(g.items + 3 * t), c0 = __ldg(g.items + 3 * t + 1), c1 = __ldg(g.items + 3 * t + 2);
-        w.a_row = mb * 128;
-        w.b_row0 = c0 * 128;
-        w.b_row1 = c1 >= 0 ? c1 * 128 : -1;
-        w.nk = (g.KK + 127) >> 7;
-        w.klist = nullptr;
-    } else {
-        const int rbi = t / g.n_col_tiles, nt = t - rbi * g.n_col_tiles;
-        const int rb = g.order ? __ldg(g.order + rbi) : rbi;
-        w.a_row = rb * 128;
-        w.b_row0 = nt * BN;
-        w.b_row1 = (nt * BN + 128 < g.NN) ? nt * BN + 128 : -1;
-        if (g.mode == MODE_DSD) {
-            const int beg = __ldg(g.list_ptr + rb);
-            w.nk = __ldg(g.list_ptr + rb + 1) - beg;
-            w.klist = g.list_idx + beg;
-        } else {
-            w.nk = (g.KK + 127) >> 7;
-            w.klist = nullptr;
+    __device__ __forceinline__ static long long range_start(long long total, int cta, int n_ctas) {
+        return total * cta / n_ctas;
+    }
+    __device__ __forceinline__ int count(const GemmArgs& g, int r) const {
+        return __ldg(g.list_ptr + r + 1) - __ldg(g.list_ptr + r);
+    }
+    __device__ __forceinline__ int tile_len(const GemmArgs& g) const {
+        return g.mode == MODE_DSD ? count(g, rb) : nk_uniform;
+    }
+    __device__ __forceinline__ void next_tile(const GemmArgs& g) {
+        i0 = 0;
+        if (g.mode == MODE_SDD) { ++rb; return; }
+        if (++nt == g.n_col_tiles) {
+            nt = 0;
+            ++rb;
+            if (g.mode == MODE_DSD)
+                while (rb < g.n_row_blocks && count(g, rb) == 0) ++rb;
         }
     }
-    return w;
-}
+    __device__ void init(const GemmArgs& g, int cta, int n_ctas) {
+        split = g.split != 0;
+        nk_uniform = (g.KK + 127) >> 7;
+        n_tiles = g.mode == MODE_SDD ? __ldg(g.n_items) : g.n_row_blocks * g.n_col_tiles;
+        t = cta;
+        stride = n_ctas;
+        u = u_end = total = 0;
+        rb = nt = i0 = 0;
+        if (!split) return;
+        if (g.mode == MODE_DSD) total = (long long)g.n_col_tiles * __ldg(g.list_ptr + g.n_row_blocks);
+        else total = (long long)n_tiles * nk_uniform;
+        u = range_start(total, cta, n_ctas);
+        u_end = range_start(total, cta + 1, n_ctas);
+        if (u >= u_end) return;
+        if (g.mode == MODE_DSD) {
+            const int v = int(u / g.n_col_tiles);
+            int lo = 0, hi = g.n_row_blocks - 1;   // first row block with list_ptr[r + 1] > v
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (__ldg(g.list_ptr + mid + 1) > v) hi = mid; else lo = mid + 1;
+            }
+            rb = lo;
+            const long long rem = u - (long long)g.n_col_tiles * __ldg(g.list_ptr + rb);
+            const int cnt = count(g, rb);
+            nt = int(rem / cnt);
+            i0 = int(rem - (long long)nt * cnt);
+        } else {
+            const long long tile = u / nk_uniform;
+            i0 = int(u - tile * nk_uniform);
+            if (g.mode == MODE_SDD) { rb = int(tile); }
+            else { rb = int(tile / g.n_col_tiles); nt = int(tile - (long long)rb * g.n_col_tiles); }
+        }
+    }
+    __device__ __forceinline__ void fill(const GemmArgs& g, Seg& s, int row_block, int n_tile) const {
+        if (g.mode == MODE_SDD) {
+            const int mb = __ldg(g.items + 3 * row_block), c0 = __ldg(g.items + 3 * row_block + 1),
+                      c1 = __ldg(g.items + 3 * row_block + 2);
+            s.a_row = mb * 128;
+            s.b_row0 = c0 * 128;
+            s.b_row1 = c1 >= 0 ? c1 * 128 : -1;
+            s.nk = nk_uniform;
+            s.klist = nullptr;
+        } else {
+            s.a_row = row_block * 128;
+            s.b_row0 = n_tile * BN;
+            s.b_row1 = (n_tile * BN + 128 < g.NN) ? n_tile * BN + 128 : -1;
+            if (g.mode == MODE_DSD) {
+                const int beg = __ldg(g.list_ptr + row_block);
+                s.nk = __ldg(g.list_ptr + row_block + 1) - beg;
+                s.klist = g.list_idx + beg;
+            } else {
+                s.nk = nk_uniform;
+                s.klist = nullptr;
+            }
+        }
+    }
+    __device__ bool next(const GemmArgs& g, Seg& s) {
+        if (!split) {
+            for (; t < n_tiles; t += stride) {
+                if (g.mode == MODE_SDD) {
+                    fill(g, s, t, 0);
+                } else {
+                    const int rbi = t / g.n_col_tiles;
+                    fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, t - rbi * g.n_col_tiles);
+                }
+                if (s.nk == 0) continue;          // empty row blocks are zero-filled by the epilogue warps
+                s.i0 = 0;
+                s.i1 = s.nk;
+                s.tile_end = 0;
+                t += stride;
+                return true;
+            }
+            return false;
+        }
+        if (u >= u_end) return false;
+        fill(g, s, rb, nt);
+        s.i0 = i0;
+        const long long room = u_end - u;
+        s.i1 = (room >= s.nk - i0) ? s.nk : i0 + int(room);
+        s.tile_end = u - i0 + s.nk;
+        u += s.i1 - i0;
+        if (s.i1 == s.nk) next_tile(g); else i0 = s.i1;
+        return true;
+    }
+};
 
 // ------------------------------------------------------------------ epilogue stores
 __device__ __forceinline__ uint32_t pack2(float a, float b, int is_bf16) {
@@ -141,8 +256,28 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& g, bool vec_ok, int 
     }
 }
 
+// Column-major result (row stride 1): the 32-column chunk is transposed through shared memory so that global
+// stores are 256-byte rows of the result instead of 2-byte scalars.  `xs` is XPOSE_BYTES of shared memory owned
+// by the epilogue group; all 128 epilogue threads call this together.
+__device__ __forceinline__ void store_chunk_transposed(const GemmArgs& g, unsigned short* xs, int etid, int row0, int col,
+                                                       const uint32_t (&r)[32]) {
+    // xs[j][k]: j = column inside the chunk, k = row inside the tile
+#pragma unroll
+    for (int j = 0; j < 32; ++j) xs[j * 128 + etid] = cvt1(__uint_as_float(r[j]) * g.scale, g.is_bf16);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    unsigned short* C = static_cast<unsigned short*>(g.C);
+    const int kc = (etid & 15) * 8, jsub = etid >> 4;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int j = pass * 8 + jsub;
+        if (col + j < g.NN && row0 + kc < g.MM)
+            *reinterpret_cast<uint4*>(C + (long long)(col + j) * g.c_cs + row0 + kc) =
+                *reinterpret_cast<const uint4*>(xs + j * 128 + kc);
+    }
+}
+
 // Zero a 128 x 128 output tile with the 128 epilogue threads (tid in [0,128)).
-__device__ __forceinline__ void zero_tile(const GemmArgs& g, bool vec_ok, int tid, int row0, int col0) {
+__device__ __forceinline__ void zero_tile(const GemmArgs& g, bool vec_ok, bool vec_t_ok, int tid, int row0, int col0) {
     unsigned short* C = static_cast<unsigned short*>(g.C);
     if (vec_ok && row0 + 128 <= g.MM && col0 + 128 <= g.NN) {
         const int cchunk = tid & 15, rsub = tid >> 4;
@@ -150,6 +285,13 @@ __device__ __forceinline__ void zero_tile(const GemmArgs& g, bool vec_ok, int ti
         for (int i = 0; i < 16; ++i) {
             const int row = row0 + i * 8 + rsub;
             *reinterpret_cast<uint4*>(C + (long long)row * g.c_rs + col0 + cchunk * 8) = make_uint4(0, 0, 0, 0);
+        }
+    } else if (vec_t_ok && row0 + 128 <= g.MM && col0 + 128 <= g.NN) {
+        const int rchunk = tid & 15, csub = tid >> 4;
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+            const int col = col0 + i * 8 + csub;
+            *reinterpret_cast<uint4*>(C + (long long)col * g.c_cs + row0 + rchunk * 8) = make_uint4(0, 0, 0, 0);
         }
     } else if (g.c_rs == 1) {
         for (int j = 0; j < 128; ++j)
@@ -159,6 +301,55 @@ __device__ __forceinline__ void zero_tile(const GemmArgs& g, bool vec_ok, int ti
             if (row0 + i < g.MM && col0 + tid < g.NN) C[(long long)(row0 + i) * g.c_rs + (long long)(col0 + tid) * g.c_cs] = 0;
     }
 }
+
+// ------------------------------------------------------------------ epilogue-group helpers
+// The four epilogue warps (128 threads) synchronise on named barrier 1, never on barrier 0.
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(r)
+        : "r"(uint32_t(ok))
+        : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void flag_set(int* flag, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(v) : "memory");
+}
+// Bounded wait for another CTA's flag (same limit and abort protocol as mbar_wait).
+__device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_flag, int* status, int code) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v != 0) return true;
+        if ((it & 0xff) == 0xff) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+#ifdef SD_TIMING
+// Development aid (not compiled into the product): per-CTA timestamps of one launch.
+__device__ unsigned long long sd_timing[1024][8];
+#define SD_STAMP(slot)                                                                     \
+    do {                                                                                   \
+        sd_timing[blockIdx.x][slot] = global_timer_ns();                                   \
+    } while (0)
+#else
+#define SD_STAMP(slot) do {} while (0)
+#endif
 
 // ------------------------------------------------------------------ the kernel
 template <bool A_MN, bool B_MN>
@@ -170,11 +361,13 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     const uint32_t tiles = (raw_addr + 1023u) & ~1023u;   // 128B swizzle atoms need 1024-byte alignment
     uint8_t* aligned = smem_raw + (tiles - raw_addr);
     uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + TILE_SMEM);
-    // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty
+    // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty, [12] preload
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 13);
+    const uint32_t bar_preload = bar_tempty + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
+    unsigned short* xpose = reinterpret_cast<unsigned short*>(aligned + TILE_SMEM + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -187,6 +380,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             mbar_init(bar_tfull + 8 * a, 1);
             mbar_init(bar_tempty + 8 * a, 4);
         }
+        mbar_init(bar_preload, 4);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmapA);
@@ -201,7 +395,10 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int n_work = num_work(g);
+    const int n_ctas = gridDim.x, cta = blockIdx.x;
+#ifdef SD_TIMING
+    if (threadIdx.x == 0) { SD_STAMP(0); sd_timing[blockIdx.x][6] = clock64(); }
+#endif
 
     if (warp == 0) {
         // ============================== producer
@@ -209,10 +406,12 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < n_work; t += gridDim.x) {
-                const Work w = get_work(g, t);
+            WorkIter it;
+            it.init(g, cta, n_ctas);
+            Seg w;
+            while (ok && it.next(g, w)) {
                 const uint32_t tx = A_BYTES + (w.b_row1 >= 0 ? B_BYTES : B_HALF_BYTES);
-                for (int i = 0; ok && i < w.nk; ++i) {
+                for (int i = w.i0; ok && i < w.i1; ++i) {
                     const int kb = w.klist ? __ldg(w.klist + i) : i;
                     for (int h = 0; h < 2; ++h) {
                         const int k = kb * 128 + h * BK;
@@ -242,6 +441,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                     }
                 }
             }
+            SD_STAMP(1);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -254,15 +454,21 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < n_work; t += gridDim.x) {
-                const Work w = get_work(g, t);
-                if (w.nk == 0) continue;
+            WorkIter it;
+            it.init(g, cta, n_ctas);
+            Seg w;
+            while (ok && it.next(g, w)) {
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, g.status, ST_MMA_ACC)) break;
+                uint32_t accumulate = 0;
+                if (w.i0 == 0 && w.i1 < w.nk) {
+                    // finisher: the other CTAs' partial sums are placed in this accumulator first
+                    if (!mbar_wait(bar_preload, 0, abort_flag, g.status, ST_FIXUP)) break;
+                    accumulate = 1;
+                }
                 tc_fence_after();
                 const uint32_t d = tmem_base + acc * BN;
                 const uint32_t idesc = w.b_row1 >= 0 ? g.idesc256 : g.idesc128;
-                uint32_t accumulate = 0;
-                for (int i = 0; ok && i < w.nk; ++i) {
+                for (int i = w.i0; ok && i < w.i1; ++i) {
                     const int kb = w.klist ? __ldg(w.klist + i) : i;
                     for (int h = 0; h < 2; ++h) {
                         if (kb * 128 + h * BK >= g.KK) break;
@@ -284,45 +490,119 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1;
             }
+            SD_STAMP(2);
         }
         __syncwarp();
     } else {
         // ============================== epilogue (warps 2..5 own TMEM lane quadrants 2,3,0,1)
         const int quad = warp & 3;
         const int etid = quad * 32 + lane;   // 0..127, also the row inside the tile this thread owns
-        const bool vec_ok = g.c_cs == 1 && (g.c_rs & 7) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
+        const bool aligned16 = (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
+        const bool vec_ok = g.c_cs == 1 && (g.c_rs & 7) == 0 && aligned16;      // row-major result, 16-byte rows
+        const bool vec_t_ok = g.c_rs == 1 && (g.c_cs & 7) == 0 && aligned16;    // column-major result
+        // Output that no unit covers is zero-filled here, before the first accumulator is ready.
         if (g.mode == MODE_SDD) {
             const int nz = __ldg(g.n_zero);
-            for (int z = blockIdx.x; z < nz; z += gridDim.x)
-                zero_tile(g, vec_ok, etid, __ldg(g.zero_pairs + 2 * z) * 128, __ldg(g.zero_pairs + 2 * z + 1) * 128);
+            for (int z = cta; z < nz; z += n_ctas)
+                zero_tile(g, vec_ok, vec_t_ok, etid, __ldg(g.zero_pairs + 2 * z) * 128, __ldg(g.zero_pairs + 2 * z + 1) * 128);
+        } else if (g.mode == MODE_DSD) {
+            // row blocks with nothing kept: their 128x128 output tiles are spread over all CTAs
+            const int ncol = (g.NN + 127) >> 7;
+            for (int z = cta; z < g.n_row_blocks * ncol; z += n_ctas) {
+                const int rb = z / ncol;
+                if (__ldg(g.list_ptr + rb + 1) == __ldg(g.list_ptr + rb))
+                    zero_tile(g, vec_ok, vec_t_ok, etid, rb * 128, (z - rb * ncol) * 128);
+            }
         }
+        WorkIter it;
+        it.init(g, cta, n_ctas);
+        // Which of this CTA's segments (if any) is the head of a tile that other CTAs finish computing?
+        int fin_idx = -1, fin_chunks = 0;
+        long long fin_tile_end = 0;
+        {
+            WorkIter scan = it;
+            Seg s;
+            for (int n = 0; scan.next(g, s); ++n)
+                if (s.i0 == 0 && s.i1 < s.nk) { fin_idx = n; fin_chunks = s.b_row1 >= 0 ? 8 : 4; fin_tile_end = s.tile_end; }
+        }
+        // Adds the partial tiles of the contributing CTAs into TMEM buffer (fin_idx & 1).
+        auto preload = [&]() -> bool {
+            int last_c = cta;
+            for (int c = cta + 1; c < n_ctas && WorkIter::range_start(it.total, c, n_ctas) < fin_tile_end; ++c) last_c = c;
+            bool ok = true;
+            if (etid == 0)
+                for (int c = cta + 1; ok && c <= last_c; ++c)
+                    if (WorkIter::range_start(it.total, c + 1, n_ctas) > WorkIter::range_start(it.total, c, n_ctas))
+                        ok = flag_wait(g.ws_flags + c, abort_flag, g.status, ST_FIXUP);
+            if (!epilogue_all(ok)) return false;
+            const uint32_t taddr = tmem_base + (fin_idx & 1) * BN + (uint32_t(quad * 32) << 16);
+            for (int c = 0; c < fin_chunks; ++c) {
+                uint32_t r[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0;
+                for (int pc = cta + 1; pc <= last_c; ++pc) {
+                    if (WorkIter::range_start(it.total, pc + 1, n_ctas) == WorkIter::range_start(it.total, pc, n_ctas)) continue;
+                    const float* src = g.ws_slots + size_t(pc) * WS_SLOT_FLOATS + size_t(c * 32) * BM + etid;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(src + j * BM));
+                }
+                tmem_st_32x32(taddr + c * 32, r);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_preload);
+            epilogue_sync();                                     // every thread has read the partials
+            if (etid == 0)
+                for (int c = cta + 1; c <= last_c; ++c) flag_set(g.ws_flags + c, 0);
+            return true;
+        };
+        bool alive = true;
+        if (fin_idx == 0) alive = preload();                     // nothing to overlap with: do it first
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int t = blockIdx.x; t < n_work; t += gridDim.x) {
-            const Work w = get_work(g, t);
-            if (w.nk == 0) {
-                zero_tile(g, vec_ok, etid, w.a_row, w.b_row0);
-                if (w.b_row1 >= 0) zero_tile(g, vec_ok, etid, w.a_row, w.b_row1);
-                continue;
-            }
-            if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE)) break;
+        Seg w;
+        float* my_slot = g.split ? g.ws_slots + size_t(cta) * WS_SLOT_FLOATS : nullptr;
+        for (int seg = 0; alive && it.next(g, w); ++seg) {
+            const bool partial = w.i0 > 0;                       // goes to this CTA's workspace slot
+            const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
+            if (!epilogue_all(ok)) break;                        // uniform decision of the 128 epilogue threads
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
             const int row = w.a_row + etid;
             const int nchunks = w.b_row1 >= 0 ? 8 : 4;
+            const bool transposed = !partial && vec_t_ok && w.a_row + 128 <= g.MM;
             for (int c = 0; c < nchunks; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32, r);
                 tmem_ld_wait();
                 const int col = c < 4 ? w.b_row0 + c * 32 : w.b_row1 + (c - 4) * 32;
-                store_chunk(g, vec_ok, row, col, r);
+                if (partial) {
+                    float* dst = my_slot + size_t(c * 32) * BM + etid;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) __stcg(dst + j * BM, __uint_as_float(r[j]));
+                } else if (transposed) {
+                    store_chunk_transposed(g, xpose + (c & 1) * (XPOSE_BYTES / 2), etid, w.a_row, col, r);
+                } else {
+                    store_chunk(g, vec_ok, row, col, r);
+                }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            if (partial) {
+                __threadfence();                                 // partial tile visible before the flag
+                epilogue_sync();
+                if (etid == 0) flag_set(g.ws_flags + cta, 1);
+            }
+            // as late as possible: the accumulator just drained (or the still unused second one) is the finisher's
+            if (fin_idx == seg + 2 || (fin_idx == 1 && seg == 0)) alive = preload();
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
+#ifdef SD_TIMING
+        if (etid == 0) { SD_STAMP(3); sd_timing[blockIdx.x][7] = clock64(); }
+#endif
         __syncwarp();
     }
 
@@ -365,6 +645,35 @@ static int make_operand_map(CUtensorMap* out, bool* mn_major, const char* name, 
     if (outer > 1 && (ld < inner || (ld & 7)))
         return fail(SD_ERR_LAYOUT, "%s leading stride (%lld) must be >= %lld and a multiple of 8 elements", name,
                     (long long)ld, (long long)inner);
+    // Bind the device's primary context to this thread before the first driver-API call: a thread that has
+    // made no runtime call yet (e.g. an autograd worker) has no current context and cuTensorMapEncodeTiled
+    // would fail with CUDA_ERROR_INVALID_CONTEXT.  Done once per thread and device.
+    int dev = 0;
+    SD_CUDA_TRY(cudaGetDevice(&dev));
+    static thread_local int bound_device = -1;
+    if (bound_device != dev) {
+        SD_CUDA_TRY(cudaSetDevice(dev));
+        bound_device = dev;
+    }
+    // Small per-thread cache: training loops present the same few operands over and over.
+    struct MapKey {
+        const void* ptr; int64_t ld; int rows, kk, dtype, dev; bool k_major;
+        bool operator==(const MapKey& o) const {
+            return ptr == o.ptr && ld == o.ld && rows == o.rows && kk == o.kk && dtype == o.dtype && dev == o.dev &&
+                   k_major == o.k_major;
+        }
+    };
+    constexpr int kCache = 32;
+    static thread_local MapKey keys[kCache];
+    static thread_local CUtensorMap maps[kCache];
+    static thread_local int used = 0, next_slot = 0;
+    const MapKey key{ptr, ld, rows, kk, dtype, dev, k_major};
+    for (int i = 0; i < used; ++i)
+        if (keys[i] == key) {
+            *out = maps[i];
+            *mn_major = !k_major;
+            return SD_OK;
+        }
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable in this driver");
     cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
@@ -375,6 +684,9 @@ static int make_operand_map(CUtensorMap* out, bool* mn_major, const char* name, 
                      const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", name, int(r));
+    const int slot = used < kCache ? used++ : (next_slot = (next_slot + 1) % kCache);
+    keys[slot] = key;
+    maps[slot] = *out;
     *mn_major = !k_major;
     return SD_OK;
 }
@@ -418,7 +730,7 @@ static PlanView view_plan(const void* plan, int R, int C) {
 
 static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
                     void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
-                    float scale, int dtype, int* status, void* stream) {
+                    float scale, int dtype, void* workspace, int* status, void* stream) {
     if (M <= 0 || N <= 0 || K <= 0) return fail(SD_ERR_INVALID_ARG, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
     if (dtype != SD_F16 && dtype != SD_BF16) return fail(SD_ERR_INVALID_ARG, "dtype must be SD_F16 or SD_BF16");
     if (!C) return fail(SD_ERR_INVALID_ARG, "C is null");
@@ -426,13 +738,6 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     if (mode != MODE_DENSE && !plan) return fail(SD_ERR_INVALID_ARG, "plan is null");
     if (mode == MODE_DSD && plan_side != SD_PLAN_ROWS && plan_side != SD_PLAN_COLS)
         return fail(SD_ERR_INVALID_ARG, "plan_side must be SD_PLAN_ROWS or SD_PLAN_COLS");
-
-    // Bind the device's primary context to this thread before the first driver-API call: a thread that
-    // has made no runtime call yet (e.g. an autograd worker) has no current context and
-    // cuTensorMapEncodeTiled would fail with CUDA_ERROR_INVALID_CONTEXT.
-    int dev = 0;
-    SD_CUDA_TRY(cudaGetDevice(&dev));
-    SD_CUDA_TRY(cudaSetDevice(dev));
 
     CUtensorMap ta, tb;
     bool a_mn = false, b_mn = false;
@@ -471,9 +776,20 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         g.items = v.sdd_items; g.n_items = v.header + H_SDD_ITEMS;
         g.zero_pairs = v.drop_pairs; g.n_zero = v.header + H_NDROP;
     }
-    if (mode != MODE_SDD) {
-        const long long tiles = (long long)g.n_row_blocks * g.n_col_tiles;
-        if (tiles < grid) grid = int(tiles);
+    // Schedule: with fewer output tiles than SMs, whole tiles would leave SMs idle, so the K-tile stream is
+    // cut into equal shares instead (needs the workspace).  Otherwise whole tiles, heaviest first.
+    const long long tiles_upper = mode == MODE_SDD ? (long long)g.n_row_blocks * ((((N + 127) / 128) + 1) / 2)
+                                                   : (long long)g.n_row_blocks * g.n_col_tiles;
+    const long long units_upper = tiles_upper * ((K + 127) / 128);
+    if (workspace && tiles_upper < grid && units_upper > tiles_upper) {
+        if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(SD_ERR_LAYOUT, "workspace must be 16-byte aligned");
+        if (grid > WS_MAX_CTAS) grid = WS_MAX_CTAS;
+        if (units_upper < grid) grid = int(units_upper);
+        g.split = 1;
+        g.ws_flags = static_cast<int*>(workspace);
+        g.ws_slots = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + WS_FLAG_BYTES);
+    } else if (tiles_upper < grid) {
+        grid = int(tiles_upper);
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!a_mn && !b_mn) return launch_variant<false, false>(ta, tb, g, grid, st);
@@ -487,24 +803,46 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
 extern "C" {
 
 int sd_gemm(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
-            int64_t c_rs, int64_t c_cs, int M, int N, int K, float scale, int dtype, int* status, void* stream) {
+            int64_t c_rs, int64_t c_cs, int M, int N, int K, float scale, int dtype, void* workspace, int* status,
+            void* stream) {
     return sd::run_gemm(sd::MODE_DENSE, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, nullptr, 0, scale, dtype,
-                        status, stream);
+                        workspace, status, stream);
 }
 
 int sd_gemm_dsd(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
                 int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side, float scale,
-                int dtype, int* status, void* stream) {
+                int dtype, void* workspace, int* status, void* stream) {
     return sd::run_gemm(sd::MODE_DSD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, plan_side, scale,
-                        dtype, status, stream);
+                        dtype, workspace, status, stream);
 }
 
 int sd_gemm_sdd(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
                 int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, float scale, int dtype,
-                int* status, void* stream) {
+                void* workspace, int* status, void* stream) {
     return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
-                        status, stream);
+                        workspace, status, stream);
 }
+
+size_t sd_workspace_bytes(void) {
+    int sms = 0;
+    if (sd::sm_count_current_device(&sms) != SD_OK) return 0;
+    if (sms > sd::WS_MAX_CTAS) sms = sd::WS_MAX_CTAS;
+    return sd::WS_FLAG_BYTES + size_t(sms) * sd::WS_SLOT_BYTES;
+}
+
+int sd_workspace_init(void* workspace, void* stream) {
+    if (!workspace) return sd::fail(SD_ERR_INVALID_ARG, "workspace is null");
+    SD_CUDA_TRY(cudaMemsetAsync(workspace, 0, sd::WS_FLAG_BYTES, static_cast<cudaStream_t>(stream)));
+    return SD_OK;
+}
+
+#ifdef SD_TIMING
+int sd_debug_timing(unsigned long long* host_out /* [1024][8] */) {
+    SD_CUDA_TRY(cudaDeviceSynchronize());
+    SD_CUDA_TRY(cudaMemcpyFromSymbol(host_out, sd::sd_timing, sizeof(unsigned long long) * 1024 * 8));
+    return SD_OK;
+}
+#endif
 
 int sd_check_status(const int* status, void* stream) {
     if (!status) return sd::fail(SD_ERR_INVALID_ARG, "status is null");

@@ -21,7 +21,8 @@ SD_PLAN_ROWS, SD_PLAN_COLS = 0, 1
 #: every symbol include/sparsedrop.h declares
 EXPORTS = (
     "sd_version", "sd_last_error", "sd_plan_bytes", "sd_plan_offsets", "sd_plan_from_seed",
-    "sd_plan_from_mask", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd", "sd_check_status",
+    "sd_plan_from_mask", "sd_workspace_bytes", "sd_workspace_init", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd",
+    "sd_check_status",
 )
 
 
@@ -55,11 +56,15 @@ def lib() -> C.CDLL:
     L.sd_plan_from_mask.argtypes = [vp, i32, i32, i32, vp, i64, i64, vp]
     mat = [vp, i64, i64]
     L.sd_gemm.restype = i32
-    L.sd_gemm.argtypes = mat * 3 + [i32, i32, i32, f32, i32, vp, vp]
+    L.sd_gemm.argtypes = mat * 3 + [i32, i32, i32, f32, i32, vp, vp, vp]
     L.sd_gemm_dsd.restype = i32
-    L.sd_gemm_dsd.argtypes = mat * 3 + [i32, i32, i32, vp, i32, f32, i32, vp, vp]
+    L.sd_gemm_dsd.argtypes = mat * 3 + [i32, i32, i32, vp, i32, f32, i32, vp, vp, vp]
     L.sd_gemm_sdd.restype = i32
-    L.sd_gemm_sdd.argtypes = mat * 3 + [i32, i32, i32, vp, f32, i32, vp, vp]
+    L.sd_gemm_sdd.argtypes = mat * 3 + [i32, i32, i32, vp, f32, i32, vp, vp, vp]
+    L.sd_workspace_bytes.restype = C.c_size_t
+    L.sd_workspace_bytes.argtypes = []
+    L.sd_workspace_init.restype = i32
+    L.sd_workspace_init.argtypes = [vp, vp]
     L.sd_check_status.restype = i32
     L.sd_check_status.argtypes = [vp, vp]
     return L

@@ -117,6 +117,49 @@ class BlockPlan:
     def tile_mask(self): return self.buf[self.layout.mask:self.layout.mask + self.R * self.C].view(self.R, self.C)
 
 
+_workspaces: dict = {}
+
+
+def workspace(device: torch.device) -> torch.Tensor:
+    """Scratch for the equal-share schedule of the GEMM kernel, one per (device, current stream).
+
+    Launches that can overlap on the GPU must not share a workspace, hence the stream in the key.
+    """
+    stream = _lib.stream_ptr(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        with torch.cuda.device(device):
+            ws = torch.empty(_lib.lib().sd_workspace_bytes(), dtype=torch.uint8, device=device)
+            _lib.check(_lib.lib().sd_workspace_init(ws.data_ptr(), stream))
+        _workspaces[key] = ws
+    return ws
+
+
+def _ws_ptr(ws, device: torch.device):
+    if ws is None:
+        return None
+    if isinstance(ws, str):          # "auto"
+        return workspace(device).data_ptr()
+    return ws.data_ptr()
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` only when ``dev`` is not already current (the common case costs nothing)."""
+
+    def __init__(self, device: torch.device):
+        idx = device.index
+        self.guard = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+
+
 def _mat(x: torch.Tensor):
     return (x.data_ptr(), x.stride(0), x.stride(1))
 
@@ -141,18 +184,21 @@ def _check_pair(A: torch.Tensor, B: torch.Tensor) -> int:
     return _lib.dtype_code(A.dtype)
 
 
-def dense(A: torch.Tensor, B: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``scale * A @ B.T`` on the tcgen05 kernel with every tile kept."""
+def dense(A: torch.Tensor, B: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None,
+          ws="auto") -> torch.Tensor:
+    """``scale * A @ B.T`` on the tcgen05 kernel with every tile kept.
+
+    ``ws``: "auto" (cached per device and stream), a uint8 CUDA tensor, or None (whole-tile shares)."""
     dt = _check_pair(A, B)
     Cm = _out(A, B, out)
-    with torch.cuda.device(A.device):
+    with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm(*_mat(A), *_mat(B), *_mat(Cm), A.size(0), B.size(0), A.size(1),
-                                      float(scale), dt, None, _lib.stream_ptr(A.device)))
+                                      float(scale), dt, _ws_ptr(ws, A.device), None, _lib.stream_ptr(A.device)))
     return Cm
 
 
 def dsd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, side: int, scale: float,
-        out: torch.Tensor | None = None) -> torch.Tensor:
+        out: torch.Tensor | None = None, ws="auto") -> torch.Tensor:
     """``scale * (keep o A) @ B.T``; ``side`` says whether A's row blocks are the plan's rows or columns."""
     dt = _check_pair(A, B)
     M, K = A.shape
@@ -160,23 +206,24 @@ def dsd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, side: int, scale: flo
     if (plan.R, plan.C) != want:
         raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match operand A {tuple(A.shape)} (need {want})")
     Cm = _out(A, B, out)
-    with torch.cuda.device(A.device):
+    with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm_dsd(*_mat(A), *_mat(B), *_mat(Cm), M, B.size(0), K, plan.buf.data_ptr(),
-                                          side, float(scale), dt, None, _lib.stream_ptr(A.device)))
+                                          side, float(scale), dt, _ws_ptr(ws, A.device), None,
+                                          _lib.stream_ptr(A.device)))
     return Cm
 
 
 def sdd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float,
-        out: torch.Tensor | None = None) -> torch.Tensor:
+        out: torch.Tensor | None = None, ws="auto") -> torch.Tensor:
     """``scale * keep o (A @ B.T)``: kept output tiles computed, dropped tiles written as zeros."""
     dt = _check_pair(A, B)
     M, N = A.size(0), B.size(0)
     if (plan.R, plan.C) != (ceil(M / TILE), ceil(N / TILE)):
         raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the output {(M, N)}")
     Cm = _out(A, B, out)
-    with torch.cuda.device(A.device):
+    with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm_sdd(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),
-                                          float(scale), dt, None, _lib.stream_ptr(A.device)))
+                                          float(scale), dt, _ws_ptr(ws, A.device), None, _lib.stream_ptr(A.device)))
     return Cm
 
 

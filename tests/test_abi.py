@@ -52,16 +52,17 @@ def test_argument_validation_without_a_gpu(built_lib):
     assert built_lib.sd_plan_from_mask(buf, 4, 4, 1, None, 4, 1, None) == SD_ERR_INVALID_ARG
     # GEMM entry points reject bad sizes / dtypes / layouts before touching the device
     a = C.cast(buf, C.c_void_p)
-    assert built_lib.sd_gemm(a, 128, 1, a, 128, 1, a, 128, 1, 0, 128, 128, 1.0, 0, None, None) == SD_ERR_INVALID_ARG
-    assert built_lib.sd_gemm(a, 128, 1, a, 128, 1, a, 128, 1, 128, 128, 128, 1.0, 7, None, None) == SD_ERR_INVALID_ARG
-    assert built_lib.sd_gemm(a, 128, 1, a, 128, 1, a, 128, 2, 128, 128, 128, 1.0, 0, None, None) == SD_ERR_LAYOUT
-    assert built_lib.sd_gemm(a, 128, 2, a, 128, 1, a, 128, 1, 128, 128, 128, 1.0, 0, None, None) == SD_ERR_LAYOUT
+    assert built_lib.sd_gemm(a, 128, 1, a, 128, 1, a, 128, 1, 0, 128, 128, 1.0, 0, None, None, None) == SD_ERR_INVALID_ARG
+    assert built_lib.sd_gemm(a, 128, 1, a, 128, 1, a, 128, 1, 128, 128, 128, 1.0, 7, None, None, None) == SD_ERR_INVALID_ARG
+    assert built_lib.sd_gemm(a, 128, 1, a, 128, 1, a, 128, 2, 128, 128, 128, 1.0, 0, None, None, None) == SD_ERR_LAYOUT
+    assert built_lib.sd_gemm(a, 128, 2, a, 128, 1, a, 128, 1, 128, 128, 128, 1.0, 0, None, None, None) == SD_ERR_LAYOUT
     assert b"row or column major" in built_lib.sd_last_error()
-    assert built_lib.sd_gemm(a, 100, 1, a, 128, 1, a, 128, 1, 128, 128, 128, 1.0, 0, None, None) == SD_ERR_LAYOUT
-    assert built_lib.sd_gemm_dsd(a, 128, 1, a, 128, 1, a, 128, 1, 128, 128, 128, None, 0, 1.0, 0, None, None) \
+    assert built_lib.sd_gemm(a, 100, 1, a, 128, 1, a, 128, 1, 128, 128, 128, 1.0, 0, None, None, None) == SD_ERR_LAYOUT
+    assert built_lib.sd_gemm_dsd(a, 128, 1, a, 128, 1, a, 128, 1, 128, 128, 128, None, 0, 1.0, 0, None, None, None) \
         == SD_ERR_INVALID_ARG
-    assert built_lib.sd_gemm_dsd(a, 128, 1, a, 128, 1, a, 128, 1, 128, 128, 128, a, 5, 1.0, 0, None, None) \
+    assert built_lib.sd_gemm_dsd(a, 128, 1, a, 128, 1, a, 128, 1, 128, 128, 128, a, 5, 1.0, 0, None, None, None) \
         == SD_ERR_INVALID_ARG
-    assert built_lib.sd_gemm_sdd(a, 128, 1, a, 128, 1, None, 128, 1, 128, 128, 128, a, 1.0, 0, None, None) \
+    assert built_lib.sd_gemm_sdd(a, 128, 1, a, 128, 1, None, 128, 1, 128, 128, 128, a, 1.0, 0, None, None, None) \
         == SD_ERR_INVALID_ARG
     assert built_lib.sd_check_status(None, None) == SD_ERR_INVALID_ARG
+    assert built_lib.sd_workspace_init(None, None) == SD_ERR_INVALID_ARG

@@ -38,6 +38,7 @@ ps = [0.0, 0.1, 0.2, 0.5, 0.9, 0.99, 0.999]
 
 @pytest.mark.parametrize("mnk,p", list(product(mnks, ps)))
 def test_blockwise_dropout_matmul_reference_grid(built_lib, mnk, p):
+    """Through the reference-shaped GEMM facade (equal-share schedule with the cached workspace)."""
     from flash_dropout.cuda.binding_gemm import GEMM
     M, N, K = mnk
     x, w, dy = _inputs(M, N, K, seed=0)
@@ -136,13 +137,19 @@ def test_block_size_larger_than_tile(built_lib):
 def test_full_size_properties_4096(built_lib):
     """BASELINE config 2 (4096^3, p = 0.5): size-independent properties instead of a CPU oracle pass.
 
+    With whole-tile shares (no workspace) every output element is one sequential fp32 accumulation over its
+    kept K tiles, so:
     * skipping a dropped tile == multiplying by an explicitly zeroed tile, bit for bit (zeros add nothing
       to an fp32 accumulator), for all three products;
     * p = 0 plan == the dense kernel, bit for bit;
     * dropped tiles of dx are exact zeros; linearity in the scale.
     """
     from flash_dropout import _lib
-    from flash_dropout.cuda.binding_gemm import BlockPlan, dense, dsd, sdd
+    from flash_dropout.cuda import binding_gemm as bg
+    from flash_dropout.cuda.binding_gemm import BlockPlan
+    dense = lambda *a, **k: bg.dense(*a, ws=None, **k)
+    dsd = lambda *a, **k: bg.dsd(*a, ws=None, **k)
+    sdd = lambda *a, **k: bg.sdd(*a, ws=None, **k)
     M = N = K = 4096
     p = 0.5
     x, w, dy = (t.to(DEV) for t in _inputs(M, N, K, seed=9))
@@ -164,6 +171,51 @@ def test_full_size_properties_4096(built_lib):
     # against cuBLAS on the masked input (fp32 accumulate both sides)
     torch.testing.assert_close(y.float(), s * (xz.float() @ w.float().T), rtol=RTOL, atol=ATOL)
     torch.testing.assert_close(dsd(x, w, plan, _lib.SD_PLAN_ROWS, 2 * s).float(), 2 * y.float(), rtol=2e-3, atol=2e-3)
+
+
+def test_equal_share_schedule_4096(built_lib):
+    """Same workload with the workspace: shares are cut inside tiles and partial accumulators are added up in
+    CTA order.  The regrouped fp32 sums may differ from the sequential ones by an fp16 rounding step, never
+    more; results are reproducible run to run; dropped dx tiles stay exact zeros."""
+    from flash_dropout import _lib
+    from flash_dropout.cuda.binding_gemm import BlockPlan, dense, dsd, sdd
+    M = N = K = 4096
+    x, w, dy = (t.to(DEV) for t in _inputs(M, N, K, seed=9))
+    for p in (0.0, 0.5, 0.9):
+        plan = BlockPlan.from_seed(M, K, 128, p, 0, 0, DEV)
+        keep = (~plan.mask).repeat_interleave(128, 0).repeat_interleave(128, 1)
+        s = 1 / (1 - p)
+        dw_a, dw_b = (torch.empty(N, K, device=DEV, dtype=torch.float16) for _ in range(2))
+        pairs = [
+            (dsd(x, w, plan, _lib.SD_PLAN_ROWS, s), dsd(x, w, plan, _lib.SD_PLAN_ROWS, s, ws=None)),
+            (sdd(dy, w.T, plan, s), sdd(dy, w.T, plan, s, ws=None)),
+            (dsd(x.T, dy.T, plan, _lib.SD_PLAN_COLS, s, out=dw_a.T).T, dsd(x.T, dy.T, plan, _lib.SD_PLAN_COLS, s, out=dw_b.T, ws=None).T),
+        ]
+        for split, whole in pairs:
+            torch.testing.assert_close(split.float(), whole.float(), rtol=2e-3, atol=2e-3)
+        assert (pairs[1][0][~keep] == 0).all()
+        assert torch.equal(pairs[0][0], dsd(x, w, plan, _lib.SD_PLAN_ROWS, s))          # deterministic
+        assert torch.equal(pairs[1][0], sdd(dy, w.T, plan, s))
+    torch.testing.assert_close(dense(x, w).float(), x.float() @ w.float().T, rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 8192), (128, 128, 16384), (256, 512, 4096), (640, 384, 2048)])
+def test_many_ctas_per_tile(built_lib, M, N, K):
+    """Fewer output tiles than SMs: one tile is shared by many CTAs and its owner adds up many partials."""
+    from flash_dropout import _lib
+    from flash_dropout.cuda.binding_gemm import BlockPlan, dense, dsd, sdd
+    x, w, dy = _inputs(M, N, K, seed=11)
+    A, B, dC = x.to(DEV), w.to(DEV), dy.to(DEV)
+    _close(dense(A, B), x.float() @ w.float().T, "dense")
+    p = 0.5
+    mask_np = pm.block_mask(M, K, 128, p, seed=12)
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, 128, p, w, dy)
+    plan = BlockPlan.from_mask(torch.from_numpy(mask_np).to(DEV), M, K, 128)
+    _close(dsd(A, B, plan, _lib.SD_PLAN_ROWS, 2.0), y_ref, "y")
+    _close(sdd(dC, B.T, plan, 2.0), dx_ref, "dx")
+    _close(dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, 2.0).T, dw_ref, "dw")
+    for _ in range(3):      # flags are left cleared: back-to-back launches reuse the workspace
+        _close(dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, 2.0).T, dw_ref, "dw again")
 
 
 def test_errors_mirror_the_reference(built_lib):
