@@ -146,6 +146,33 @@ int sd_gemm_dsd(const void* A, int64_t a_rs, int64_t a_cs,
                 int M, int N, int K, const void* plan, int plan_side,
                 float scale, int dtype, void* workspace, int* status, void* stream);
 
+/*
+ * DSD without a caller workspace and without any allocation.  No counterpart in the reference.
+ *
+ * For callers that cannot hand this library device memory of their own: a host process whose device
+ * memory all belongs to its own pool or fixed budget, a latency-bound loop that must not take the
+ * device-wide synchronisation an allocation implies, or a plain C caller with no allocator at hand.
+ * sd_gemm_dsd() needs such a caller to allocate the workspace before it can spread a small product over
+ * all SMs; this entry point computes the same product with scratch that is built into the library:
+ * a file-scope device array of 8 196 KiB (4 KiB of flags + 64 partial tiles of 128 KiB) that every GPU
+ * which loads the library holds until the process exits.  It calls no cudaMalloc / cudaFree and no
+ * allocating library routine; inputs, the plan and the output are still the caller's.
+ *
+ * Limit: at most 64 output tiles of 128 x 256, i.e. ceil(M/128) * ceil(N/256) <= 64 (a 1024 x 2048
+ * result, say); the grid is at most 64 CTAs.  Larger products return SD_ERR_TOO_LARGE — they have at
+ * least one tile per CTA and need no scratch: use sd_gemm_dsd() with workspace = NULL.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current) and keeps it; make that first call outside any stream capture.  Every call on a
+ * device shares the one array: its flags are cleared on the stream at the start of each call, and two
+ * calls that can overlap on the GPU (different streams, different threads) race on it — serialise them.
+ */
+int sd_gemm_dsd_static_scratch(const void* A, int64_t a_rs, int64_t a_cs,
+                               const void* B, int64_t b_rs, int64_t b_cs,
+                               void* C, int64_t c_rs, int64_t c_cs,
+                               int M, int N, int K, const void* plan, int plan_side,
+                               float scale, int dtype, int* status, void* stream);
+
 /* SDD: C = scale * keep o (A . B^T): only kept 128x128 output tiles are computed, dropped tiles
  * are written as zeros.  The plan is ceil(M/128) x ceil(N/128).  Replaces GEMM.gemm_sdd
  * (flash_dropout/cuda/binding_gemm.py:39-47, flash_dropout/cuda/src/matmul_sdd.cuh:69-105). */

@@ -42,6 +42,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "sd_common.h"
 #include "sd_plan.cuh"
 #include "sd_ptx.cuh"
@@ -730,7 +732,7 @@ static PlanView view_plan(const void* plan, int R, int C) {
 
 static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
                     void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
-                    float scale, int dtype, void* workspace, int* status, void* stream) {
+                    float scale, int dtype, void* workspace, int* status, void* stream, int max_ctas = 0) {
     if (M <= 0 || N <= 0 || K <= 0) return fail(SD_ERR_INVALID_ARG, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
     if (dtype != SD_F16 && dtype != SD_BF16) return fail(SD_ERR_INVALID_ARG, "dtype must be SD_F16 or SD_BF16");
     if (!C) return fail(SD_ERR_INVALID_ARG, "C is null");
@@ -781,6 +783,14 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     const long long tiles_upper = mode == MODE_SDD ? (long long)g.n_row_blocks * ((((N + 127) / 128) + 1) / 2)
                                                    : (long long)g.n_row_blocks * g.n_col_tiles;
     const long long units_upper = tiles_upper * ((K + 127) / 128);
+    if (max_ctas > 0) {
+        if (tiles_upper > max_ctas)
+            return fail(SD_ERR_TOO_LARGE,
+                        "%lld output tiles of 128x256 exceed the %d the built-in scratch serves; launches this large "
+                        "need no scratch: call sd_gemm_dsd with workspace = NULL",
+                        tiles_upper, max_ctas);
+        if (grid > max_ctas) grid = max_ctas;
+    }
     if (workspace && tiles_upper < grid && units_upper > tiles_upper) {
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(SD_ERR_LAYOUT, "workspace must be 16-byte aligned");
         if (grid > WS_MAX_CTAS) grid = WS_MAX_CTAS;
@@ -796,6 +806,33 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     if (!a_mn && b_mn) return launch_variant<false, true>(ta, tb, g, grid, st);
     if (a_mn && !b_mn) return launch_variant<true, false>(ta, tb, g, grid, st);
     return launch_variant<true, true>(ta, tb, g, grid, st);
+}
+
+// ------------------------------------------------------------------ built-in scratch
+// Scratch of sd_gemm_dsd_static_scratch(): the same layout as a caller's workspace (flags, then one fp32
+// partial tile per CTA) for at most kStaticScratchSlots CTAs: 4 KiB + 64 x 128 KiB = 8 196 KiB of device
+// memory that every GPU which loads this library holds until the process exits.
+constexpr int kStaticScratchSlots = 64;
+static __device__ __align__(256) unsigned char sd_static_scratch[WS_FLAG_BYTES + kStaticScratchSlots * WS_SLOT_BYTES];
+
+// Device address of the array on the current device.  In host code the array's name is only a stand-in for
+// the symbol, not a device pointer: the address has to be asked for, once per device, with that device current.
+static int static_scratch_address(void** out) {
+    static std::mutex mu;
+    static void* cached[64] = {};
+    int dev = 0;
+    SD_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 64 && cached[dev]) {
+        *out = cached[dev];
+        return SD_OK;
+    }
+    void* p = nullptr;
+    SD_CUDA_TRY(cudaGetSymbolAddress(&p, sd_static_scratch));
+    if (!p) return fail(SD_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the built-in scratch");
+    if (dev < 64) cached[dev] = p;
+    *out = p;
+    return SD_OK;
 }
 
 }  // namespace sd
@@ -834,6 +871,19 @@ int sd_workspace_init(void* workspace, void* stream) {
     if (!workspace) return sd::fail(SD_ERR_INVALID_ARG, "workspace is null");
     SD_CUDA_TRY(cudaMemsetAsync(workspace, 0, sd::WS_FLAG_BYTES, static_cast<cudaStream_t>(stream)));
     return SD_OK;
+}
+
+int sd_gemm_dsd_static_scratch(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
+                               void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
+                               float scale, int dtype, int* status, void* stream) {
+    void* scratch = nullptr;
+    int rc = sd::static_scratch_address(&scratch);
+    if (rc) return rc;
+    // The array keeps whatever the previous call left.  Partial tiles are always written before they are
+    // read, but the flags must start at zero, also after a launch that gave up on a wait.
+    SD_CUDA_TRY(cudaMemsetAsync(scratch, 0, sd::WS_FLAG_BYTES, static_cast<cudaStream_t>(stream)));
+    return sd::run_gemm(sd::MODE_DSD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, plan_side, scale,
+                        dtype, scratch, status, stream, sd::kStaticScratchSlots);
 }
 
 #ifdef SD_TIMING
