@@ -335,12 +335,113 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------ training steps
+def run_train(args) -> None:
+    """BASELINE configs[3] (MLP) / configs[4] (char-GPT): one optimizer step per "step", batch sharded over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from flash_dropout import random as sd_random
+    from flash_dropout.train import GPT, BasicNet, FlatGradDataParallel, train_step
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the SparseDrop kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(SEED)
+    variant = args.variant
+    if args.workload == "mlp":
+        per_gpu, p = 512, 0.5
+        model = BasicNet(784, 2, 1024, 10, dict(p=p, variant=variant, block_size=(128, 128))).to(dev)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True)
+        g = torch.Generator().manual_seed(SEED + 1 + rank)
+        host_x = torch.rand(per_gpu, 28, 28, generator=g).pin_memory()
+        host_y = torch.randint(0, 10, (per_gpu,), generator=g).pin_memory()
+        name = "BASELINE configs[3]: MLP 784-1024-1024-1024-10, bf16 autocast, batch 512/GPU, p=0.5, AdamW lr 1e-3"
+        loss_of = lambda m, x, y: torch.nn.functional.cross_entropy(m(x).float(), y)
+    else:
+        per_gpu, p = 64, 0.2
+        model = GPT(65, 256, 6, 6, 384, dict(p=p, variant=variant, block_size=(128, 128))).to(dev)
+        opt = model.configure_optimizers(weight_decay=0.1, lr=3e-4)
+        g = torch.Generator().manual_seed(SEED + 1 + rank)
+        host_x = torch.randint(0, 65, (per_gpu, 256), generator=g).pin_memory()
+        host_y = host_x
+        name = "BASELINE configs[4]: char-GPT 6 layers d=384 6 heads ctx 256 vocab 65, bf16 autocast, batch 64/GPU, p=0.2, AdamW"
+        loss_of = lambda m, x, y: m(x)[1]
+    dp = FlatGradDataParallel(model)
+    sd_random.manual_seed(SEED, subsequence=rank)
+    x_dev, y_dev = host_x.to(dev), host_y.to(dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one(resident: bool):
+        if resident:
+            x, y = x_dev, y_dev
+        else:
+            x, y = host_x.to(dev, non_blocking=True), host_y.to(dev, non_blocking=True)
+        loss = train_step(model, dp, opt, lambda m: loss_of(m, x, y), autocast_dtype=torch.bfloat16)
+        return loss if resident else loss.item()
+
+    results = {}
+    for label, resident in (("value", True), ("e2e", False)):
+        for _ in range(warmup):
+            one(resident)
+        barrier()
+        sampler = ClockSampler(local) if label == "value" else None
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            last = one(resident)
+        e1.record()
+        barrier()
+        t1 = time.perf_counter()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        results[label] = ms.item()
+        if sampler:
+            clocks = sampler.stop(t0, t1)
+    if rank == 0:
+        n_mm = sum(1 for m in model.modules() if m.__class__.__name__ == "DropoutMM")
+        line = {
+            "metric": "train-step samples/s", "value": per_gpu * world * steps / (results["value"] * 1e-3),
+            "unit": "samples/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": results["value"] / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 autocast (fp32 accumulate, fp32 master weights)", "data": "synthetic",
+            "config": {"workload": name, "variant": variant, "parallelism": f"dp{world}",
+                       "step": "zero_grad + fwd + bwd (bucketed NCCL all-reduce overlapped) + optimizer"},
+            "e2e": {"value": per_gpu * world * steps / (results["e2e"] * 1e-3), "unit": "samples/s",
+                    "h2d_bytes_per_step": host_x.numel() * host_x.element_size() + (0 if host_y is host_x else host_y.numel() * 8),
+                    "d2h_bytes_per_step": 4, "ms_per_step": results["e2e"] / steps},
+            "gpu_launches": (4 * n_mm * steps) if "blockwise[cuda]" in variant else 0, "clocks": clocks,
+            "final_loss": float(last),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=("gemm", "mlp", "gpt"), default="gemm",
+                    help="gemm: the headline 4096^3 SparseDrop linear (default); mlp / gpt: one training step")
+    ap.add_argument("--variant", default="blockwise[cuda]", help="DropoutMM variant for the training workloads")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the p=0 comparison and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
@@ -353,9 +454,13 @@ def main() -> None:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__),
                "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup)]
+        cmd += ["--workload", args.workload, "--variant", args.variant]
         if args.no_extras:
             cmd.append("--no-extras")
         raise SystemExit(subprocess.call(cmd))
+    if args.workload != "gemm":
+        run_train(args)
+        return
     run_ours(args)
 
 

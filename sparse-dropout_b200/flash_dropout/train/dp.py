@@ -1,0 +1,124 @@
+"""Batch-sharded data parallelism for the SparseDrop training steps.
+
+The reference is single-GPU (no torch.distributed call site anywhere in it); this is the part of the
+1/2/4/8-GPU training-step workload that is new.  One process per GPU.  Every rank runs the identical hot path
+on its own batch shard with its own mask stream (Philox subsequence = rank), and the only exchange is the
+all-reduce (mean) of the gradients:
+
+  * all gradients live in ONE flat buffer of the parameters' dtype (fp32 master weights); each parameter's ``.grad`` is a view into it, so there is no
+    pack / unpack copy around the collective;
+  * the buffer is cut into buckets in reverse parameter order; a bucket's all-reduce is launched
+    asynchronously (NCCL's own stream) the moment autograd has accumulated its last gradient, so communication
+    overlaps the rest of backward;
+  * ``finish()`` waits for the outstanding buckets before the optimizer step.
+Works with any backend torch.distributed offers (NCCL on GPUs, gloo for the CPU tests).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from flash_dropout import random as sd_random
+
+
+class FlatGradDataParallel:
+    def __init__(self, module: torch.nn.Module, process_group=None, bucket_bytes: int = 16 << 20,
+                 broadcast_from: int | None = 0):
+        self.module = module
+        self.group = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.params = [p for p in module.parameters() if p.requires_grad]
+        dev = self.params[0].device
+        total = sum(p.numel() for p in self.params)
+        dtype = self.params[0].dtype
+        if any(p.dtype != dtype for p in self.params):
+            raise ValueError("all trainable parameters must share one dtype (the master-weight dtype)")
+        self.flat_grad = torch.zeros(total, dtype=dtype, device=dev)
+        self._esize = self.flat_grad.element_size()
+        # parameters are laid out in REVERSE registration order: backward produces gradients roughly last
+        # layer first, so bucket 0 (the front of the buffer) completes first
+        off = 0
+        self._slices = {}
+        for p in reversed(self.params):
+            n = p.numel()
+            p.grad = self.flat_grad[off:off + n].view_as(p)
+            self._slices[p] = (off, off + n)
+            off += n
+        # buckets = contiguous ranges of the flat buffer
+        self.buckets: list[tuple[int, int]] = []
+        self._bucket_of = {}
+        start, cur = 0, 0
+        for p in reversed(self.params):
+            lo, hi = self._slices[p]
+            self._bucket_of[p] = len(self.buckets)
+            cur = hi
+            if (cur - start) * self._esize >= bucket_bytes:
+                self.buckets.append((start, cur))
+                start = cur
+        if cur > start:
+            self.buckets.append((start, cur))
+        self._bucket_size = [0] * len(self.buckets)
+        for p in self.params:
+            self._bucket_size[self._bucket_of[p]] += 1
+        self._pending = list(self._bucket_size)
+        self._handles = []
+        if self.world > 1:
+            if broadcast_from is not None:
+                for p in module.parameters():
+                    dist.broadcast(p.data, src=broadcast_from, group=self.group)
+                for b in module.buffers():
+                    dist.broadcast(b.data, src=broadcast_from, group=self.group)
+            for p in self.params:
+                p.register_post_accumulate_grad_hook(self._on_grad_ready)
+        sd_random.set_subsequence(self.rank)     # every rank draws its own masks from the shared seed
+
+    # ------------------------------------------------------------------
+    def _on_grad_ready(self, p: torch.Tensor) -> None:
+        b = self._bucket_of[p]
+        self._pending[b] -= 1
+        if self._pending[b] == 0:
+            lo, hi = self.buckets[b]
+            self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                                                 async_op=True))
+
+    def zero_grad(self) -> None:
+        self.flat_grad.zero_()
+        self._pending = list(self._bucket_size)
+        self._handles = []
+
+    def finish(self) -> None:
+        """Wait for the bucket all-reduces and turn the sums into means."""
+        if self.world == 1:
+            return
+        for b, left in enumerate(self._pending):       # parameters that received no gradient this step
+            if left > 0:
+                lo, hi = self.buckets[b]
+                self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                                                     async_op=True))
+                self._pending[b] = 0
+        for h in self._handles:
+            h.wait()
+        self._handles = []
+        self.flat_grad.div_(self.world)
+
+    def grads_are_views(self) -> bool:
+        """True while autograd kept accumulating in place into the flat buffer."""
+        base = self.flat_grad.data_ptr()
+        return all(p.grad is not None and p.grad.data_ptr() == base + self._esize * self._slices[p][0] for p in self.params)
+
+
+def train_step(model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torch.optim.Optimizer, loss_fn,
+               autocast_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """zero grads -> forward/backward (bucket all-reduces overlap backward) -> wait -> optimizer step."""
+    dp.zero_grad()
+    dev_type = dp.flat_grad.device.type
+    if autocast_dtype is not None:
+        with torch.autocast(dev_type, dtype=autocast_dtype):
+            loss = loss_fn(model)
+    else:
+        loss = loss_fn(model)
+    loss.backward()
+    dp.finish()
+    optimizer.step()
+    return loss.detach()

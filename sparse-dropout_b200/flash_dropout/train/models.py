@@ -1,0 +1,112 @@
+"""The two models the reference trains with DropoutMM, restated (architecture, parameter names and
+initialisation follow the reference so checkpoints stay interchangeable):
+
+  BasicNet — eval/mlp/model.py:8-40: in_proj, `num_layers` hidden DropoutMM layers, out_proj whose width is
+             padded to a multiple of 128 and sliced back, ReLU in between.
+  GPT      — eval/llm/model.py:8-173: nanoGPT-style decoder; q/k/v/out projections and both MLP linears are
+             DropoutMM, LayerNorm without bias, causal SDPA, untied lm_head, AdamW with decay on >=2-D params.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from flash_dropout.layers import DropoutMM
+
+
+def next_multiple(x: int, base: int) -> int:
+    return -(-x // base) * base
+
+
+class BasicNet(nn.Module):
+    def __init__(self, input_dim: int, num_layers: int, hidden_dim: int, output_dim: int, dropout: dict):
+        super().__init__()
+        assert num_layers >= 0
+        self.output_dim = output_dim
+        self.in_proj = DropoutMM(input_dim, hidden_dim, **dropout)
+        self.out_proj = DropoutMM(hidden_dim, next_multiple(output_dim, 128), **dropout)
+        self.layers = nn.ModuleList(DropoutMM(hidden_dim, hidden_dim, **dropout) for _ in range(num_layers))
+        self.act = nn.ReLU()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x = self.act(self.in_proj(x.flatten(1)))
+        for layer in self.layers:
+            x = self.act(layer(x))
+        return self.out_proj(x)[..., : self.output_dim]
+
+
+class CausalSelfAttention(nn.Module):
+    def __init__(self, n_embed: int, n_head: int, dropout: dict):
+        super().__init__()
+        assert n_embed % n_head == 0
+        self.n_head = n_head
+        self.q_proj = DropoutMM(n_embed, n_embed, **dropout)
+        self.k_proj = DropoutMM(n_embed, n_embed, **dropout)
+        self.v_proj = DropoutMM(n_embed, n_embed, **dropout)
+        self.out_proj = DropoutMM(n_embed, n_embed, **dropout)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        b, s, d = x.shape
+        heads = lambda t: t.view(b, s, self.n_head, d // self.n_head).transpose(1, 2)
+        y = F.scaled_dot_product_attention(heads(self.q_proj(x)), heads(self.k_proj(x)), heads(self.v_proj(x)),
+                                           is_causal=True)
+        return self.out_proj(y.transpose(1, 2).reshape(b, s, d))
+
+
+class MLP(nn.Module):
+    def __init__(self, n_embed: int, dropout: dict):
+        super().__init__()
+        self.c_fc = DropoutMM(n_embed, 4 * n_embed, **dropout)
+        self.gelu = nn.GELU()
+        self.c_proj = DropoutMM(4 * n_embed, n_embed, **dropout)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.c_proj(self.gelu(self.c_fc(x)))
+
+
+class Block(nn.Module):
+    def __init__(self, n_embed: int, n_head: int, dropout: dict):
+        super().__init__()
+        self.ln_1 = nn.LayerNorm(n_embed, bias=False)
+        self.attn = CausalSelfAttention(n_embed, n_head, dropout)
+        self.ln_2 = nn.LayerNorm(n_embed, bias=False)
+        self.mlp = MLP(n_embed, dropout)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x = x + self.attn(self.ln_1(x))
+        return x + self.mlp(self.ln_2(x))
+
+
+class GPT(nn.Module):
+    def __init__(self, vocab_size: int, context_length: int, n_layer: int, n_head: int, n_embed: int, dropout: dict):
+        super().__init__()
+        self.vocab_size, self.context_length = vocab_size, context_length
+        self.transformer = nn.ModuleDict(dict(
+            wte=nn.Embedding(vocab_size, n_embed),
+            wpe=nn.Embedding(context_length, n_embed),
+            h=nn.ModuleList(Block(n_embed, n_head, dropout) for _ in range(n_layer)),
+            ln_f=nn.LayerNorm(n_embed, bias=False),
+        ))
+        self.lm_head = nn.Linear(n_embed, vocab_size, bias=False)
+
+    def forward(self, idx: torch.Tensor, calc_loss: bool = True):
+        b, s = idx.shape
+        assert s <= self.context_length
+        pos = torch.arange(s, device=idx.device)
+        x = self.transformer.wte(idx) + self.transformer.wpe(pos)[None]
+        for block in self.transformer.h:
+            x = block(x)
+        logits = self.lm_head(self.transformer.ln_f(x))[:, :-1, :].contiguous()
+        loss = None
+        if calc_loss:   # next-token prediction
+            loss = F.cross_entropy(logits.view(-1, self.vocab_size).float(), idx[:, 1:].reshape(-1))
+        return logits, loss
+
+    def configure_optimizers(self, weight_decay: float, lr: float, fused: bool | None = None):
+        params = [p for p in self.parameters() if p.requires_grad]
+        groups = [{"params": [p for p in params if p.dim() >= 2], "weight_decay": weight_decay},
+                  {"params": [p for p in params if p.dim() < 2], "weight_decay": 0.0}]
+        if fused is None:
+            fused = all(p.is_cuda for p in params)
+        return torch.optim.AdamW(groups, lr=lr, fused=fused)

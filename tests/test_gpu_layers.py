@@ -98,3 +98,39 @@ def test_non_contiguous_grad_output(built_lib):
     y = F.cuda_blockwise_dropout_matmul(x, w, 128, 0.0)
     y.sum().backward()                                   # expanded (stride-0) upstream gradient
     torch.testing.assert_close(x.grad.float(), w.float().sum(0).expand(256, 256), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("kind", ["mlp", "gpt"])
+def test_training_step_consumers(built_lib, kind):
+    """The two models of the training-step workloads run a few optimizer steps on the SparseDrop kernels."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.train import GPT, BasicNet, FlatGradDataParallel, train_step
+    torch.manual_seed(0)
+    sd_random.manual_seed(3, subsequence=0)
+    drop = dict(p=0.5 if kind == "mlp" else 0.2, variant="blockwise[cuda]", block_size=(128, 128))
+    if kind == "mlp":
+        model = BasicNet(784, 2, 1024, 10, drop).to(DEV)
+        x, y = torch.rand(512, 28, 28, device=DEV), torch.randint(0, 10, (512,), device=DEV)
+        loss_fn = lambda m: torch.nn.functional.cross_entropy(m(x).float(), y)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True)
+    else:
+        model = GPT(65, 256, 2, 6, 384, drop).to(DEV)
+        idx = torch.randint(0, 65, (16, 256), device=DEV)
+        loss_fn = lambda m: m(idx)[1]
+        opt = model.configure_optimizers(0.1, 1e-3)
+    dp = FlatGradDataParallel(model)
+
+    def eval_loss():
+        model.eval()
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            v = loss_fn(model).item()
+        model.train()
+        return v
+
+    before = eval_loss()
+    losses = [train_step(model, dp, opt, loss_fn, autocast_dtype=torch.bfloat16).item() for _ in range(30)]
+    assert dp.grads_are_views()
+    assert all(torch.isfinite(torch.tensor(losses)))
+    assert eval_loss() < before                              # it learns the fixed batch
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+    sd_random.follow_torch_seed()
