@@ -182,6 +182,28 @@ int sd_gemm_sdd(const void* A, int64_t a_rs, int64_t a_cs,
                 int M, int N, int K, const void* plan,
                 float scale, int dtype, void* workspace, int* status, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Convolution stages.  The im2col matrix of flash_dropout/functional/im2col_conv2d.py:17-20
+ * (M = N*P*Q rows, K = C*R*S columns, k = c*R*S + r*S + s) is kept K-outer: colT[k][m], 16-bit,
+ * leading dimension ldm (>= M, multiple of 8, base 16-byte aligned), with k_gemm >= K rows
+ * (k_gemm = the K the GEMMs are called with, a multiple of 8; rows K..k_gemm-1 must be zero).
+ * colT.T is the MN-major A operand of sd_gemm_dsd; the plan is ceil(M/128) x ceil(k_gemm/128).
+ * x and dx are contiguous NCHW.  Blockwise dropout on a convolution has no counterpart in the
+ * reference (flash_dropout/layers/dropout_conv.py:86-99 is commented out); the dense im2col it
+ * replaces is F.unfold in im2col_conv2d.py:17.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Writes the kept 128x128 blocks of colT (all blocks if plan is NULL).  Dropped blocks are not touched. */
+int sd_im2col_kept(const void* x, int N, int C, int H, int W, int R, int S,
+                   int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                   void* colT, int64_t ldm, int k_gemm, const void* plan, void* stream);
+
+/* Adjoint: dx[n,c,h,w] = sum of the dcolT entries that x[n,c,h,w] fed, reading kept blocks only
+ * (all blocks if plan is NULL).  fp32 accumulation, output in `dtype`. */
+int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int H, int W, int R, int S,
+                   int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                   void* dx, const void* plan, int dtype, void* stream);
+
 /* Synchronises the stream, reads *status and returns SD_OK or SD_ERR_TIMEOUT. */
 int sd_check_status(const int* status, void* stream);
 

@@ -1,0 +1,198 @@
+// im2col / col2im stages of the SparseDrop convolution, restricted to the kept 128x128 blocks.
+//
+// The im2col matrix of flash_dropout/functional/im2col_conv2d.py:17-20 has M = N*P*Q rows and K = C*R*S
+// columns, k = c*R*S + r*S + s.  It is stored K-outer here ("colT": row k holds all M entries of column k,
+// leading dimension ldm), because consecutive m are consecutive pixels of the NCHW input, so both the gather
+// and the store run along the contiguous direction and the GEMM kernel takes colT.T as an MN-major operand.
+// Only blocks the plan keeps are ever written or read: at p = 0.5 half of the 2 x 302 MB an unfold
+// (flash_dropout/functional/im2col_conv2d.py:17) moves.  Both kernels are pure data movement: HBM-bound.
+//
+// The reference's own CUDA im2col (flash_dropout/cuda/src/im2col.cuh:17-72) is an NHWC scatter that was never
+// built; nothing is taken from it.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "sd_common.h"
+#include "sd_plan.cuh"
+
+namespace sd {
+
+struct ConvGeom {
+    int N, C, H, W, R, S, P, Q;
+    int pad_h, pad_w, stride_h, stride_w, dil_h, dil_w;
+    int M, K;           // N*P*Q, C*R*S
+    long long ldm;      // leading dimension of colT (>= M, multiple of 8)
+    int Rb, Cb;         // plan grid: ceil(M/128) x ceil(K/128) (K as the GEMM sees it)
+};
+
+constexpr int kConvThreads = 256;
+
+// One CTA per kept block (grid-stride): 128 k-rows x 128 m-columns of colT.  Thread t owns the 8 consecutive m
+// starting at (t % 16) * 8 and visits k-rows (t / 16) + 16 * pass.
+__global__ void __launch_bounds__(kConvThreads) im2col_kept_kernel(const unsigned short* __restrict__ x,
+                                                                   unsigned short* __restrict__ colT, ConvGeom g,
+                                                                   const int* __restrict__ kept_pairs,
+                                                                   const int* __restrict__ n_kept) {
+    const int total = kept_pairs ? __ldg(n_kept) : g.Rb * g.Cb;
+    const int mgrp = threadIdx.x & 15, ksub = threadIdx.x >> 4;
+    const int PQ = g.P * g.Q, HW = g.H * g.W, RS = g.R * g.S;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        const int mb = kept_pairs ? __ldg(kept_pairs + 2 * t) : t / g.Cb;
+        const int kb = kept_pairs ? __ldg(kept_pairs + 2 * t + 1) : t - (t / g.Cb) * g.Cb;
+        const int m0 = mb * 128 + mgrp * 8;
+        if (m0 >= g.ldm) continue;
+        // decode the 8 output pixels once
+        long long base[8];
+        int hb[8], wb[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int m = m0 + j;
+            if (m < g.M) {
+                const int n = m / PQ, pq = m - n * PQ, p = pq / g.Q, q = pq - p * g.Q;
+                base[j] = (long long)n * g.C * HW;
+                hb[j] = p * g.stride_h - g.pad_h;
+                wb[j] = q * g.stride_w - g.pad_w;
+            } else {
+                base[j] = 0;
+                hb[j] = -(1 << 28);   // never in range: the padding columns of colT are zero
+                wb[j] = 0;
+            }
+        }
+#pragma unroll 2
+        for (int pass = 0; pass < 8; ++pass) {
+            const int k = kb * 128 + pass * 16 + ksub;
+            if (k >= g.K) break;
+            const int c = k / RS, rs = k - c * RS, r = rs / g.S, s = rs - r * g.S;
+            const int hoff = r * g.dil_h, woff = s * g.dil_w;
+            const unsigned short* xc = x + (long long)c * HW;
+            unsigned short v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int h = hb[j] + hoff, w = wb[j] + woff;
+                const bool in = (unsigned)h < (unsigned)g.H && (unsigned)w < (unsigned)g.W;
+                v[j] = in ? __ldg(xc + base[j] + (long long)h * g.W + w) : (unsigned short)0;
+            }
+            uint4 o;
+            o.x = v[0] | (uint32_t(v[1]) << 16);
+            o.y = v[2] | (uint32_t(v[3]) << 16);
+            o.z = v[4] | (uint32_t(v[5]) << 16);
+            o.w = v[6] | (uint32_t(v[7]) << 16);
+            *reinterpret_cast<uint4*>(colT + (long long)k * g.ldm + m0) = o;
+        }
+    }
+}
+
+__device__ __forceinline__ float to_float(unsigned short v, int is_bf16) {
+    return is_bf16 ? __bfloat162float(__ushort_as_bfloat16(v)) : __half2float(__ushort_as_half(v));
+}
+__device__ __forceinline__ unsigned short from_float(float f, int is_bf16) {
+    return is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f)) : __half_as_ushort(__float2half_rn(f));
+}
+
+// Adjoint of the kept-block im2col: dx[n,c,h,w] = sum over the filter taps (r,s) that map (h,w) to an output
+// pixel (p,q) of dcolT[k(c,r,s)][m(n,p,q)], skipping dropped blocks (their entries are zero by definition).
+// One thread per input element, consecutive threads along w, so every tap is a coalesced read along m.
+__global__ void __launch_bounds__(kConvThreads) col2im_kept_kernel(const unsigned short* __restrict__ dcolT,
+                                                                   unsigned short* __restrict__ dx, ConvGeom g,
+                                                                   const unsigned char* __restrict__ tile_mask,
+                                                                   int is_bf16) {
+    const long long total = (long long)g.N * g.C * g.H * g.W;
+    const int PQ = g.P * g.Q, RS = g.R * g.S;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int w = int(i % g.W);
+        long long rest = i / g.W;
+        const int h = int(rest % g.H);
+        rest /= g.H;
+        const int c = int(rest % g.C), n = int(rest / g.C);
+        float acc = 0.f;
+        for (int r = 0; r < g.R; ++r) {
+            const int hh = h + g.pad_h - r * g.dil_h;
+            if (hh < 0 || hh % g.stride_h) continue;
+            const int p = hh / g.stride_h;
+            if (p >= g.P) continue;
+            for (int s = 0; s < g.S; ++s) {
+                const int ww = w + g.pad_w - s * g.dil_w;
+                if (ww < 0 || ww % g.stride_w) continue;
+                const int q = ww / g.stride_w;
+                if (q >= g.Q) continue;
+                const int m = n * PQ + p * g.Q + q, k = c * RS + r * g.S + s;
+                if (tile_mask && tile_mask[(m >> 7) * g.Cb + (k >> 7)]) continue;
+                acc += to_float(__ldg(dcolT + (long long)k * g.ldm + m), is_bf16);
+            }
+        }
+        dx[i] = from_float(acc, is_bf16);
+    }
+}
+
+static int make_geom(ConvGeom* g, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
+                     int stride_w, int dil_h, int dil_w, int64_t ldm, int k_gemm) {
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || R <= 0 || S <= 0)
+        return fail(SD_ERR_INVALID_ARG, "conv sizes must be positive");
+    if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0)
+        return fail(SD_ERR_INVALID_ARG, "stride and dilation must be positive, padding non-negative");
+    const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / stride_h + 1;
+    const int Q = (W + 2 * pad_w - dil_w * (S - 1) - 1) / stride_w + 1;
+    if (P <= 0 || Q <= 0) return fail(SD_ERR_INVALID_ARG, "the filter does not fit the padded input");
+    const long long M = (long long)N * P * Q, K = (long long)C * R * S;
+    if (M > (1ll << 30) || K > (1ll << 30)) return fail(SD_ERR_TOO_LARGE, "im2col matrix too large (M=%lld, K=%lld)", M, K);
+    if (ldm < M || (ldm & 7)) return fail(SD_ERR_LAYOUT, "ldm (%lld) must be >= N*P*Q (%lld) and a multiple of 8", (long long)ldm, M);
+    if (k_gemm < K) return fail(SD_ERR_INVALID_ARG, "k_gemm (%d) must be >= C*R*S (%lld)", k_gemm, K);
+    *g = ConvGeom{N, C, H, W, R, S, P, Q, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, int(M), int(K), ldm,
+                  int((M + 127) / 128), (k_gemm + 127) / 128};
+    return SD_OK;
+}
+
+}  // namespace sd
+
+extern "C" {
+
+int sd_im2col_kept(const void* x, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
+                   int stride_w, int dil_h, int dil_w, void* colT, int64_t ldm, int k_gemm, const void* plan,
+                   void* stream) {
+    if (!x || !colT) return sd::fail(SD_ERR_INVALID_ARG, "x or colT is null");
+    if ((reinterpret_cast<uintptr_t>(colT) & 15)) return sd::fail(SD_ERR_LAYOUT, "colT must be 16-byte aligned");
+    sd::ConvGeom g;
+    int rc = sd::make_geom(&g, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, ldm, k_gemm);
+    if (rc) return rc;
+    const int *pairs = nullptr, *n_kept = nullptr;
+    if (plan) {
+        const sd_plan_layout L = sd::plan_layout(g.Rb, g.Cb);
+        const unsigned char* b = static_cast<const unsigned char*>(plan);
+        pairs = reinterpret_cast<const int*>(b + L.kept_pairs);
+        n_kept = reinterpret_cast<const int*>(b + L.header) + sd::H_NNZ;
+    }
+    int sms = 0;
+    rc = sd::sm_count_current_device(&sms);
+    if (rc) return rc;
+    long long blocks = (long long)g.Rb * g.Cb;
+    int grid = int(blocks < (long long)sms * 8 ? blocks : (long long)sms * 8);
+    sd::im2col_kept_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const unsigned short*>(x), static_cast<unsigned short*>(colT), g, pairs, n_kept);
+    SD_CUDA_TRY(cudaGetLastError());
+    return SD_OK;
+}
+
+int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int H, int W, int R, int S, int pad_h,
+                   int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, void* dx, const void* plan, int dtype,
+                   void* stream) {
+    if (!dcolT || !dx) return sd::fail(SD_ERR_INVALID_ARG, "dcolT or dx is null");
+    if (dtype != SD_F16 && dtype != SD_BF16) return sd::fail(SD_ERR_INVALID_ARG, "dtype must be SD_F16 or SD_BF16");
+    sd::ConvGeom g;
+    int rc = sd::make_geom(&g, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, ldm, k_gemm);
+    if (rc) return rc;
+    const unsigned char* mask = nullptr;
+    if (plan) mask = static_cast<const unsigned char*>(plan) + sd::plan_layout(g.Rb, g.Cb).mask;
+    int sms = 0;
+    rc = sd::sm_count_current_device(&sms);
+    if (rc) return rc;
+    const long long total = (long long)N * C * H * W;
+    long long blocks = (total + sd::kConvThreads - 1) / sd::kConvThreads;
+    int grid = int(blocks < (long long)sms * 16 ? blocks : (long long)sms * 16);
+    sd::col2im_kept_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask, dtype == SD_BF16);
+    SD_CUDA_TRY(cudaGetLastError());
+    return SD_OK;
+}
+
+}  // extern "C"

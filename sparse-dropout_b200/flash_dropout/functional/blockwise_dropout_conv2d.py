@@ -1,37 +1,134 @@
-"""Conv2d with blockwise dropout on its im2col matrix, on the sm_100a DSD/SDD kernels.
+"""Conv2d with blockwise dropout on its im2col matrix, on the sm_100a kernels.
 
 The reference has no such op (its blockwise conv variants are commented out,
 flash_dropout/layers/dropout_conv.py:86-99).  Semantics defined here: the im2col matrix of
 flash_dropout/functional/im2col_conv2d.py:17-20 — M = N*P*Q rows, K = C*R*S columns in unfold order
 k = c*R*S + r*S + s — gets one Bernoulli(p) drop decision per block_size x block_size block
 (K zero-padded to the next multiple of the block), then the linear with the kernel viewed (Kout, CRS).
+
+Data flow (nothing goes through F.unfold):
+  forward   im2col_kept  : x (NCHW) -> kept blocks of colT[K][M]                 (HBM-bound gather)
+            DSD          : y2d[M, Kout] = (keep o colT^T) . W2d^T / (1-p)        (colT^T is an MN-major operand)
+            y is returned as an NCHW-shaped view of y2d (channels_last strides), no permute copy
+  backward  DSD          : dW2d[Kout, K] written transposed, reduction over kept row blocks of each K tile
+            SDD          : dcolT[K][M] = keep o (dy2d . W2d) / (1-p), stored column-major
+            col2im_kept  : dx (NCHW) = adjoint gather over kept blocks           (HBM-bound)
+  colT is recomputed in backward from the saved input (33 MB instead of 300 MB of saved activations at
+  BASELINE's conv config).
 """
 from __future__ import annotations
 
-import torch
-import torch.nn.functional as F
+from math import ceil
 
-from .blockwise_dropout_matmul_cuda import blockwise_dropout_matmul
-from .im2col_conv2d import conv_output_size, im2col_matrix
+import torch
+
+from flash_dropout import _lib
+from flash_dropout import random as sd_random
+from flash_dropout.cuda.binding_gemm import BlockPlan, _on_device, dsd, sdd
+
+from .im2col_conv2d import conv_output_size
+
+
+def _round8(v: int) -> int:
+    return (v + 7) & ~7
+
+
+def im2col_kept(x: torch.Tensor, kernel_size, padding, stride, dilation, plan: BlockPlan | None,
+                k_gemm: int | None = None) -> torch.Tensor:
+    """colT[k_gemm][ldm] (K-outer im2col matrix) with only the plan's kept blocks filled in."""
+    N, C, H, W = x.shape
+    R, S = kernel_size
+    P, Q = conv_output_size(H, W, R, S, padding, stride, dilation)
+    M, K = N * P * Q, C * R * S
+    k_gemm = k_gemm or _round8(K)
+    ldm = _round8(M)
+    colT = torch.empty((k_gemm, ldm), dtype=x.dtype, device=x.device)
+    if k_gemm > K:
+        colT[K:].zero_()
+    x = x.contiguous()
+    with _on_device(x.device):
+        _lib.check(_lib.lib().sd_im2col_kept(
+            x.data_ptr(), N, C, H, W, R, S, padding[0], padding[1], stride[0], stride[1], dilation[0], dilation[1],
+            colT.data_ptr(), ldm, k_gemm, plan.buf.data_ptr() if plan is not None else None,
+            _lib.stream_ptr(x.device)))
+    return colT
+
+
+def col2im_kept(dcolT: torch.Tensor, x_shape, kernel_size, padding, stride, dilation,
+                plan: BlockPlan | None) -> torch.Tensor:
+    N, C, H, W = x_shape
+    R, S = kernel_size
+    dx = torch.empty(x_shape, dtype=dcolT.dtype, device=dcolT.device)
+    with _on_device(dcolT.device):
+        _lib.check(_lib.lib().sd_col2im_kept(
+            dcolT.data_ptr(), dcolT.stride(0), dcolT.size(0), N, C, H, W, R, S, padding[0], padding[1], stride[0],
+            stride[1], dilation[0], dilation[1], dx.data_ptr(), plan.buf.data_ptr() if plan is not None else None,
+            _lib.dtype_code(dcolT.dtype), _lib.stream_ptr(dcolT.device)))
+    return dx
+
+
+class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, kernel, block_size, p, padding, stride, dilation, plan):
+        assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
+        if not (input.is_cuda and kernel.is_cuda):
+            raise RuntimeError("input and kernel must be CUDA")
+        if input.dtype != kernel.dtype:
+            raise RuntimeError(f"input ({input.dtype}) and kernel ({kernel.dtype}) must have the same dtype")
+        _lib.dtype_code(input.dtype)
+        N, C, H, W = input.shape
+        Ko, Ck, R, S = kernel.shape
+        if Ck != C:
+            raise RuntimeError(f"kernel expects {Ck} input channels, input has {C}")
+        P, Q = conv_output_size(H, W, R, S, padding, stride, dilation)
+        M, K = N * P * Q, C * R * S
+        Kg, Kog = _round8(K), _round8(Ko)
+        if plan is None:
+            seed, offset = sd_random.next_seed_offset()
+            plan = BlockPlan.from_seed(M, Kg, block_size, p, seed, offset, input.device)
+        w2d = kernel.reshape(Ko, K)
+        if Kg != K or Kog != Ko:                         # 16-byte rows for TMA; zero padding changes nothing
+            w2d = torch.nn.functional.pad(w2d, (0, Kg - K, 0, Kog - Ko))
+        w2d = w2d.contiguous()
+        colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg)
+        y2d = dsd(colT.T[:M], w2d, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))      # (M, Kog)
+        ctx.save_for_backward(input, w2d)
+        ctx.plan, ctx.p = plan, p
+        ctx.geom = (padding, stride, dilation, (R, S), Ko, K)
+        return y2d.view(N, P, Q, Kog)[..., :Ko].permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, w2d = ctx.saved_tensors
+        plan, scale = ctx.plan, 1.0 / (1.0 - ctx.p)
+        padding, stride, dilation, (R, S), Ko, K = ctx.geom
+        N, C, H, W = input.shape
+        Kog, Kg = w2d.shape
+        M = grad_output.numel() // Ko
+        dy2d = grad_output.to(input.dtype).permute(0, 2, 3, 1).reshape(M, Ko)   # free for channels_last gradients
+        if Kog != Ko:
+            dy2d = torch.nn.functional.pad(dy2d, (0, Kog - Ko))
+        dy2d = dy2d.contiguous()
+        grad_input = grad_kernel = None
+        if ctx.needs_input_grad[1]:
+            colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg)
+            dw2d = torch.empty((Kog, Kg), dtype=input.dtype, device=input.device)
+            dsd(colT[:, :M], dy2d.T, plan, _lib.SD_PLAN_COLS, scale, out=dw2d.T)
+            grad_kernel = dw2d[:Ko, :K].reshape(Ko, C, R, S)
+            del colT
+        if ctx.needs_input_grad[0]:
+            dcolT = torch.empty((Kg, (M + 7) & ~7), dtype=input.dtype, device=input.device)
+            sdd(dy2d, w2d.T, plan, scale, out=dcolT.T[:M])
+            grad_input = col2im_kept(dcolT, input.shape, (R, S), padding, stride, dilation, plan)
+        return grad_input, grad_kernel, None, None, None, None, None, None
 
 
 def blockwise_dropout_conv2d(input: torch.Tensor, kernel: torch.Tensor, block_size: int, p: float,
                              padding=(0, 0), stride=(1, 1), dilation=(1, 1), plan=None) -> torch.Tensor:
-    N, C, H, W = input.shape
-    Ko, _, R, S = kernel.shape
-    P, Q = conv_output_size(H, W, R, S, padding, stride, dilation)
+    """Conv2d (no bias) whose im2col matrix is block-dropped with probability ``p``; NCHW in, NCHW-shaped out."""
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
         input, kernel = input.to(dt), kernel.to(dt)
-    a = im2col_matrix(input, (R, S), padding, stride, dilation).reshape(N * P * Q, C * R * S)
-    w = kernel.reshape(Ko, C * R * S)
-    pad_k = (-a.size(1)) % 8
-    pad_n = (-Ko) % 8
-    if pad_k:   # 16-byte rows for TMA; zero columns change nothing
-        a, w = F.pad(a, (0, pad_k)), F.pad(w, (0, pad_k))
-    if pad_n:
-        w = F.pad(w, (0, 0, 0, pad_n))
-    out = blockwise_dropout_matmul(a, w, block_size, p, plan)      # (N PQ, Ko)
-    if pad_n:
-        out = out[:, :Ko]
-    return out.reshape(N, P * Q, Ko).transpose(1, 2).reshape(N, Ko, P, Q)
+    with torch.autocast("cuda", enabled=False):
+        return BlockwiseDropoutConv2dCUDA.apply(input, kernel, block_size, p, tuple(padding), tuple(stride),
+                                                tuple(dilation), plan)

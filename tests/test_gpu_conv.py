@@ -1,0 +1,104 @@
+"""im2col / col2im stages (kept blocks only) and the SparseDrop convolution vs the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as TF
+
+from oracle import masked_dense as md
+from oracle import philox_mask as pm
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+GEOMS = [  # N, C, H, W, R, S, padding, stride, dilation
+    (2, 16, 16, 16, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (3, 5, 9, 7, 3, 2, (0, 1), (2, 1), (1, 1)),
+    (2, 8, 10, 10, 3, 3, (2, 2), (1, 2), (2, 2)),
+    (1, 64, 32, 32, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (4, 3, 13, 11, 5, 5, (2, 2), (2, 2), (1, 1)),
+]
+
+
+@pytest.mark.parametrize("geom", GEOMS)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_im2col_and_col2im_against_unfold_fold(built_lib, geom, dtype):
+    """Bit-exact data movement: every kept block equals the unfold matrix, dropped blocks are left alone;
+    col2im equals fold of the masked matrix (fp32 sum of at most R*S 16-bit values, rounded once)."""
+    from flash_dropout.cuda.binding_gemm import BlockPlan
+    from flash_dropout.functional.blockwise_dropout_conv2d import col2im_kept, im2col_kept
+    N, C, H, W, R, S, pad, stride, dil = geom
+    g = torch.Generator().manual_seed(N * 100 + C)
+    x = torch.randn(N, C, H, W, generator=g).to(dtype)
+    cols = TF.unfold(x.float(), (R, S), padding=pad, stride=stride, dilation=dil)      # (N, K, PQ)
+    K, PQ = cols.shape[1], cols.shape[2]
+    M = N * PQ
+    want = cols.permute(1, 0, 2).reshape(K, M)                                           # colT
+    Kg = (K + 7) & ~7
+    for p in (0.0, 0.5):
+        mask = pm.block_mask(M, Kg, 128, p, seed=5)
+        plan = BlockPlan.from_mask(torch.from_numpy(mask).to(DEV), M, Kg, 128)
+        colT = torch.full((Kg, (M + 7) & ~7), 7.0, dtype=dtype, device=DEV)              # sentinel in dropped blocks
+        got = im2col_kept(x.to(DEV), (R, S), pad, stride, dil, plan, Kg)
+        keep = md._keep_matrix(mask, M, Kg, 128).T.bool()[:K]                            # (K, M)
+        assert torch.equal(got[:K, :M].float().cpu()[keep], want[keep])
+        if Kg > K:
+            assert (got[K:] == 0).all()
+        # adjoint on a random cotangent
+        dcol = torch.randn(Kg, (M + 7) & ~7, generator=g).to(dtype)
+        dcol_masked = dcol[:K, :M].float() * keep
+        want_dx = TF.fold(dcol_masked.view(K, N, PQ).permute(1, 0, 2), (H, W), (R, S), padding=pad, stride=stride,
+                          dilation=dil)
+        got_dx = col2im_kept(dcol.to(DEV), (N, C, H, W), (R, S), pad, stride, dil, plan)
+        torch.testing.assert_close(got_dx.float().cpu(), want_dx.to(dtype).float(), rtol=2e-2, atol=2e-2)
+    dense = im2col_kept(x.to(DEV), (R, S), pad, stride, dil, None, Kg)
+    assert torch.equal(dense[:K, :M].float().cpu(), want)
+
+
+@pytest.mark.parametrize("geom,Ko", [(GEOMS[0], 128), (GEOMS[1], 24), (GEOMS[2], 40), (GEOMS[4], 10)])
+def test_conv_op_against_oracle(built_lib, geom, Ko):
+    import flash_dropout.functional as F
+    from flash_dropout import random as sd_random
+    N, C, H, W, R, S, pad, stride, dil = geom
+    p = 0.5
+    g = torch.Generator().manual_seed(Ko)
+    x = torch.randn(N, C, H, W, generator=g).half()
+    k = (torch.randn(Ko, C, R, S, generator=g) / (C * R * S) ** 0.5).half()
+    xa, ka = x.to(DEV).requires_grad_(), k.to(DEV).requires_grad_()
+    sd_random.manual_seed(31, subsequence=0)
+    y = F.cuda_blockwise_dropout_conv2d(xa, ka, 128, p, padding=pad, stride=stride, dilation=dil)
+    P, Q = y.shape[2:]
+    dy = (torch.randn(N, Ko, P, Q, generator=g) * 0.25).half()
+    y.backward(dy.to(DEV))
+    M, K = N * P * Q, C * R * S
+    mask = pm.block_mask(M, K, 128, p, seed=31, offset=0)
+    y_ref = md.conv_forward(x, k, mask, 128, p, pad, stride, dil)
+    dx_ref, dk_ref = md.conv_backward(x, k, mask, 128, p, dy, pad, stride, dil)
+    torch.testing.assert_close(y.float().cpu(), y_ref, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(ka.grad.float().cpu(), dk_ref, rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(xa.grad.float().cpu(), dx_ref, rtol=1e-2, atol=2e-2)
+    sd_random.follow_torch_seed()
+
+
+def test_conv_baseline_config_shapes(built_lib):
+    """BASELINE configs[2] at a reduced batch (N=16 of 256): 64 -> 128 channels, 32x32, 3x3, pad 1, p=0.5;
+    mask grid (N*1024/128) x 5 with a ragged last K block (576 = 4.5 blocks)."""
+    import flash_dropout.functional as F
+    from flash_dropout import random as sd_random
+    N = 16
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(N, 64, 32, 32, generator=g).half()
+    k = (torch.randn(128, 64, 3, 3, generator=g) / 24).half()
+    dy = torch.randn(N, 128, 32, 32, generator=g).half()
+    xa, ka = x.to(DEV).requires_grad_(), k.to(DEV).requires_grad_()
+    sd_random.manual_seed(1, subsequence=0)
+    y = F.cuda_blockwise_dropout_conv2d(xa, ka, 128, 0.5, padding=(1, 1))
+    y.backward(dy.to(DEV))
+    mask = pm.block_mask(N * 1024, 576, 128, 0.5, seed=1, offset=0)
+    assert mask.shape == (N * 8, 5)
+    y_ref = md.conv_forward(x, k, mask, 128, 0.5, (1, 1))
+    dx_ref, dk_ref = md.conv_backward(x, k, mask, 128, 0.5, dy, (1, 1))
+    torch.testing.assert_close(y.float().cpu(), y_ref, rtol=1e-2, atol=1e-2)
+    # dW sums 16384 products per element (sigma ~ 128): compare relative to that scale
+    torch.testing.assert_close(ka.grad.float().cpu() / 128, dk_ref / 128, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(xa.grad.float().cpu(), dx_ref, rtol=1e-2, atol=2e-2)
+    sd_random.follow_torch_seed()
