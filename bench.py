@@ -375,6 +375,73 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------ conv
+def run_conv(args) -> None:
+    """BASELINE configs[2]: Conv2d 64->128, 3x3, pad 1 on 256x64x32x32 fp16, blockwise dropout p=0.5, fwd+bwd."""
+    import torch
+
+    import flash_dropout.functional as F
+    from flash_dropout import random as sd_random
+    from flash_dropout.cuda.binding_gemm import BlockPlan
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    Nb, C, H, W, Ko, p = 256, 64, 32, 32, 128, P_DROP
+    g = torch.Generator().manual_seed(SEED)
+    x = torch.randn(Nb, C, H, W, generator=g).half().to(dev).requires_grad_()
+    k = (torch.randn(Ko, C, 3, 3, generator=g) / 24).half().to(dev).requires_grad_()
+    dy = torch.randn(Nb, Ko, H, W, generator=g).half().to(dev).contiguous(memory_format=torch.channels_last)
+    M, K = Nb * H * W, C * 9
+    steps, warmup = args.steps, max(args.warmup, 3)
+    sd_random.manual_seed(SEED, subsequence=0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def sparse_step():
+        x.grad = k.grad = None
+        y = F.cuda_blockwise_dropout_conv2d(x, k, BLOCK, p, padding=(1, 1))
+        y.backward(dy)
+
+    def dense_step():
+        x.grad = k.grad = None
+        y = torch.nn.functional.conv2d(x, k, padding=1)
+        y.backward(dy)
+
+    def unfold_step():
+        x.grad = k.grad = None
+        a = torch.nn.functional.unfold(x, (3, 3), padding=1).transpose(1, 2).reshape(M, K)
+        y = F.cuda_blockwise_dropout_matmul(a, k.reshape(Ko, K), BLOCK, p)
+        y.backward(dy.permute(0, 2, 3, 1).reshape(M, Ko))
+
+    def timeit(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    t_sparse, t_dense, t_unfold = timeit(sparse_step), timeit(dense_step), timeit(unfold_step)
+    plan = BlockPlan.from_seed(M, K, BLOCK, p, SEED, 0, dev)
+    mask = plan.tile_mask.cpu()
+    widths = torch.tensor([128, 128, 128, 128, 64])            # last K block is 64 wide (576 = 4.5 blocks)
+    kept_cols = ((mask == 0).float() * widths).sum().item()    # kept (row block, k) columns
+    flops = 3 * 2.0 * 128 * Ko * kept_cols                     # fwd + dW + dX on kept blocks
+    print(json.dumps({
+        "metric": "SparseDrop conv fwd+bwd useful TFLOP/s", "value": flops / (t_sparse * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": t_sparse, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": "BASELINE configs[2]: Conv2d 64->128 3x3 pad 1, input 256x64x32x32 fp16, 128x128 blocks "
+                               "on the im2col matrix (262144 x 576), p=0.5, fwd+bwd", "l2": "256 MB flush between steps"},
+        "compare_ms": {"sparsedrop_im2col_kept+dsd/sdd": t_sparse, "cudnn_dense_conv_fwd_bwd": t_dense,
+                       "torch_unfold+sparsedrop_linear": t_unfold},
+        "gpu_launches": 6 * steps}))
+
+
 # ------------------------------------------------------------------------------------------ training steps
 def run_train(args) -> None:
     """BASELINE configs[3] (MLP) / configs[4] (char-GPT): one optimizer step per "step", batch sharded over ranks."""
@@ -479,7 +546,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--workload", choices=("gemm", "mlp", "gpt"), default="gemm",
+    ap.add_argument("--workload", choices=("gemm", "mlp", "gpt", "conv"), default="gemm",
                     help="gemm: the headline 4096^3 SparseDrop linear (default); mlp / gpt: one training step")
     ap.add_argument("--variant", default="blockwise[cuda]", help="DropoutMM variant for the training workloads")
     ap.add_argument("--no-extras", action="store_true",
@@ -498,6 +565,9 @@ def main() -> None:
         if args.no_extras:
             cmd.append("--no-extras")
         raise SystemExit(subprocess.call(cmd))
+    if args.workload == "conv":
+        run_conv(args)
+        return
     if args.workload != "gemm":
         run_train(args)
         return

@@ -100,6 +100,15 @@ int sd_plan_from_seed(void* plan, int R, int C, int rep, uint64_t seed, uint64_t
                       uint8_t* mask_out, void* stream);
 
 /*
+ * Same draw, but the offset is base_offset + *device_counter, read on the device, and the launch
+ * increments *device_counter (a uint64 in device memory).  The host no longer chooses the offset, so a
+ * captured CUDA graph that contains this launch draws a fresh mask on every replay.  No counterpart in
+ * the reference (its masks come from torch.rand on the host-controlled generator, utils.py:15).
+ */
+int sd_plan_from_seed_counter(void* plan, int R, int C, int rep, uint64_t seed, uint64_t base_offset,
+                              uint64_t* device_counter, float p, uint8_t* mask_out, void* stream);
+
+/*
  * Build the plan from a caller-supplied bool mask (1 byte per logical block, any two strides),
  * the form in which the reference passes masks to gemm_dsd / gemm_sdd
  * (flash_dropout/cuda/binding_gemm.py:29-47).  mask is ceil(R/rep) x ceil(C/rep).
@@ -181,6 +190,15 @@ int sd_gemm_sdd(const void* A, int64_t a_rs, int64_t a_cs,
                 void* C, int64_t c_rs, int64_t c_cs,
                 int M, int N, int K, const void* plan,
                 float scale, int dtype, void* workspace, int* status, void* stream);
+
+/* Same as sd_gemm_sdd but dropped tiles of C are left untouched instead of being zero-filled, for
+ * consumers that read kept tiles only (sd_col2im_kept): saves writing the dropped share of C.
+ * No counterpart in the reference. */
+int sd_gemm_sdd_kept(const void* A, int64_t a_rs, int64_t a_cs,
+                     const void* B, int64_t b_rs, int64_t b_cs,
+                     void* C, int64_t c_rs, int64_t c_cs,
+                     int M, int N, int K, const void* plan,
+                     float scale, int dtype, void* workspace, int* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Convolution stages.  The im2col matrix of flash_dropout/functional/im2col_conv2d.py:17-20

@@ -27,6 +27,57 @@ struct ConvGeom {
 
 constexpr int kConvThreads = 256;
 
+// Elements [e0, e0 + 8) of a row of `len` 16-bit elements, zero outside [0, len).  The row starts 16-byte aligned
+// and len is a multiple of 8, so each of the (at most two) aligned 8-element chunks the window touches lies either
+// entirely inside the row or entirely outside it: two 16-byte loads and a funnel shift replace eight 2-byte loads.
+__device__ __forceinline__ void load8_shifted(const unsigned short* __restrict__ row, int e0, int len, uint32_t (&out)[4]) {
+    const int a = e0 & ~7, sh = e0 - a;
+    uint4 c0 = make_uint4(0, 0, 0, 0), c1 = make_uint4(0, 0, 0, 0);
+    if (a >= 0 && a < len) c0 = __ldg(reinterpret_cast<const uint4*>(row + a));
+    if (sh && a + 8 >= 0 && a + 8 < len) c1 = __ldg(reinterpret_cast<const uint4*>(row + a + 8));
+    uint32_t w0 = c0.x, w1 = c0.y, w2 = c0.z, w3 = c0.w, w4 = c1.x, w5 = c1.y, w6 = c1.z, w7 = c1.w;
+    const int ws = sh >> 1;
+    if (ws & 1) { w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5; w5 = w6; w6 = w7; }
+    if (ws & 2) { w0 = w2; w1 = w3; w2 = w4; w3 = w5; w4 = w6; }
+    const uint32_t sb = (sh & 1) * 16;
+    out[0] = __funnelshift_r(w0, w1, sb);
+    out[1] = __funnelshift_r(w1, w2, sb);
+    out[2] = __funnelshift_r(w2, w3, sb);
+    out[3] = __funnelshift_r(w3, w4, sb);
+}
+
+// Fast im2col for unit horizontal stride with W % 8 == 0 and Q % 8 == 0: the 8 output pixels a thread owns sit in
+// one output row, so each k-row is one shifted 8-element window of one input row.
+__global__ void __launch_bounds__(kConvThreads) im2col_kept_rows_kernel(const unsigned short* __restrict__ x,
+                                                                        unsigned short* __restrict__ colT, ConvGeom g,
+                                                                        const int* __restrict__ kept_pairs,
+                                                                        const int* __restrict__ n_kept) {
+    const int total = kept_pairs ? __ldg(n_kept) : g.Rb * g.Cb;
+    const int mgrp = threadIdx.x & 15, ksub = threadIdx.x >> 4;
+    const int PQ = g.P * g.Q, HW = g.H * g.W, RS = g.R * g.S;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        const int mb = kept_pairs ? __ldg(kept_pairs + 2 * t) : t / g.Cb;
+        const int kb = kept_pairs ? __ldg(kept_pairs + 2 * t + 1) : t - (t / g.Cb) * g.Cb;
+        const int m0 = mb * 128 + mgrp * 8;
+        if (m0 >= g.ldm) continue;
+        const bool live = m0 < g.M;                      // M % 8 == 0 here, so the group is all in or all out
+        const int n = live ? m0 / PQ : 0, pq = m0 - n * PQ, p = pq / g.Q, q0 = pq - p * g.Q;
+        const unsigned short* xn = x + (long long)n * g.C * HW;
+        const int hbase = p * g.stride_h - g.pad_h, wbase = q0 - g.pad_w;
+#pragma unroll 2
+        for (int pass = 0; pass < 8; ++pass) {
+            const int k = kb * 128 + pass * 16 + ksub;
+            if (k >= g.K) break;
+            const int c = k / RS, rs = k - c * RS, r = rs / g.S, s = rs - r * g.S;
+            const int h = hbase + r * g.dil_h;
+            uint32_t o[4] = {0, 0, 0, 0};
+            if (live && (unsigned)h < (unsigned)g.H)
+                load8_shifted(xn + (long long)c * HW + (long long)h * g.W, wbase + s * g.dil_w, g.W, o);
+            *reinterpret_cast<uint4*>(colT + (long long)k * g.ldm + m0) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 // One CTA per kept block (grid-stride): 128 k-rows x 128 m-columns of colT.  Thread t owns the 8 consecutive m
 // starting at (t % 16) * 8 and visits k-rows (t / 16) + 16 * pass.
 __global__ void __launch_bounds__(kConvThreads) im2col_kept_kernel(const unsigned short* __restrict__ x,
@@ -125,6 +176,61 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_kernel(const unsigne
     }
 }
 
+// Fast col2im for unit strides with W % 8 == 0 and Q % 8 == 0: a thread owns 8 consecutive w of one (n, c, h);
+// every filter tap is one shifted 8-element window of one dcolT row, whose aligned chunks each lie in one block.
+__global__ void __launch_bounds__(kConvThreads) col2im_kept_rows_kernel(const unsigned short* __restrict__ dcolT,
+                                                                        unsigned short* __restrict__ dx, ConvGeom g,
+                                                                        const unsigned char* __restrict__ tile_mask,
+                                                                        int is_bf16) {
+    const int WG = g.W >> 3;
+    const long long total = (long long)g.N * g.C * g.H * WG;
+    const int PQ = g.P * g.Q, RS = g.R * g.S;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int wg = int(i % WG);
+        long long rest = i / WG;
+        const int h = int(rest % g.H);
+        rest /= g.H;
+        const int c = int(rest % g.C), n = int(rest / g.C);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < g.R; ++r) {
+            const int p = h + g.pad_h - r * g.dil_h;
+            if ((unsigned)p >= (unsigned)g.P) continue;
+            for (int s = 0; s < g.S; ++s) {
+                const int k = c * RS + r * g.S + s;
+                const int q0 = wg * 8 + g.pad_w - s * g.dil_w;        // output column that w = wg*8 fed through tap s
+                const int a = q0 & ~7, sh = q0 - a;
+                const long long mrow = (long long)n * PQ + (long long)p * g.Q;
+                const unsigned short* row = dcolT + (long long)k * g.ldm + mrow;
+                // chunk validity: inside [0, Q) and in a kept block
+                uint4 c0 = make_uint4(0, 0, 0, 0), c1 = make_uint4(0, 0, 0, 0);
+                if (a >= 0 && a < g.Q && !(tile_mask && tile_mask[((mrow + a) >> 7) * g.Cb + (k >> 7)]))
+                    c0 = __ldg(reinterpret_cast<const uint4*>(row + a));
+                if (sh && a + 8 >= 0 && a + 8 < g.Q && !(tile_mask && tile_mask[((mrow + a + 8) >> 7) * g.Cb + (k >> 7)]))
+                    c1 = __ldg(reinterpret_cast<const uint4*>(row + a + 8));
+                uint32_t w0 = c0.x, w1 = c0.y, w2 = c0.z, w3 = c0.w, w4 = c1.x, w5 = c1.y, w6 = c1.z, w7 = c1.w;
+                const int ws = sh >> 1;
+                if (ws & 1) { w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5; w5 = w6; w6 = w7; }
+                if (ws & 2) { w0 = w2; w1 = w3; w2 = w4; w3 = w5; w4 = w6; }
+                const uint32_t sb = (sh & 1) * 16;
+                const uint32_t o[4] = {__funnelshift_r(w0, w1, sb), __funnelshift_r(w1, w2, sb),
+                                       __funnelshift_r(w2, w3, sb), __funnelshift_r(w3, w4, sb)};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[2 * j] += to_float((unsigned short)(o[j] & 0xffff), is_bf16);
+                    acc[2 * j + 1] += to_float((unsigned short)(o[j] >> 16), is_bf16);
+                }
+            }
+        }
+        uint4 out;
+        out.x = from_float(acc[0], is_bf16) | (uint32_t(from_float(acc[1], is_bf16)) << 16);
+        out.y = from_float(acc[2], is_bf16) | (uint32_t(from_float(acc[3], is_bf16)) << 16);
+        out.z = from_float(acc[4], is_bf16) | (uint32_t(from_float(acc[5], is_bf16)) << 16);
+        out.w = from_float(acc[6], is_bf16) | (uint32_t(from_float(acc[7], is_bf16)) << 16);
+        *reinterpret_cast<uint4*>(dx + i * 8) = out;
+    }
+}
+
 static int make_geom(ConvGeom* g, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
                      int stride_w, int dil_h, int dil_w, int64_t ldm, int k_gemm) {
     if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || R <= 0 || S <= 0)
@@ -167,8 +273,13 @@ int sd_im2col_kept(const void* x, int N, int C, int H, int W, int R, int S, int 
     if (rc) return rc;
     long long blocks = (long long)g.Rb * g.Cb;
     int grid = int(blocks < (long long)sms * 8 ? blocks : (long long)sms * 8);
-    sd::im2col_kept_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const unsigned short*>(x), static_cast<unsigned short*>(colT), g, pairs, n_kept);
+    const bool rows_path = stride_w == 1 && (W & 7) == 0 && (g.Q & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    if (rows_path)
+        sd::im2col_kept_rows_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(x), static_cast<unsigned short*>(colT), g, pairs, n_kept);
+    else
+        sd::im2col_kept_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(x), static_cast<unsigned short*>(colT), g, pairs, n_kept);
     SD_CUDA_TRY(cudaGetLastError());
     return SD_OK;
 }
@@ -186,11 +297,17 @@ int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int
     int sms = 0;
     rc = sd::sm_count_current_device(&sms);
     if (rc) return rc;
-    const long long total = (long long)N * C * H * W;
+    const bool rows_path = stride_w == 1 && stride_h == 1 && (W & 7) == 0 && (g.Q & 7) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(dcolT) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
+    const long long total = (long long)N * C * H * (rows_path ? W / 8 : W);
     long long blocks = (total + sd::kConvThreads - 1) / sd::kConvThreads;
     int grid = int(blocks < (long long)sms * 16 ? blocks : (long long)sms * 16);
-    sd::col2im_kept_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask, dtype == SD_BF16);
+    if (rows_path)
+        sd::col2im_kept_rows_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask, dtype == SD_BF16);
+    else
+        sd::col2im_kept_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask, dtype == SD_BF16);
     SD_CUDA_TRY(cudaGetLastError());
     return SD_OK;
 }

@@ -342,6 +342,34 @@ __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_f
     }
 }
 
+// r[0..32) += chunk `c` (32 columns) of row `etid` of the partial tiles parked by CTAs [first, last] (those with a
+// non-empty range), added in CTA order.  Two partial tiles are fetched per round trip to L2.
+__device__ __forceinline__ void add_partials(const GemmArgs& g, uint32_t (&r)[32], int first, int last, int c, int etid,
+                                             long long total, int n_ctas) {
+    const float* slot0 = g.ws_slots + size_t(c * 32) * BM + etid;
+    int pc = first;
+    while (pc <= last) {
+        int a = -1, b = -1;
+        for (; pc <= last && a < 0; ++pc)
+            if (WorkIter::range_start(total, pc + 1, n_ctas) > WorkIter::range_start(total, pc, n_ctas)) a = pc;
+        for (; pc <= last && b < 0; ++pc)
+            if (WorkIter::range_start(total, pc + 1, n_ctas) > WorkIter::range_start(total, pc, n_ctas)) b = pc;
+        if (a < 0) break;
+        const float* sa = slot0 + size_t(a) * WS_SLOT_FLOATS;
+        if (b >= 0) {
+            const float* sb = slot0 + size_t(b) * WS_SLOT_FLOATS;
+            float ta[32], tb[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { ta[j] = __ldcg(sa + j * BM); tb[j] = __ldcg(sb + j * BM); }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint((__uint_as_float(r[j]) + ta[j]) + tb[j]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(sa + j * BM));
+        }
+    }
+}
+
 #ifdef SD_TIMING
 // Development aid (not compiled into the product): per-CTA timestamps of one launch.
 __device__ unsigned long long sd_timing[1024][8];
@@ -459,10 +487,10 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             WorkIter it;
             it.init(g, cta, n_ctas);
             Seg w;
-            while (ok && it.next(g, w)) {
+            for (int seg = 0; ok && it.next(g, w); ++seg) {
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, g.status, ST_MMA_ACC)) break;
                 uint32_t accumulate = 0;
-                if (w.i0 == 0 && w.i1 < w.nk) {
+                if (seg > 0 && w.i0 == 0 && w.i1 < w.nk) {
                     // finisher: the other CTAs' partial sums are placed in this accumulator first
                     if (!mbar_wait(bar_preload, 0, abort_flag, g.status, ST_FIXUP)) break;
                     accumulate = 1;
@@ -503,7 +531,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         const bool vec_ok = g.c_cs == 1 && (g.c_rs & 7) == 0 && aligned16;      // row-major result, 16-byte rows
         const bool vec_t_ok = g.c_rs == 1 && (g.c_cs & 7) == 0 && aligned16;    // column-major result
         // Output that no unit covers is zero-filled here, before the first accumulator is ready.
-        if (g.mode == MODE_SDD) {
+        if (g.mode == MODE_SDD && g.n_zero) {
             const int nz = __ldg(g.n_zero);
             for (int z = cta; z < nz; z += n_ctas)
                 zero_tile(g, vec_ok, vec_t_ok, etid, __ldg(g.zero_pairs + 2 * z) * 128, __ldg(g.zero_pairs + 2 * z + 1) * 128);
@@ -527,27 +555,27 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             for (int n = 0; scan.next(g, s); ++n)
                 if (s.i0 == 0 && s.i1 < s.nk) { fin_idx = n; fin_chunks = s.b_row1 >= 0 ? 8 : 4; fin_tile_end = s.tile_end; }
         }
+        // Contributors of the finisher tile: CTAs (cta, fin_last] with a non-empty range.
+        int fin_last = cta;
+        if (fin_idx >= 0)
+            for (int c = cta + 1; c < n_ctas && WorkIter::range_start(it.total, c, n_ctas) < fin_tile_end; ++c) fin_last = c;
+        auto contributes = [&](int c) {
+            return WorkIter::range_start(it.total, c + 1, n_ctas) > WorkIter::range_start(it.total, c, n_ctas);
+        };
         // Adds the partial tiles of the contributing CTAs into TMEM buffer (fin_idx & 1).
         auto preload = [&]() -> bool {
-            int last_c = cta;
-            for (int c = cta + 1; c < n_ctas && WorkIter::range_start(it.total, c, n_ctas) < fin_tile_end; ++c) last_c = c;
+            const int last_c = fin_last;
             bool ok = true;
             if (etid == 0)
                 for (int c = cta + 1; ok && c <= last_c; ++c)
-                    if (WorkIter::range_start(it.total, c + 1, n_ctas) > WorkIter::range_start(it.total, c, n_ctas))
-                        ok = flag_wait(g.ws_flags + c, abort_flag, g.status, ST_FIXUP);
+                    if (contributes(c)) ok = flag_wait(g.ws_flags + c, abort_flag, g.status, ST_FIXUP);
             if (!epilogue_all(ok)) return false;
             const uint32_t taddr = tmem_base + (fin_idx & 1) * BN + (uint32_t(quad * 32) << 16);
             for (int c = 0; c < fin_chunks; ++c) {
                 uint32_t r[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = 0;
-                for (int pc = cta + 1; pc <= last_c; ++pc) {
-                    if (WorkIter::range_start(it.total, pc + 1, n_ctas) == WorkIter::range_start(it.total, pc, n_ctas)) continue;
-                    const float* src = g.ws_slots + size_t(pc) * WS_SLOT_FLOATS + size_t(c * 32) * BM + etid;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(src + j * BM));
-                }
+                add_partials(g, r, cta + 1, last_c, c, etid, it.total, n_ctas);
                 tmem_st_32x32(taddr + c * 32, r);
             }
             tmem_st_wait();
@@ -560,25 +588,35 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             return true;
         };
         bool alive = true;
-        if (fin_idx == 0) alive = preload();                     // nothing to overlap with: do it first
         int acc = 0;
         uint32_t acc_phase = 0;
         Seg w;
         float* my_slot = g.split ? g.ws_slots + size_t(cta) * WS_SLOT_FLOATS : nullptr;
         for (int seg = 0; alive && it.next(g, w); ++seg) {
             const bool partial = w.i0 > 0;                       // goes to this CTA's workspace slot
-            const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
+            // When the finisher tile is this CTA's very first segment there is no earlier main loop to hide a
+            // preload behind; its own MMAs run at once and the partials are added here instead.
+            const bool late_fix = seg == 0 && fin_idx == 0;
+            bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
+            if (late_fix && etid == 0)
+                for (int c = cta + 1; ok && c <= fin_last; ++c)
+                    if (contributes(c)) ok = flag_wait(g.ws_flags + c, abort_flag, g.status, ST_FIXUP);
             if (!epilogue_all(ok)) break;                        // uniform decision of the 128 epilogue threads
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
             const int row = w.a_row + etid;
             const int nchunks = w.b_row1 >= 0 ? 8 : 4;
             const bool transposed = !partial && vec_t_ok && w.a_row + 128 <= g.MM;
+            // chunk c+1 is in flight from TMEM while chunk c is converted and stored
+            uint32_t rbuf[2][32];
+            tmem_ld_32x32(taddr, rbuf[0]);
+            tmem_ld_wait();
+#pragma unroll 2
             for (int c = 0; c < nchunks; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + c * 32, r);
-                tmem_ld_wait();
+                uint32_t (&r)[32] = rbuf[c & 1];
+                if (c + 1 < nchunks) tmem_ld_32x32(taddr + (c + 1) * 32, rbuf[(c + 1) & 1]);
                 const int col = c < 4 ? w.b_row0 + c * 32 : w.b_row1 + (c - 4) * 32;
+                if (late_fix) add_partials(g, r, cta + 1, fin_last, c, etid, it.total, n_ctas);
                 if (partial) {
                     float* dst = my_slot + size_t(c * 32) * BM + etid;
 #pragma unroll
@@ -588,6 +626,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 } else {
                     store_chunk(g, vec_ok, row, col, r);
                 }
+                tmem_ld_wait();
             }
             tc_fence_before();
             __syncwarp();
@@ -596,6 +635,10 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 __threadfence();                                 // partial tile visible before the flag
                 epilogue_sync();
                 if (etid == 0) flag_set(g.ws_flags + cta, 1);
+            } else if (late_fix) {
+                epilogue_sync();                                 // every thread has read the partials
+                if (etid == 0)
+                    for (int c = cta + 1; c <= fin_last; ++c) flag_set(g.ws_flags + c, 0);
             }
             // as late as possible: the accumulator just drained (or the still unused second one) is the finisher's
             if (fin_idx == seg + 2 || (fin_idx == 1 && seg == 0)) alive = preload();
@@ -732,7 +775,8 @@ static PlanView view_plan(const void* plan, int R, int C) {
 
 static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
                     void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
-                    float scale, int dtype, void* workspace, int* status, void* stream, int max_ctas = 0) {
+                    float scale, int dtype, void* workspace, int* status, void* stream, int max_ctas = 0,
+                    bool zero_dropped = true) {
     if (M <= 0 || N <= 0 || K <= 0) return fail(SD_ERR_INVALID_ARG, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
     if (dtype != SD_F16 && dtype != SD_BF16) return fail(SD_ERR_INVALID_ARG, "dtype must be SD_F16 or SD_BF16");
     if (!C) return fail(SD_ERR_INVALID_ARG, "C is null");
@@ -776,7 +820,7 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     } else if (mode == MODE_SDD) {
         PlanView v = view_plan(plan, g.n_row_blocks, (N + 127) / 128);
         g.items = v.sdd_items; g.n_items = v.header + H_SDD_ITEMS;
-        g.zero_pairs = v.drop_pairs; g.n_zero = v.header + H_NDROP;
+        if (zero_dropped) { g.zero_pairs = v.drop_pairs; g.n_zero = v.header + H_NDROP; }
     }
     // Schedule: with fewer output tiles than SMs, whole tiles would leave SMs idle, so the K-tile stream is
     // cut into equal shares instead (needs the workspace).  Otherwise whole tiles, heaviest first.
@@ -858,6 +902,13 @@ int sd_gemm_sdd(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_
                 void* workspace, int* status, void* stream) {
     return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
                         workspace, status, stream);
+}
+
+int sd_gemm_sdd_kept(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
+                     int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, float scale, int dtype,
+                     void* workspace, int* status, void* stream) {
+    return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
+                        workspace, status, stream, 0, /*zero_dropped=*/false);
 }
 
 size_t sd_workspace_bytes(void) {

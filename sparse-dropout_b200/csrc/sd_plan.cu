@@ -51,6 +51,7 @@ struct PlanArgs {
     int R, C, rep;
     int from_seed;
     unsigned long long seed, offset;
+    unsigned long long* counter;   // optional device counter added to `offset`, incremented by this launch
     float p;
     const unsigned char* mask_in;
     long long mask_rs, mask_cs;
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
     unsigned char* m = in_smem ? smask : gmask;
 
     if (threadIdx.x == 0) { s_max_row = 0; s_max_col = 0; }
+    const unsigned long long offset = a.offset + (a.counter ? *a.counter : 0ull);
 
     // ---- phase 0: the drop decision of every tile (1 = dropped)
     for (int i = threadIdx.x; i < RC; i += kPlanThreads) {
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
         const int lr = r / rep, lc = c / rep;
         bool drop;
         if (a.from_seed) {
-            drop = philox_drop(a.seed, a.offset, (unsigned long long)lr * Cm + lc, a.p);
+            drop = philox_drop(a.seed, offset, (unsigned long long)lr * Cm + lc, a.p);
             if (a.mask_out && r == lr * rep && c == lc * rep) a.mask_out[(long long)lr * Cm + lc] = drop;
         } else {
             drop = a.mask_in[lr * a.mask_rs + lc * a.mask_cs] != 0;
@@ -158,8 +160,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
         }
     }
 
-    // ---- phase 2: columns.  Thread t owns columns [t*cpt, (t+1)*cpt).
-    {
+    // ---- phase 2: columns.
+    if (R <= 4 * C) {
+        // wide or square grid: thread t owns columns [t*cpt, (t+1)*cpt) and walks their rows
         const int cpt = (C + kPlanThreads - 1) / kPlanThreads;
         const int c0 = min(C, int(threadIdx.x) * cpt), c1 = min(C, c0 + cpt);
         int kept = 0, mx = 0;
@@ -178,6 +181,26 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
                 if (m[r * C + c] == 0) row_idx[off++] = r;
         }
         if (threadIdx.x == 0) col_ptr[C] = nnz;
+    } else {
+        // tall grid (e.g. the im2col matrix of a conv: thousands of row blocks, a handful of K tiles):
+        // one column at a time, every thread counts its own chunk of rows, a CTA-wide scan orders them
+        const int rpt = (R + kPlanThreads - 1) / kPlanThreads;
+        const int r0 = min(R, int(threadIdx.x) * rpt), r1 = min(R, r0 + rpt);
+        int col_start = 0;
+        for (int c = 0; c < C; ++c) {
+            int cnt = 0;
+            for (int r = r0; r < r1; ++r) cnt += (m[r * C + c] == 0);
+            int col_total;
+            int off = col_start + block_exclusive_scan(cnt, warp_sums, col_total);
+            for (int r = r0; r < r1; ++r)
+                if (m[r * C + c] == 0) row_idx[off++] = r;
+            if (threadIdx.x == 0) {
+                col_ptr[c] = col_start;
+                if (col_total > s_max_col) s_max_col = col_total;
+            }
+            col_start += col_total;
+        }
+        if (threadIdx.x == 0) col_ptr[C] = col_start;
     }
     __syncthreads();   // row_ptr / col_ptr visible to the whole CTA
 
@@ -224,6 +247,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
     if (threadIdx.x == 0) {
         header[H_MAX_ROW] = s_max_row;
         header[H_MAX_COL] = s_max_col;
+        if (a.counter) *a.counter = offset - a.offset + 1;   // every thread read it before the first barrier
     }
 }
 
@@ -261,6 +285,20 @@ int sd_plan_from_seed(void* plan, int R, int C, int rep, uint64_t seed, uint64_t
     a.R = R; a.C = C; a.rep = rep;
     a.from_seed = 1;
     a.seed = seed; a.offset = offset; a.p = p;
+    a.mask_out = mask_out;
+    return sd::launch_plan(a, stream);
+}
+
+int sd_plan_from_seed_counter(void* plan, int R, int C, int rep, uint64_t seed, uint64_t base_offset,
+                              uint64_t* device_counter, float p, uint8_t* mask_out, void* stream) {
+    if (!(p >= 0.0f && p < 1.0f)) return sd::fail(SD_ERR_INVALID_ARG, "Dropout probability must be in [0, 1)");
+    if (!device_counter) return sd::fail(SD_ERR_INVALID_ARG, "device_counter is null");
+    sd::PlanArgs a{};
+    a.plan = static_cast<unsigned char*>(plan);
+    a.R = R; a.C = C; a.rep = rep;
+    a.from_seed = 1;
+    a.seed = seed; a.offset = base_offset; a.p = p;
+    a.counter = reinterpret_cast<unsigned long long*>(device_counter);
     a.mask_out = mask_out;
     return sd::launch_plan(a, stream);
 }

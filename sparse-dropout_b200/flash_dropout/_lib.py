@@ -20,8 +20,8 @@ SD_PLAN_ROWS, SD_PLAN_COLS = 0, 1
 
 #: every symbol include/sparsedrop.h declares
 EXPORTS = (
-    "sd_version", "sd_last_error", "sd_plan_bytes", "sd_plan_offsets", "sd_plan_from_seed",
-    "sd_plan_from_mask", "sd_workspace_bytes", "sd_workspace_init", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd",
+    "sd_version", "sd_last_error", "sd_plan_bytes", "sd_plan_offsets", "sd_plan_from_seed", "sd_plan_from_seed_counter",
+    "sd_plan_from_mask", "sd_workspace_bytes", "sd_workspace_init", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd", "sd_gemm_sdd_kept",
     "sd_gemm_dsd_static_scratch", "sd_im2col_kept", "sd_col2im_kept", "sd_check_status",
 )
 
@@ -52,6 +52,8 @@ def lib() -> C.CDLL:
     L.sd_plan_offsets.argtypes = [i32, i32, C.POINTER(PlanLayout)]
     L.sd_plan_from_seed.restype = i32
     L.sd_plan_from_seed.argtypes = [vp, i32, i32, i32, u64, u64, f32, vp, vp]
+    L.sd_plan_from_seed_counter.restype = i32
+    L.sd_plan_from_seed_counter.argtypes = [vp, i32, i32, i32, u64, u64, vp, f32, vp, vp]
     L.sd_plan_from_mask.restype = i32
     L.sd_plan_from_mask.argtypes = [vp, i32, i32, i32, vp, i64, i64, vp]
     mat = [vp, i64, i64]
@@ -61,6 +63,8 @@ def lib() -> C.CDLL:
     L.sd_gemm_dsd.argtypes = mat * 3 + [i32, i32, i32, vp, i32, f32, i32, vp, vp, vp]
     L.sd_gemm_sdd.restype = i32
     L.sd_gemm_sdd.argtypes = mat * 3 + [i32, i32, i32, vp, f32, i32, vp, vp, vp]
+    L.sd_gemm_sdd_kept.restype = i32
+    L.sd_gemm_sdd_kept.argtypes = L.sd_gemm_sdd.argtypes
     L.sd_gemm_dsd_static_scratch.restype = i32
     L.sd_gemm_dsd_static_scratch.argtypes = mat * 3 + [i32, i32, i32, vp, i32, f32, i32, vp, vp]
     L.sd_im2col_kept.restype = i32

@@ -64,12 +64,38 @@ class BlockPlan:
         rep = _rep(block_size)
         plan = cls(ceil(M / TILE), ceil(K / TILE), device)
         mask = torch.empty((ceil(plan.R / rep), ceil(plan.C / rep)), dtype=torch.bool, device=device)
-        with torch.cuda.device(device):
+        with _on_device(device):
             _lib.check(_lib.lib().sd_plan_from_seed(
                 plan.buf.data_ptr(), plan.R, plan.C, rep, seed & (2**64 - 1), offset & (2**64 - 1), float(p),
                 mask.data_ptr(), _lib.stream_ptr(device)))
         plan.mask = mask
         return plan
+
+    @classmethod
+    def from_device_counter(cls, M: int, K: int, block_size: int, p: float, seed: int, base_offset: int,
+                            counter: torch.Tensor, device: torch.device) -> "BlockPlan":
+        """Like ``from_seed`` with offset = base_offset + counter[0], read and incremented on the device."""
+        assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
+        rep = _rep(block_size)
+        plan = cls(ceil(M / TILE), ceil(K / TILE), device)
+        mask = torch.empty((ceil(plan.R / rep), ceil(plan.C / rep)), dtype=torch.bool, device=device)
+        with _on_device(device):
+            _lib.check(_lib.lib().sd_plan_from_seed_counter(
+                plan.buf.data_ptr(), plan.R, plan.C, rep, seed & (2**64 - 1), base_offset & (2**64 - 1),
+                counter.data_ptr(), float(p), mask.data_ptr(), _lib.stream_ptr(device)))
+        plan.mask = mask
+        return plan
+
+    @classmethod
+    def draw(cls, M: int, K: int, block_size: int, p: float, device: torch.device) -> "BlockPlan":
+        """Next mask of the stream ``flash_dropout.random`` describes (host- or device-side counter)."""
+        from flash_dropout import random as sd_random
+        counter = sd_random.device_counter(device)
+        if counter is not None:
+            seed, base = sd_random.seed_and_base()
+            return cls.from_device_counter(M, K, block_size, p, seed, base, counter, device)
+        seed, offset = sd_random.next_seed_offset()
+        return cls.from_seed(M, K, block_size, p, seed, offset, device)
 
     @classmethod
     def from_mask(cls, mask: torch.Tensor, M: int, K: int, block_size: int) -> "BlockPlan":
@@ -214,15 +240,17 @@ def dsd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, side: int, scale: flo
 
 
 def sdd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float,
-        out: torch.Tensor | None = None, ws="auto") -> torch.Tensor:
-    """``scale * keep o (A @ B.T)``: kept output tiles computed, dropped tiles written as zeros."""
+        out: torch.Tensor | None = None, ws="auto", zero_dropped: bool = True) -> torch.Tensor:
+    """``scale * keep o (A @ B.T)``: kept output tiles computed, dropped tiles written as zeros
+    (or left untouched with ``zero_dropped=False``, for consumers that only read kept tiles)."""
     dt = _check_pair(A, B)
     M, N = A.size(0), B.size(0)
     if (plan.R, plan.C) != (ceil(M / TILE), ceil(N / TILE)):
         raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the output {(M, N)}")
     Cm = _out(A, B, out)
     with _on_device(A.device):
-        _lib.check(_lib.lib().sd_gemm_sdd(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),
+        fn = _lib.lib().sd_gemm_sdd if zero_dropped else _lib.lib().sd_gemm_sdd_kept
+        _lib.check(fn(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),
                                           float(scale), dt, _ws_ptr(ws, A.device), None, _lib.stream_ptr(A.device)))
     return Cm
 

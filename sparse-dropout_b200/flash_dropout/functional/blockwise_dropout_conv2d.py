@@ -84,8 +84,7 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
         M, K = N * P * Q, C * R * S
         Kg, Kog = _round8(K), _round8(Ko)
         if plan is None:
-            seed, offset = sd_random.next_seed_offset()
-            plan = BlockPlan.from_seed(M, Kg, block_size, p, seed, offset, input.device)
+            plan = BlockPlan.draw(M, Kg, block_size, p, input.device)
         w2d = kernel.reshape(Ko, K)
         if Kg != K or Kog != Ko:                         # 16-byte rows for TMA; zero padding changes nothing
             w2d = torch.nn.functional.pad(w2d, (0, Kg - K, 0, Kog - Ko))
@@ -118,7 +117,7 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
             del colT
         if ctx.needs_input_grad[0]:
             dcolT = torch.empty((Kg, (M + 7) & ~7), dtype=input.dtype, device=input.device)
-            sdd(dy2d, w2d.T, plan, scale, out=dcolT.T[:M])
+            sdd(dy2d, w2d.T, plan, scale, out=dcolT.T[:M], zero_dropped=False)    # col2im reads kept blocks only
             grad_input = col2im_kept(dcolT, input.shape, (R, S), padding, stride, dilation, plan)
         return grad_input, grad_kernel, None, None, None, None, None, None
 

@@ -43,8 +43,7 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
             raise RuntimeError("in_features and out_features must be multiples of 8 (16-byte TMA rows)")
         input, weight = _operand(input), _operand(weight)
         if plan is None:
-            seed, offset = sd_random.next_seed_offset()
-            plan = BlockPlan.from_seed(M, K, block_size, p, seed, offset, input.device)
+            plan = BlockPlan.draw(M, K, block_size, p, input.device)
         out = dsd(input, weight, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))
         ctx.save_for_backward(input, weight)
         ctx.plan = plan

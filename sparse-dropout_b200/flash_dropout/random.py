@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 
 _state = {"seed": None, "torch_seed": None, "offset": 0, "subsequence": 0}
+_device_counters: dict = {}      # device index -> uint64 CUDA tensor holding the offset counter
 _SUBSEQ_SHIFT = 40
 
 
@@ -55,3 +56,36 @@ def next_seed_offset() -> tuple[int, int]:
     off = _state["offset"]
     _state["offset"] = off + 1
     return seed & (2**64 - 1), (_state["subsequence"] << _SUBSEQ_SHIFT) + off
+
+
+def enable_device_counter(device: torch.device, start: int = 0) -> torch.Tensor:
+    """Keep the mask offset counter in device memory from now on (for this device).
+
+    Each plan launch then reads and increments the counter itself, so the sequence of masks no longer depends
+    on values the host passes at launch time — a captured CUDA graph draws new masks on every replay.
+    """
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = torch.full((1,), int(start), dtype=torch.int64, device=torch.device("cuda", idx))
+    _device_counters[idx] = t
+    return t
+
+
+def disable_device_counter(device: torch.device | None = None) -> None:
+    if device is None:
+        _device_counters.clear()
+    else:
+        _device_counters.pop(device.index if device.index is not None else torch.cuda.current_device(), None)
+
+
+def device_counter(device: torch.device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return _device_counters.get(idx)
+
+
+def seed_and_base() -> tuple[int, int]:
+    """(seed, base offset) for device-counter mode: the subsequence bits only; the counter supplies the rest."""
+    if _state["seed"] is None:
+        seed = torch.initial_seed()
+    else:
+        seed = _state["seed"]
+    return seed & (2**64 - 1), _state["subsequence"] << _SUBSEQ_SHIFT
