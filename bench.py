@@ -490,7 +490,19 @@ def run_train(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    graphed = None
+    if not args.no_graph:
+        from flash_dropout.train import GraphedTrainStep
+        graphed = GraphedTrainStep(model, dp, opt, loss_of, (x_dev, y_dev), autocast_dtype=torch.bfloat16)
+
     def one(resident: bool):
+        if graphed is not None:
+            if not resident:                       # the step's batch arrives from pinned host memory
+                x_dev.copy_(host_x, non_blocking=True)
+                if host_y is not host_x:
+                    y_dev.copy_(host_y, non_blocking=True)
+            loss = graphed()
+            return loss if resident else loss.item()
         if resident:
             x, y = x_dev, y_dev
         else:
@@ -528,7 +540,9 @@ def run_train(args) -> None:
             "ms_per_step": results["value"] / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 autocast (fp32 accumulate, fp32 master weights)", "data": "synthetic",
             "config": {"workload": name, "variant": variant, "parallelism": f"dp{world}",
-                       "step": "zero_grad + fwd + bwd (bucketed NCCL all-reduce overlapped) + optimizer"},
+                       "step": ("CUDA graph replay of zero_grad + fwd + bwd, then flat NCCL all-reduce + optimizer"
+                                if graphed is not None else
+                                "zero_grad + fwd + bwd (bucketed NCCL all-reduce overlapped) + optimizer")},
             "e2e": {"value": per_gpu * world * steps / (results["e2e"] * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": host_x.numel() * host_x.element_size() + (0 if host_y is host_x else host_y.numel() * 8),
                     "d2h_bytes_per_step": 4, "ms_per_step": results["e2e"] / steps},
@@ -549,6 +563,8 @@ def main() -> None:
     ap.add_argument("--workload", choices=("gemm", "mlp", "gpt", "conv"), default="gemm",
                     help="gemm: the headline 4096^3 SparseDrop linear (default); mlp / gpt: one training step")
     ap.add_argument("--variant", default="blockwise[cuda]", help="DropoutMM variant for the training workloads")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="training workloads: launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the p=0 comparison and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
@@ -562,6 +578,8 @@ def main() -> None:
                "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__),
                "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup)]
         cmd += ["--workload", args.workload, "--variant", args.variant]
+        if args.no_graph:
+            cmd.append("--no-graph")
         if args.no_extras:
             cmd.append("--no-extras")
         raise SystemExit(subprocess.call(cmd))

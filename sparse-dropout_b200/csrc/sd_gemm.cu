@@ -835,7 +835,10 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
                         tiles_upper, max_ctas);
         if (grid > max_ctas) grid = max_ctas;
     }
-    if (workspace && tiles_upper < grid && units_upper > tiles_upper) {
+    // Cutting tiles pays only when each tile is long: the partial-tile exchange costs about as much as a dozen
+    // K tiles, so short reductions keep whole tiles even on an under-filled grid.
+    const int k_tiles = (K + 127) / 128;
+    if (workspace && tiles_upper * 2 <= grid && k_tiles >= 16) {
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(SD_ERR_LAYOUT, "workspace must be 16-byte aligned");
         if (grid > WS_MAX_CTAS) grid = WS_MAX_CTAS;
         if (units_upper < grid) grid = int(units_upper);

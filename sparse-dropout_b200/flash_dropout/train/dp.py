@@ -74,7 +74,11 @@ class FlatGradDataParallel:
         sd_random.set_subsequence(self.rank)     # every rank draws its own masks from the shared seed
 
     # ------------------------------------------------------------------
+    defer_allreduce = False     # set by GraphedTrainStep: no per-bucket collectives from the hooks
+
     def _on_grad_ready(self, p: torch.Tensor) -> None:
+        if self.defer_allreduce:
+            return
         b = self._bucket_of[p]
         self._pending[b] -= 1
         if self._pending[b] == 0:
@@ -122,3 +126,63 @@ def train_step(model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torc
     dp.finish()
     optimizer.step()
     return loss.detach()
+
+
+class GraphedTrainStep:
+    """zero_grad + forward + backward captured once in a CUDA graph and replayed every step.
+
+    The training steps BASELINE names are made of dozens of small launches (a plan kernel and three GEMMs per
+    DropoutMM, plus the model's other ops); eagerly they are bound by host launch overhead, which is what the
+    reference's report identifies as the limit for small layers (report.pdf section 3.4).  Replaying a graph
+    removes that.  Masks stay fresh because the plan kernel takes its Philox offset from a counter in device
+    memory that each launch increments (``flash_dropout.random.enable_device_counter``).
+
+    The gradient all-reduce (one flat buffer) and the optimizer step run eagerly after the replay: two or three
+    launches, and NCCL stays outside the capture.  ``inputs`` are static device tensors: copy each batch into
+    them before calling the step.
+    """
+
+    def __init__(self, model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torch.optim.Optimizer, loss_fn,
+                 inputs: tuple, autocast_dtype: torch.dtype | None = None, warmup: int = 3):
+        self.model, self.dp, self.optimizer = model, dp, optimizer
+        self.inputs = inputs
+        dev = dp.flat_grad.device
+        if dev.type != "cuda":
+            raise RuntimeError("GraphedTrainStep needs CUDA")
+        if sd_random.device_counter(dev) is None:
+            sd_random.enable_device_counter(dev)
+        self._hooks_enabled = False
+
+        def fwd_bwd():
+            dp.flat_grad.zero_()
+            if autocast_dtype is not None:
+                with torch.autocast("cuda", dtype=autocast_dtype):
+                    loss = loss_fn(model, *inputs)
+            else:
+                loss = loss_fn(model, *inputs)
+            loss.backward()
+            return loss.detach()
+
+        dp.defer_allreduce = True                      # bucket hooks stay quiet: one flat all-reduce after replay
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):                    # allocations, autotuning and lazy init happen here
+                fwd_bwd()
+                self._finish()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.loss = fwd_bwd()
+
+    def _finish(self) -> None:
+        if self.dp.world > 1:
+            dist.all_reduce(self.dp.flat_grad, op=dist.ReduceOp.SUM, group=self.dp.group)
+            self.dp.flat_grad.div_(self.dp.world)
+        self.optimizer.step()
+
+    def __call__(self) -> torch.Tensor:
+        self.graph.replay()
+        self._finish()
+        return self.loss

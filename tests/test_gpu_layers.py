@@ -134,3 +134,29 @@ def test_training_step_consumers(built_lib, kind):
     assert eval_loss() < before                              # it learns the fixed batch
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
     sd_random.follow_torch_seed()
+
+
+def test_graphed_train_step_draws_fresh_masks(built_lib):
+    """The captured step replays with new masks (device-side offset counter) and keeps learning."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.train import BasicNet, FlatGradDataParallel, GraphedTrainStep
+    torch.manual_seed(0)
+    sd_random.manual_seed(11, subsequence=0)
+    model = BasicNet(784, 2, 1024, 10, dict(p=0.5, variant="blockwise[cuda]", block_size=128)).to(DEV)
+    x, y = torch.rand(512, 28, 28, device=DEV), torch.randint(0, 10, (512,), device=DEV)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True)
+    dp = FlatGradDataParallel(model)
+    step = GraphedTrainStep(model, dp, opt, lambda m, a, b: torch.nn.functional.cross_entropy(m(a).float(), b),
+                            (x, y), autocast_dtype=torch.bfloat16)
+    counter = sd_random.device_counter(DEV)
+    c0 = counter.item()
+    losses = [step().item() for _ in range(20)]
+    assert counter.item() == c0 + 20 * 4                      # four DropoutMM layers, one mask each per replay
+    assert len(set(losses)) > 10 and all(np.isfinite(losses))
+    assert dp.grads_are_views()
+    model.eval()
+    with torch.no_grad():
+        final = torch.nn.functional.cross_entropy(model(x).float(), y).item()
+    assert final < 2.30
+    sd_random.disable_device_counter()
+    sd_random.follow_torch_seed()

@@ -96,3 +96,16 @@ def test_functional_mask_uses_device_draw(built_lib):
     assert np.array_equal(m0.cpu().numpy(), pm.block_mask(1024, 2048, 128, 0.5, 42, 0))
     assert np.array_equal(m1.cpu().numpy(), pm.block_mask(1024, 2048, 128, 0.5, 42, 1))
     sd_random.follow_torch_seed()
+
+
+def test_device_counter_supplies_the_offset(built_lib):
+    """Offset = base + counter read on the device; each launch increments the counter (CUDA-graph friendly)."""
+    from flash_dropout.cuda.binding_gemm import BlockPlan
+    dev = torch.device("cuda:0")
+    counter = torch.full((1,), 5, dtype=torch.int64, device=dev)
+    base = 3 << 40
+    for i in range(3):
+        plan = BlockPlan.from_device_counter(1024, 2048, 128, 0.5, 77, base, counter, dev)
+        torch.cuda.synchronize()
+        assert counter.item() == 6 + i
+        assert np.array_equal(plan.mask.cpu().numpy(), pm.block_mask(1024, 2048, 128, 0.5, 77, base + 5 + i))
