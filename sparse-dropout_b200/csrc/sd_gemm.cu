@@ -22,26 +22,23 @@
 // (row|col)-major x (row|col)-major operand matrix of flash_dropout/cuda/src/gemm_binding.cu:51-53.
 //
 // Scheduling.  With several output tiles per SM, whole tiles are dealt round-robin from a list sorted
-// heaviest row block first.  With fewer tiles than SMs (small layers, or the dW product of a conv whose
-// reduction runs over hundreds of thousands of rows) the unit of work becomes one kept 128-wide K tile of
-// one output tile: all units of the launch form one sequence (tiles in row-block order, kept K tiles
-// ascending) that is cut into gridDim.x equal contiguous ranges, one per CTA, so every SM gets the same
-// number of MMA steps.  A range may then begin or end inside an output tile:
-//   * the CTA that owns the first unit of a tile is its finisher and writes the result;
-//   * a CTA that starts in the middle of a tile computes its part first thing, stores the fp32
-//     partial accumulator in its own workspace slot and raises its flag;
-//   * the finisher (for which that tile is the last thing it does) waits, bounded, for the flags
-//     two segments ahead of time, adds the partials in CTA order (deterministic) straight into the
-//     TMEM accumulator the tile will use (tcgen05.st) and clears the flags; its MMAs then
-//     accumulate on top, so the tile ends with an ordinary epilogue and the fix-up is hidden
-//     behind the main loop of the segment in between.
-// The second schedule needs the caller's workspace; without one, whole tiles are used throughout.
+// heaviest row block first.  With fewer tiles than SMs and a long reduction (the dW product of a layer fed
+// thousands of rows, or of a conv whose reduction runs over all N*P*Q pixels) the unit of work becomes one
+// kept 128-wide K tile of one output tile: all units of the launch form one sequence (tiles in row-block
+// order, kept K tiles ascending) that is cut into equal contiguous ranges, one per CTA, so every SM gets the
+// same number of MMA steps.  A range may then begin or end inside an output tile.  Every CTA that computed
+// only part of a tile parks its fp32 accumulator in the workspace (slot 0: the tile its range starts inside,
+// slot 1: the tile its range ends inside) and counts itself in; after its last segment it waits, bounded, for
+// the tile's other CTAs and then adds up ITS share of the tile's 32x32 units over all parked accumulators, in
+// CTA order (so results do not depend on timing), and stores them.  The CTA that finishes last clears the
+// counters.  This needs the caller's workspace; without one, whole tiles are used throughout.
 //
 // Every wait is bounded (sd_ptx.cuh: mbar_wait); on expiry the CTA records a code in the status
 // word, every role leaves its loop, TMEM is freed and the kernel returns normally.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "sd_common.h"
@@ -64,9 +61,9 @@ constexpr int TMEM_COLS = 512;
 
 // Workspace of the split schedule: flags first, then one fp32 partial tile per CTA.
 constexpr int WS_MAX_CTAS = 1024;
-constexpr size_t WS_FLAG_BYTES = WS_MAX_CTAS * sizeof(int);
+constexpr size_t WS_FLAG_BYTES = 2 * WS_MAX_CTAS * sizeof(int);   // arrive[] then done[], indexed by the tile owner's CTA
 constexpr size_t WS_SLOT_FLOATS = size_t(BM) * BN;
-constexpr size_t WS_SLOT_BYTES = WS_SLOT_FLOATS * sizeof(float);   // 128 KiB
+constexpr size_t WS_SLOT_BYTES = WS_SLOT_FLOATS * sizeof(float);   // 128 KiB; two slots per CTA
 
 enum GemmMode { MODE_DENSE = 0, MODE_DSD = 1, MODE_SDD = 2 };
 enum StatusCode { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_ACC = 3, ST_EPILOGUE = 4, ST_FIXUP = 5 };
@@ -112,6 +109,7 @@ struct WorkIter {
     int t, n_tiles, stride;      // whole tiles: next tile, tile count, gridDim.x
     int nk_uniform;              // dense / SDD: K tiles per output tile
     int rb, nt, i0;              // split position: row block (SDD: work item), n tile, offset inside the tile
+    int n_eff;                   // split: number of CTAs that have a range
     bool split;
 
     __device__ __forceinline__ static long long range_start(long long total, int cta, int n_ctas) {
@@ -141,12 +139,15 @@ struct WorkIter {
         stride = n_ctas;
         u = u_end = total = 0;
         rb = nt = i0 = 0;
+        n_eff = n_ctas;
         if (!split) return;
         if (g.mode == MODE_DSD) total = (long long)g.n_col_tiles * __ldg(g.list_ptr + g.n_row_blocks);
         else total = (long long)n_tiles * nk_uniform;
-        u = range_start(total, cta, n_ctas);
-        u_end = range_start(total, cta + 1, n_ctas);
-        if (u >= u_end) return;
+        // never more ranges than units, so no range is empty: the CTAs of a shared tile are then simply consecutive
+        n_eff = total < n_ctas ? int(total) : n_ctas;
+        if (cta >= n_eff) return;
+        u = range_start(total, cta, n_eff);
+        u_end = range_start(total, cta + 1, n_eff);
         if (g.mode == MODE_DSD) {
             const int v = int(u / g.n_col_tiles);
             int lo = 0, hi = g.n_row_blocks - 1;   // first row block with list_ptr[r + 1] > v
@@ -342,34 +343,6 @@ __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_f
     }
 }
 
-// r[0..32) += chunk `c` (32 columns) of row `etid` of the partial tiles parked by CTAs [first, last] (those with a
-// non-empty range), added in CTA order.  Two partial tiles are fetched per round trip to L2.
-__device__ __forceinline__ void add_partials(const GemmArgs& g, uint32_t (&r)[32], int first, int last, int c, int etid,
-                                             long long total, int n_ctas) {
-    const float* slot0 = g.ws_slots + size_t(c * 32) * BM + etid;
-    int pc = first;
-    while (pc <= last) {
-        int a = -1, b = -1;
-        for (; pc <= last && a < 0; ++pc)
-            if (WorkIter::range_start(total, pc + 1, n_ctas) > WorkIter::range_start(total, pc, n_ctas)) a = pc;
-        for (; pc <= last && b < 0; ++pc)
-            if (WorkIter::range_start(total, pc + 1, n_ctas) > WorkIter::range_start(total, pc, n_ctas)) b = pc;
-        if (a < 0) break;
-        const float* sa = slot0 + size_t(a) * WS_SLOT_FLOATS;
-        if (b >= 0) {
-            const float* sb = slot0 + size_t(b) * WS_SLOT_FLOATS;
-            float ta[32], tb[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) { ta[j] = __ldcg(sa + j * BM); tb[j] = __ldcg(sb + j * BM); }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint((__uint_as_float(r[j]) + ta[j]) + tb[j]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(sa + j * BM));
-        }
-    }
-}
-
 #ifdef SD_TIMING
 // Development aid (not compiled into the product): per-CTA timestamps of one launch.
 __device__ unsigned long long sd_timing[1024][8];
@@ -381,6 +354,113 @@ __device__ unsigned long long sd_timing[1024][8];
 #define SD_STAMP(slot) do {} while (0)
 #endif
 
+// ------------------------------------------------------------------ shared tiles of the equal-share schedule
+// CTA whose unit range [range_start(c), range_start(c + 1)) contains unit `first`.
+__device__ __forceinline__ int tile_owner(long long total, long long first, int n_ctas) {
+    int c = int(first * n_ctas / total);
+    if (c >= n_ctas) c = n_ctas - 1;
+    while (c + 1 < n_ctas && WorkIter::range_start(total, c + 1, n_ctas) <= first) ++c;
+    while (c > 0 && WorkIter::range_start(total, c, n_ctas) > first) --c;
+    return c;
+}
+
+// Bounded wait until a counter another CTA increments reaches `target`.
+__device__ __forceinline__ bool counter_wait(const int* counter, int target, volatile int* abort_flag, int* status, int code) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= target) return true;
+        if ((it & 0xff) == 0xff) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// All CTAs whose ranges intersect one output tile have parked their partial accumulators (the owner of the tile's
+// first unit in its slot 1, the others in their slot 0) and counted themselves in arrive[owner].  Once the count is
+// complete, every participant adds up a different share of the tile's 32x32 units over all partials, in CTA order
+// (so the result does not depend on timing), scales, converts and stores it.  The last participant to finish clears
+// the two counters, which leaves the workspace ready for the next launch.
+__device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, long long total, int cta, int n_ctas, int etid,
+                                   volatile int* abort_flag) {
+    const int owner = tile_owner(total, seg.tile_end - seg.nk, n_ctas);
+    const int last = tile_owner(total, seg.tile_end - 1, n_ctas);
+    const int P = last - owner + 1, my_index = cta - owner;
+    int* arrive = g.ws_flags + owner;
+    int* done = g.ws_flags + WS_MAX_CTAS + owner;
+    bool ok = true;
+    if (etid == 0) ok = counter_wait(arrive, P, abort_flag, g.status, ST_FIXUP);
+    if (!epilogue_all(ok)) return false;
+#ifdef SD_TIMING
+    if (etid == 0) SD_STAMP(5);
+#endif
+    const int n_units = (seg.b_row1 >= 0 ? 8 : 4) * 4;
+    unsigned short* C = static_cast<unsigned short*>(g.C);
+    const bool quad_ok = g.c_cs == 1 && (g.c_rs & 3) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 7) == 0;
+    // A unit is 8 four-column pieces x 32 rows of 16 bytes.  All 128 threads share each unit (two pieces per thread) and keep the
+    // loads of four partial tiles in flight at once, so the depth of the dependent chain is P / 4 round trips.
+    for (int uu = my_index; uu < n_units; uu += P) {
+        const int c = uu >> 2, q = uu & 3;
+        float4 acc2[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+        const size_t unit_off = size_t(uu) * 1024 + size_t(etid) * 4;
+        int pc = owner;
+        while (pc <= last) {
+            const float4* src[4];
+            int n = 0;
+            for (; pc <= last && n < 4; ++pc)
+                src[n++] = reinterpret_cast<const float4*>(
+                    g.ws_slots + (size_t(2 * pc) + (pc == owner ? 1 : 0)) * WS_SLOT_FLOATS + unit_off);
+            float4 v[4][2];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (i < n) { v[i][0] = __ldcg(src[i]); v[i][1] = __ldcg(src[i] + 128); }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (i < n) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        acc2[h].x += v[i][h].x; acc2[h].y += v[i][h].y; acc2[h].z += v[i][h].z; acc2[h].w += v[i][h].w;
+                    }
+                }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int e = etid + 128 * h;                        // piece index inside the unit: [4-column piece][row]
+            const int row = seg.a_row + q * 32 + (e & 31);
+            const int col = (c < 4 ? seg.b_row0 + c * 32 : seg.b_row1 + (c - 4) * 32) + (e >> 5) * 4;
+            if (row >= g.MM || col >= g.NN) continue;
+            const float f[4] = {acc2[h].x * g.scale, acc2[h].y * g.scale, acc2[h].z * g.scale, acc2[h].w * g.scale};
+            if (quad_ok && col + 4 <= g.NN) {
+                uint2 o;
+                o.x = pack2(f[0], f[1], g.is_bf16);
+                o.y = pack2(f[2], f[3], g.is_bf16);
+                *reinterpret_cast<uint2*>(C + (long long)row * g.c_rs + col) = o;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (col + j < g.NN) C[(long long)row * g.c_rs + (long long)(col + j) * g.c_cs] = cvt1(f[j], g.is_bf16);
+            }
+        }
+    }
+    epilogue_sync();                                             // every thread has read its share
+    if (etid == 0) {
+        __threadfence();
+        if (atomicAdd(done, 1) == P - 1) {
+            flag_set(arrive, 0);
+            flag_set(done, 0);
+        }
+    }
+    return true;
+}
+
 // ------------------------------------------------------------------ the kernel
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -391,10 +471,9 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     const uint32_t tiles = (raw_addr + 1023u) & ~1023u;   // 128B swizzle atoms need 1024-byte alignment
     uint8_t* aligned = smem_raw + (tiles - raw_addr);
     uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + TILE_SMEM);
-    // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty, [12] preload
+    // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty, [12] unused
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
-    const uint32_t bar_preload = bar_tempty + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
     unsigned short* xpose = reinterpret_cast<unsigned short*>(aligned + TILE_SMEM + 256);
@@ -410,7 +489,6 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             mbar_init(bar_tfull + 8 * a, 1);
             mbar_init(bar_tempty + 8 * a, 4);
         }
-        mbar_init(bar_preload, 4);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmapA);
@@ -490,11 +568,6 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             for (int seg = 0; ok && it.next(g, w); ++seg) {
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, g.status, ST_MMA_ACC)) break;
                 uint32_t accumulate = 0;
-                if (seg > 0 && w.i0 == 0 && w.i1 < w.nk) {
-                    // finisher: the other CTAs' partial sums are placed in this accumulator first
-                    if (!mbar_wait(bar_preload, 0, abort_flag, g.status, ST_FIXUP)) break;
-                    accumulate = 1;
-                }
                 tc_fence_after();
                 const uint32_t d = tmem_base + acc * BN;
                 const uint32_t idesc = w.b_row1 >= 0 ? g.idesc256 : g.idesc128;
@@ -546,67 +619,25 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         }
         WorkIter it;
         it.init(g, cta, n_ctas);
-        // Which of this CTA's segments (if any) is the head of a tile that other CTAs finish computing?
-        int fin_idx = -1, fin_chunks = 0;
-        long long fin_tile_end = 0;
-        {
-            WorkIter scan = it;
-            Seg s;
-            for (int n = 0; scan.next(g, s); ++n)
-                if (s.i0 == 0 && s.i1 < s.nk) { fin_idx = n; fin_chunks = s.b_row1 >= 0 ? 8 : 4; fin_tile_end = s.tile_end; }
-        }
-        // Contributors of the finisher tile: CTAs (cta, fin_last] with a non-empty range.
-        int fin_last = cta;
-        if (fin_idx >= 0)
-            for (int c = cta + 1; c < n_ctas && WorkIter::range_start(it.total, c, n_ctas) < fin_tile_end; ++c) fin_last = c;
-        auto contributes = [&](int c) {
-            return WorkIter::range_start(it.total, c + 1, n_ctas) > WorkIter::range_start(it.total, c, n_ctas);
-        };
-        // Adds the partial tiles of the contributing CTAs into TMEM buffer (fin_idx & 1).
-        auto preload = [&]() -> bool {
-            const int last_c = fin_last;
-            bool ok = true;
-            if (etid == 0)
-                for (int c = cta + 1; ok && c <= last_c; ++c)
-                    if (contributes(c)) ok = flag_wait(g.ws_flags + c, abort_flag, g.status, ST_FIXUP);
-            if (!epilogue_all(ok)) return false;
-            const uint32_t taddr = tmem_base + (fin_idx & 1) * BN + (uint32_t(quad * 32) << 16);
-            for (int c = 0; c < fin_chunks; ++c) {
-                uint32_t r[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = 0;
-                add_partials(g, r, cta + 1, last_c, c, etid, it.total, n_ctas);
-                tmem_st_32x32(taddr + c * 32, r);
-            }
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_preload);
-            epilogue_sync();                                     // every thread has read the partials
-            if (etid == 0)
-                for (int c = cta + 1; c <= last_c; ++c) flag_set(g.ws_flags + c, 0);
-            return true;
-        };
-        bool alive = true;
         int acc = 0;
         uint32_t acc_phase = 0;
         Seg w;
-        float* my_slot = g.split ? g.ws_slots + size_t(cta) * WS_SLOT_FLOATS : nullptr;
-        for (int seg = 0; alive && it.next(g, w); ++seg) {
-            const bool partial = w.i0 > 0;                       // goes to this CTA's workspace slot
-            // When the finisher tile is this CTA's very first segment there is no earlier main loop to hide a
-            // preload behind; its own MMAs run at once and the partials are added here instead.
-            const bool late_fix = seg == 0 && fin_idx == 0;
-            bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
-            if (late_fix && etid == 0)
-                for (int c = cta + 1; ok && c <= fin_last; ++c)
-                    if (contributes(c)) ok = flag_wait(g.ws_flags + c, abort_flag, g.status, ST_FIXUP);
-            if (!epilogue_all(ok)) break;                        // uniform decision of the 128 epilogue threads
+        // Tiles this CTA shares with others: at most the one its range starts inside (slot 0) and the one its range
+        // ends inside (slot 1).  Their partial accumulators are reduced after the segment loop.
+        Seg shared[2];
+        int n_shared = 0;
+        bool alive = true;
+        while (alive && it.next(g, w)) {
+            const bool partial = w.i0 > 0 || w.i1 < w.nk;
+            const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
+            if (!epilogue_all(ok)) { alive = false; break; }     // uniform decision of the 128 epilogue threads
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
             const int row = w.a_row + etid;
             const int nchunks = w.b_row1 >= 0 ? 8 : 4;
             const bool transposed = !partial && vec_t_ok && w.a_row + 128 <= g.MM;
+            float* slot = nullptr;
+            if (partial) slot = g.ws_slots + (size_t(2 * cta) + (w.i0 > 0 ? 0 : 1)) * WS_SLOT_FLOATS;
             // chunk c+1 is in flight from TMEM while chunk c is converted and stored
             uint32_t rbuf[2][32];
             tmem_ld_32x32(taddr, rbuf[0]);
@@ -616,11 +647,12 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 uint32_t (&r)[32] = rbuf[c & 1];
                 if (c + 1 < nchunks) tmem_ld_32x32(taddr + (c + 1) * 32, rbuf[(c + 1) & 1]);
                 const int col = c < 4 ? w.b_row0 + c * 32 : w.b_row1 + (c - 4) * 32;
-                if (late_fix) add_partials(g, r, cta + 1, fin_last, c, etid, it.total, n_ctas);
                 if (partial) {
-                    float* dst = my_slot + size_t(c * 32) * BM + etid;
+                    // unit (chunk c, quadrant) = 32 rows x 32 fp32 columns stored as [4-column piece][row]: each warp
+                    // store instruction writes 512 contiguous bytes
+                    uint4* dst = reinterpret_cast<uint4*>(slot + size_t(c * 4 + quad) * 1024) + lane;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) __stcg(dst + j * BM, __uint_as_float(r[j]));
+                    for (int v = 0; v < 8; ++v) __stcg(dst + v * 32, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
                 } else if (transposed) {
                     store_chunk_transposed(g, xpose + (c & 1) * (XPOSE_BYTES / 2), etid, w.a_row, col, r);
                 } else {
@@ -631,20 +663,20 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-            if (partial) {
-                __threadfence();                                 // partial tile visible before the flag
-                epilogue_sync();
-                if (etid == 0) flag_set(g.ws_flags + cta, 1);
-            } else if (late_fix) {
-                epilogue_sync();                                 // every thread has read the partials
-                if (etid == 0)
-                    for (int c = cta + 1; c <= fin_last; ++c) flag_set(g.ws_flags + c, 0);
-            }
-            // as late as possible: the accumulator just drained (or the still unused second one) is the finisher's
-            if (fin_idx == seg + 2 || (fin_idx == 1 && seg == 0)) alive = preload();
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
+            if (partial) {
+                __threadfence();                                 // partial tile visible before the arrival count
+                epilogue_sync();
+                if (etid == 0) atomicAdd(g.ws_flags + tile_owner(it.total, w.tile_end - w.nk, it.n_eff), 1);
+                shared[n_shared++] = w;
+            }
         }
+#ifdef SD_TIMING
+        if (etid == 0) SD_STAMP(4);
+#endif
+        for (int t = 0; alive && t < n_shared; ++t)
+            alive = reduce_shared_tile(g, shared[t], it.total, cta, it.n_eff, etid, abort_flag);
 #ifdef SD_TIMING
         if (etid == 0) { SD_STAMP(3); sd_timing[blockIdx.x][7] = clock64(); }
 #endif
@@ -838,7 +870,11 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     // Cutting tiles pays only when each tile is long: the partial-tile exchange costs about as much as a dozen
     // K tiles, so short reductions keep whole tiles even on an under-filled grid.
     const int k_tiles = (K + 127) / 128;
-    if (workspace && tiles_upper * 2 <= grid && k_tiles >= 16) {
+    static const int split_min_k_tiles = [] {
+        const char* e = getenv("SD_SPLIT_MIN_KTILES");   // tuning knob: minimum reduction length (in 128-wide K tiles)
+        return e ? atoi(e) : 16;
+    }();
+    if (workspace && tiles_upper * 2 <= grid && k_tiles >= split_min_k_tiles) {
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(SD_ERR_LAYOUT, "workspace must be 16-byte aligned");
         if (grid > WS_MAX_CTAS) grid = WS_MAX_CTAS;
         if (units_upper < grid) grid = int(units_upper);
@@ -856,11 +892,11 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
 }
 
 // ------------------------------------------------------------------ built-in scratch
-// Scratch of sd_gemm_dsd_static_scratch(): the same layout as a caller's workspace (flags, then one fp32
-// partial tile per CTA) for at most kStaticScratchSlots CTAs: 4 KiB + 64 x 128 KiB = 8 196 KiB of device
+// Scratch of sd_gemm_dsd_static_scratch(): the same layout as a caller's workspace (counters, then two fp32
+// partial tiles per CTA) for at most kStaticScratchSlots CTAs: 8 KiB + 2 x 64 x 128 KiB = 16 392 KiB of device
 // memory that every GPU which loads this library holds until the process exits.
 constexpr int kStaticScratchSlots = 64;
-static __device__ __align__(256) unsigned char sd_static_scratch[WS_FLAG_BYTES + kStaticScratchSlots * WS_SLOT_BYTES];
+static __device__ __align__(256) unsigned char sd_static_scratch[WS_FLAG_BYTES + 2 * kStaticScratchSlots * WS_SLOT_BYTES];
 
 // Device address of the array on the current device.  In host code the array's name is only a stand-in for
 // the symbol, not a device pointer: the address has to be asked for, once per device, with that device current.
@@ -918,7 +954,7 @@ size_t sd_workspace_bytes(void) {
     int sms = 0;
     if (sd::sm_count_current_device(&sms) != SD_OK) return 0;
     if (sms > sd::WS_MAX_CTAS) sms = sd::WS_MAX_CTAS;
-    return sd::WS_FLAG_BYTES + size_t(sms) * sd::WS_SLOT_BYTES;
+    return sd::WS_FLAG_BYTES + 2 * size_t(sms) * sd::WS_SLOT_BYTES;
 }
 
 int sd_workspace_init(void* workspace, void* stream) {
