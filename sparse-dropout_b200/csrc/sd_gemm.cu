@@ -86,6 +86,7 @@ struct GemmArgs {
     int* status;
     uint32_t idesc256, idesc128;
     int split;                       // 1: equal unit ranges with fix-up (needs the workspace); 0: whole tiles
+    int tma_store;                   // result written by TMA from a swizzled staging buffer: 1 row-major, 2 column-major
     float* ws_slots;
     int* ws_flags;
 };
@@ -465,18 +466,18 @@ __device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, long long 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
-                       const GemmArgs g) {
+                       const __grid_constant__ CUtensorMap tmapC, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t tiles = (raw_addr + 1023u) & ~1023u;   // 128B swizzle atoms need 1024-byte alignment
     uint8_t* aligned = smem_raw + (tiles - raw_addr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + TILE_SMEM);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + TILE_SMEM + 2 * XPOSE_BYTES);
     // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty, [12] unused
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
-    unsigned short* xpose = reinterpret_cast<unsigned short*>(aligned + TILE_SMEM + 256);
+    unsigned short* xpose = reinterpret_cast<unsigned short*>(aligned + TILE_SMEM);   // 16 KiB epilogue staging, 1024-aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -493,6 +494,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         fence_mbar_init();
         tma_prefetch_desc(&tmapA);
         tma_prefetch_desc(&tmapB);
+        if (g.tma_store) tma_prefetch_desc(&tmapC);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -626,6 +628,8 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         // ends inside (slot 1).  Their partial accumulators are reduced after the segment loop.
         Seg shared[2];
         int n_shared = 0;
+        const uint32_t stage_base = smem_u32(xpose) + (uint32_t(quad) << 12);   // two 2 KiB buffers per epilogue warp
+        int n_stores = 0;
         bool alive = true;
         while (alive && it.next(g, w)) {
             const bool partial = w.i0 > 0 || w.i1 < w.nk;
@@ -653,6 +657,54 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                     uint4* dst = reinterpret_cast<uint4*>(slot + size_t(c * 4 + quad) * 1024) + lane;
 #pragma unroll
                     for (int v = 0; v < 8; ++v) __stcg(dst + v * 32, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
+                } else if (g.tma_store == 1) {
+                    // this warp's 32 rows x 32 columns go to its own 2 KiB staging buffer (64-byte rows, 16-byte pieces
+                    // XOR-swizzled as CU_TENSOR_MAP_SWIZZLE_64B expects) and from there to global memory by one TMA store
+                    const uint32_t buf = stage_base + ((n_stores & 1) << 11);
+                    if (n_stores >= 2) {
+                        if (lane == 0) bulk_wait_read<1>();      // the store that last used this buffer has read it
+                        __syncwarp();
+                    }
+                    const uint32_t rowaddr = buf + lane * 64, sw = (lane >> 1) & 3;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const uint32_t p0 = pack2(__uint_as_float(r[8 * v + 0]) * g.scale, __uint_as_float(r[8 * v + 1]) * g.scale, g.is_bf16);
+                        const uint32_t p1 = pack2(__uint_as_float(r[8 * v + 2]) * g.scale, __uint_as_float(r[8 * v + 3]) * g.scale, g.is_bf16);
+                        const uint32_t p2 = pack2(__uint_as_float(r[8 * v + 4]) * g.scale, __uint_as_float(r[8 * v + 5]) * g.scale, g.is_bf16);
+                        const uint32_t p3 = pack2(__uint_as_float(r[8 * v + 6]) * g.scale, __uint_as_float(r[8 * v + 7]) * g.scale, g.is_bf16);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((v ^ sw) << 4)), "r"(p0), "r"(p1),
+                                     "r"(p2), "r"(p3)
+                                     : "memory");
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmapC, buf, col, w.a_row + quad * 32);
+                        bulk_commit();
+                    }
+                    ++n_stores;
+                } else if (g.tma_store == 2) {
+                    // column-major result = row-major transpose: the warp's 32 rows x 32 columns are staged as
+                    // [column][row] (64-byte rows of the transpose, same swizzle) and stored by one TMA store
+                    const uint32_t buf = stage_base + ((n_stores & 1) << 11);
+                    if (n_stores >= 2) {
+                        if (lane == 0) bulk_wait_read<1>();
+                        __syncwarp();
+                    }
+                    const uint32_t lane_off = ((lane & 7) << 1), chunk = lane >> 3;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t addr = buf + j * 64 + (((chunk ^ ((j >> 1) & 3))) << 4) + lane_off;
+                        asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(cvt1(__uint_as_float(r[j]) * g.scale, g.is_bf16))
+                                     : "memory");
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmapC, buf, w.a_row + quad * 32, col);
+                        bulk_commit();
+                    }
+                    ++n_stores;
                 } else if (transposed) {
                     store_chunk_transposed(g, xpose + (c & 1) * (XPOSE_BYTES / 2), etid, w.a_row, col, r);
                 } else {
@@ -675,6 +727,8 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
 #ifdef SD_TIMING
         if (etid == 0) SD_STAMP(4);
 #endif
+        if (g.tma_store && lane == 0) bulk_wait_all();           // staged results are in global memory
+        __syncwarp();
         for (int t = 0; alive && t < n_shared; ++t)
             alive = reduce_shared_tile(g, shared[t], it.total, cta, it.n_eff, etid, abort_flag);
 #ifdef SD_TIMING
@@ -769,7 +823,8 @@ static int make_operand_map(CUtensorMap* out, bool* mn_major, const char* name, 
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int grid, cudaStream_t st) {
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& g, int grid,
+                          cudaStream_t st) {
     static bool configured[64] = {};
     int dev = 0;
     SD_CUDA_TRY(cudaGetDevice(&dev));
@@ -781,7 +836,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
         SD_CUDA_TRY(cudaFuncSetAttribute(sparsedrop_gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GEMM_SMEM));
     }
-    sparsedrop_gemm_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ta, tb, g);
+    sparsedrop_gemm_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ta, tb, tc, g);
     SD_CUDA_TRY(cudaGetLastError());
     return SD_OK;
 }
@@ -885,10 +940,35 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         grid = int(tiles_upper);
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (!a_mn && !b_mn) return launch_variant<false, false>(ta, tb, g, grid, st);
-    if (!a_mn && b_mn) return launch_variant<false, true>(ta, tb, g, grid, st);
-    if (a_mn && !b_mn) return launch_variant<true, false>(ta, tb, g, grid, st);
-    return launch_variant<true, true>(ta, tb, g, grid, st);
+    // Row-major result with 16-byte rows: written by TMA (clipped at the ragged edge); otherwise by the warps.
+    CUtensorMap tc = ta;
+    if (c_cs == 1 && (c_rs & 7) == 0 && c_rs >= N && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+        EncodeTiledFn enc = encode_tiled_fn();
+        cuuint64_t dims[2] = {cuuint64_t(N), cuuint64_t(M)};
+        cuuint64_t strides[1] = {cuuint64_t(M > 1 ? c_rs * 2 : ((int64_t(N) * 2 + 15) & ~int64_t(15)))};
+        cuuint32_t box[2] = {32u, 32u};
+        cuuint32_t estr[2] = {1u, 1u};
+        CUresult r = enc(&tc, dtype == SD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C,
+                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", int(r));
+        g.tma_store = 1;
+    } else if (c_rs == 1 && (c_cs & 7) == 0 && c_cs >= M && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+        EncodeTiledFn enc = encode_tiled_fn();
+        cuuint64_t dims[2] = {cuuint64_t(M), cuuint64_t(N)};            // the transpose, row-major [N][M]
+        cuuint64_t strides[1] = {cuuint64_t(N > 1 ? c_cs * 2 : ((int64_t(M) * 2 + 15) & ~int64_t(15)))};
+        cuuint32_t box[2] = {32u, 32u};
+        cuuint32_t estr[2] = {1u, 1u};
+        CUresult r = enc(&tc, dtype == SD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C,
+                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled(C^T) failed with CUresult %d", int(r));
+        g.tma_store = 2;
+    }
+    if (!a_mn && !b_mn) return launch_variant<false, false>(ta, tb, tc, g, grid, st);
+    if (!a_mn && b_mn) return launch_variant<false, true>(ta, tb, tc, g, grid, st);
+    if (a_mn && !b_mn) return launch_variant<true, false>(ta, tb, tc, g, grid, st);
+    return launch_variant<true, true>(ta, tb, tc, g, grid, st);
 }
 
 // ------------------------------------------------------------------ built-in scratch
