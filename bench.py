@@ -58,7 +58,7 @@ def measured_peaks() -> tuple[float, str]:
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index, self.period, self.samples, self._stop = index, period_s, [], threading.Event()
         self._thread = None
         self.max_mhz = None
