@@ -41,9 +41,9 @@ N_SETS = 4
 METRIC = "DSD/SDD useful TFLOP/s (DSD fwd + SDD dX + DSD dW on kept 128x128 blocks) at 4096^3 fp16, p=0.5"
 WORKLOAD = ("BASELINE configs[1]: SparseDrop linear fwd+bwd, M=N=K=4096, fp16 in / fp32 acc, 128x128 blocks, "
             "p=0.5, x,W,dy~N(0,K^-1/2), per-step Philox mask (seed 0, offset=step)")
-# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch at this workload, from the ncu capture
-# summarised in profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch at this workload (mean of the step's three launches:
+# 62.4 / 89.5 / 61.5 MB), from the ncu capture summarised in profiles/gemm_kernel_4096_p05.md.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 71.1e6
 
 
 def measured_peaks() -> tuple[float, str]:
