@@ -79,6 +79,8 @@ struct GemmArgs {
     const int* list_ptr;             // DSD: kept K-tile list of row block rb = list_idx[list_ptr[rb] .. list_ptr[rb+1])
     const int* list_idx;
     const int* order;                // DSD: row blocks sorted by kept count, heaviest first
+    const int* h_nnz;                // DSD: plan header entries: kept tiles, and the largest kept count of a row block
+    const int* h_max;
     const int* items;                // SDD: (row block, col tile 0, col tile 1 or -1)
     const int* n_items;
     const int* zero_pairs;           // SDD: dropped (row block, col tile) pairs
@@ -107,11 +109,11 @@ struct Seg {
 //                when there are fewer tiles than SMs, so that every SM still gets work.
 struct WorkIter {
     long long u, u_end, total;   // split: current unit, end of this CTA's range, all units
-    int t, n_tiles, stride;      // whole tiles: next tile, tile count, gridDim.x
+    int t, n_tiles, stride, pass;   // whole tiles: this CTA's index, tile count, gridDim.x, next pass
     int nk_uniform;              // dense / SDD: K tiles per output tile
     int rb, nt, i0;              // split position: row block (SDD: work item), n tile, offset inside the tile
     int n_eff;                   // split: number of CTAs that have a range
-    bool split;
+    bool split, snake;
 
     __device__ __forceinline__ static long long range_start(long long total, int cta, int n_ctas) {
         return total * cta / n_ctas;
@@ -138,6 +140,10 @@ struct WorkIter {
         n_tiles = g.mode == MODE_SDD ? __ldg(g.n_items) : g.n_row_blocks * g.n_col_tiles;
         t = cta;
         stride = n_ctas;
+        pass = 0;
+        // alternate the direction only when row blocks differ in length; with equal tiles (dense, SDD, a mask that
+        // dropped nothing) plain round-robin keeps neighbouring CTAs on neighbouring tiles in every pass
+        snake = g.mode == MODE_DSD && __ldg(g.h_nnz) != g.n_row_blocks * __ldg(g.h_max);
         u = u_end = total = 0;
         rb = nt = i0 = 0;
         n_eff = n_ctas;
@@ -193,18 +199,23 @@ struct WorkIter {
     }
     __device__ bool next(const GemmArgs& g, Seg& s) {
         if (!split) {
-            for (; t < n_tiles; t += stride) {
+            // pass j hands out tiles [j*stride, (j+1)*stride) of the heaviest-first list; with unequal row blocks,
+            // forwards on even passes and backwards on odd ones, so the CTA that got the heaviest tile of one pass
+            // gets the lightest of the next
+            for (; pass * stride < n_tiles; ++pass) {
+                const int tile = pass * stride + ((snake && (pass & 1)) ? stride - 1 - t : t);
+                if (tile >= n_tiles) continue;
                 if (g.mode == MODE_SDD) {
-                    fill(g, s, t, 0);
+                    fill(g, s, tile, 0);
                 } else {
-                    const int rbi = t / g.n_col_tiles;
-                    fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, t - rbi * g.n_col_tiles);
+                    const int rbi = tile / g.n_col_tiles;
+                    fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, tile - rbi * g.n_col_tiles);
                 }
                 if (s.nk == 0) continue;          // empty row blocks are zero-filled by the epilogue warps
                 s.i0 = 0;
                 s.i1 = s.nk;
                 s.tile_end = 0;
-                t += stride;
+                ++pass;
                 return true;
             }
             return false;
@@ -900,9 +911,11 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         if (plan_side == SD_PLAN_ROWS) {
             PlanView v = view_plan(plan, g.n_row_blocks, kb);
             g.list_ptr = v.row_ptr; g.list_idx = v.col_idx; g.order = v.row_order;
+            g.h_nnz = v.header + H_NNZ; g.h_max = v.header + H_MAX_ROW;
         } else {
             PlanView v = view_plan(plan, kb, g.n_row_blocks);
             g.list_ptr = v.col_ptr; g.list_idx = v.row_idx; g.order = v.col_order;
+            g.h_nnz = v.header + H_NNZ; g.h_max = v.header + H_MAX_COL;
         }
     } else if (mode == MODE_SDD) {
         PlanView v = view_plan(plan, g.n_row_blocks, (N + 127) / 128);
