@@ -251,13 +251,219 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
     }
 }
 
+// Fast path for grids with at most 32 K tiles per row (K <= 4096) and at most kBitsMaxRows row blocks: a row of
+// the mask is one 32-bit word (bit c set = tile (r, c) kept), produced by a warp ballot, and every list position is
+// a popcount of that word, so all lists are written in parallel, a warp per row.  Same outputs as plan_kernel.
+constexpr int kBitsMaxRows = 3072;
+
+__global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) {
+    __shared__ unsigned keepmask[kBitsMaxRows];
+    __shared__ int s_row_ptr[kBitsMaxRows];
+    __shared__ int s_item_ptr[kBitsMaxRows];
+    __shared__ int warp_sums[33];
+    __shared__ int col_chunk[32][33];
+    __shared__ int s_col_ptr[33];
+    __shared__ int bins[40];
+    __shared__ int s_max_row;
+
+    const int R = a.R, C = a.C, rep = a.rep;
+    const int Cm = (C + rep - 1) / rep;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const sd_plan_layout L = plan_layout(R, C);
+    int* header = reinterpret_cast<int*>(a.plan + L.header);
+    int* row_ptr = reinterpret_cast<int*>(a.plan + L.row_ptr);
+    int* col_idx = reinterpret_cast<int*>(a.plan + L.col_idx);
+    int* col_ptr = reinterpret_cast<int*>(a.plan + L.col_ptr);
+    int* row_idx = reinterpret_cast<int*>(a.plan + L.row_idx);
+    int* kept_pairs = reinterpret_cast<int*>(a.plan + L.kept_pairs);
+    int* drop_pairs = reinterpret_cast<int*>(a.plan + L.drop_pairs);
+    int* row_order = reinterpret_cast<int*>(a.plan + L.row_order);
+    int* col_order = reinterpret_cast<int*>(a.plan + L.col_order);
+    int* sdd_items = reinterpret_cast<int*>(a.plan + L.sdd_items);
+    unsigned char* gmask = a.plan + L.mask;
+    const unsigned long long offset = a.offset + (a.counter ? *a.counter : 0ull);
+    if (threadIdx.x == 0) s_max_row = 0;
+    if (threadIdx.x < 40) bins[threadIdx.x] = 0;
+
+    // ---- the drop decisions, one tile per thread; kept tiles set their bit in the row word
+    for (int r = threadIdx.x; r < R; r += kPlanThreads) keepmask[r] = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < R * C; i += kPlanThreads) {
+        const int r = i / C, c = i - r * C;
+        const int lr = r / rep, lc = c / rep;
+        bool drop;
+        if (a.from_seed) {
+            drop = philox_drop(a.seed, offset, (unsigned long long)lr * Cm + lc, a.p);
+            if (a.mask_out && r == lr * rep && c == lc * rep) a.mask_out[(long long)lr * Cm + lc] = drop;
+        } else {
+            drop = a.mask_in[lr * a.mask_rs + lc * a.mask_cs] != 0;
+        }
+        gmask[i] = drop;
+        if (!drop) atomicOr(&keepmask[r], 1u << c);
+    }
+    __syncthreads();
+
+    // ---- row offsets: thread t owns rows [t*rpt, (t+1)*rpt)
+    int nnz, n_items;
+    {
+        const int rpt = (R + kPlanThreads - 1) / kPlanThreads;
+        const int r0 = min(R, int(threadIdx.x) * rpt), r1 = min(R, r0 + rpt);
+        int kept = 0, items = 0, mx = 0;
+        for (int r = r0; r < r1; ++r) {
+            const int cnt = __popc(keepmask[r]);
+            kept += cnt;
+            items += (cnt + 1) >> 1;
+            mx = max(mx, cnt);
+        }
+        int kept_off = block_exclusive_scan(kept, warp_sums, nnz);
+        int item_off = block_exclusive_scan(items, warp_sums, n_items);
+        if (mx) atomicMax(&s_max_row, mx);
+        for (int r = r0; r < r1; ++r) {
+            const int cnt = __popc(keepmask[r]);
+            s_row_ptr[r] = kept_off;
+            s_item_ptr[r] = item_off;
+            row_ptr[r] = kept_off;
+            kept_off += cnt;
+            item_off += (cnt + 1) >> 1;
+        }
+        if (threadIdx.x == 0) row_ptr[R] = nnz;
+    }
+    __syncthreads();
+
+    // ---- row lists, one tile per thread: positions are popcounts of the row word below this column
+    for (int i = threadIdx.x; i < R * C; i += kPlanThreads) {
+        const int r = i / C, c = i - r * C;
+        const unsigned mask = keepmask[r];
+        const int base = s_row_ptr[r];
+        const int j = __popc(mask & ((1u << c) - 1u));           // kept tiles left of this column
+        if ((mask >> c) & 1u) {
+            col_idx[base + j] = c;
+            kept_pairs[2 * (base + j)] = r;
+            kept_pairs[2 * (base + j) + 1] = c;
+            if ((j & 1) == 0) {                                  // first tile of a pair: its partner is the next kept column
+                const unsigned above = c == 31 ? 0u : mask & ~((2u << c) - 1u);
+                int* it = sdd_items + 3 * (s_item_ptr[r] + (j >> 1));
+                it[0] = r;
+                it[1] = c;
+                it[2] = above ? __ffs(above) - 1 : -1;
+            }
+        } else {
+            const int d = r * C - base + (c - j);                // dropped tiles before this one
+            drop_pairs[2 * d] = r;
+            drop_pairs[2 * d + 1] = c;
+        }
+    }
+
+    // ---- columns: warp w owns the row chunk [w*rpw, (w+1)*rpw); lane = column
+    const int rpw = (R + 31) / 32;
+    const int cr0 = min(R, warp * rpw), cr1 = min(R, cr0 + rpw);
+    {
+        int cnt = 0;
+        for (int r = cr0; r < cr1; ++r) cnt += (keepmask[r] >> lane) & 1u;
+        col_chunk[warp][lane] = cnt;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int total = 0;
+        for (int w = 0; w < 32; ++w) {                           // exclusive prefix over the row chunks of this column
+            const int c = col_chunk[w][lane];
+            col_chunk[w][lane] = total;
+            total += c;
+        }
+        int incl = total;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += n;
+        }
+        s_col_ptr[lane] = incl - total;
+        if (lane == 31) s_col_ptr[32] = incl;
+        if (lane < C) col_ptr[lane] = incl - total;
+        if (lane == C - 1) col_ptr[C] = incl;
+        // column order, heaviest first (stable)
+        int rank = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int other = __shfl_sync(0xffffffffu, total, j);
+            rank += (j < C) && ((other > total) || (other == total && j < lane));
+        }
+        if (lane < C) col_order[rank] = lane;
+        int mxc = lane < C ? total : 0;
+#pragma unroll
+        for (int d = 16; d; d >>= 1) mxc = max(mxc, __shfl_xor_sync(0xffffffffu, mxc, d));
+        if (lane == 0) {
+            header[H_NNZ] = nnz;
+            header[H_SDD_ITEMS] = n_items;
+            header[H_NDROP] = R * C - nnz;
+            header[H_R] = R;
+            header[H_C] = C;
+            header[H_MAX_ROW] = s_max_row;
+            header[H_MAX_COL] = mxc;
+            if (a.counter) *a.counter = offset - a.offset + 1;   // every thread read it before the first barrier
+        }
+    }
+    __syncthreads();
+    if (lane < C) {
+        int off = s_col_ptr[lane] + col_chunk[warp][lane];
+        for (int r = cr0; r < cr1; ++r)
+            if ((keepmask[r] >> lane) & 1u) row_idx[off++] = r;
+    }
+
+    // ---- row order, heaviest first (stable rank sort for short lists, counting sort otherwise)
+    if (R <= 64) {
+        if (int(threadIdx.x) < R) {
+            const int mine = __popc(keepmask[threadIdx.x]);
+            int rank = 0;
+            for (int j = 0; j < R; ++j) {
+                const int other = __popc(keepmask[j]);
+                rank += (other > mine) || (other == mine && j < int(threadIdx.x));
+            }
+            row_order[rank] = threadIdx.x;
+        }
+    } else {
+        // counting sort on the kept count (at most 33 bins); lanes of a warp that share a bin add to it once
+        const int rounds = (R + kPlanThreads - 1) / kPlanThreads;
+        for (int k = 0; k < rounds; ++k) {
+            const int r = k * kPlanThreads + threadIdx.x;
+            const unsigned live = __ballot_sync(0xffffffffu, r < R);
+            if (r < R) {
+                const int key = C - __popc(keepmask[r]);
+                const unsigned peers = __match_any_sync(live, key);
+                if (lane == __ffs(peers) - 1) atomicAdd(&bins[key], __popc(peers));
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int run = 0;
+            for (int k = 0; k <= C; ++k) { const int c = bins[k]; bins[k] = run; run += c; }
+        }
+        __syncthreads();
+        for (int k = 0; k < rounds; ++k) {
+            const int r = k * kPlanThreads + threadIdx.x;
+            const unsigned live = __ballot_sync(0xffffffffu, r < R);
+            if (r < R) {
+                const int key = C - __popc(keepmask[r]);
+                const unsigned peers = __match_any_sync(live, key);
+                const int leader = __ffs(peers) - 1;
+                int base = 0;
+                if (lane == leader) base = atomicAdd(&bins[key], __popc(peers));
+                base = __shfl_sync(peers, base, leader);
+                row_order[base + __popc(peers & ((1u << lane) - 1u))] = r;
+            }
+        }
+    }
+}
+
 static int launch_plan(const PlanArgs& a, void* stream) {
     if (!a.plan) return fail(SD_ERR_INVALID_ARG, "plan buffer is null");
     if (a.R <= 0 || a.C <= 0) return fail(SD_ERR_INVALID_ARG, "plan grid must be positive (R=%d, C=%d)", a.R, a.C);
     if (a.rep <= 0) return fail(SD_ERR_INVALID_ARG, "block_size must be a positive multiple of 128");
     if (int64_t(a.R) * a.C > (int64_t(1) << 26))
         return fail(SD_ERR_TOO_LARGE, "plan grid %d x %d exceeds 2^26 tiles", a.R, a.C);
-    plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    if (a.C <= 32 && a.R <= kBitsMaxRows)
+        plan_bits_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    else
+        plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     SD_CUDA_TRY(cudaGetLastError());
     return SD_OK;
 }

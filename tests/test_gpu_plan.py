@@ -18,6 +18,9 @@ CASES = [  # (M, K, block_size, p, seed, offset)
     (128, 128, 128, 0.5, 6, 0), (384, 640, 128, 0.3, 7, 2**40 + 9),
     (1024, 2048, 256, 0.5, 8, 0), (1000, 1500, 512, 0.4, 9, 1),    # logical blocks larger than a tile
     (300, 392, 128, 0.4, 2**63 + 12345, 0),
+    # beyond the 32-column / 3072-row fast path: the general kernel (wide, and tall)
+    (1024, 8192, 128, 0.5, 10, 0), (640, 5120, 128, 0.3, 11, 1), (524288, 384, 128, 0.5, 12, 0),
+    (393216, 4096, 128, 0.5, 13, 2),      # exactly 3072 rows x 32 columns: largest grid of the fast path
 ]
 
 
