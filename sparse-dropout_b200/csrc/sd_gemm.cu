@@ -515,6 +515,10 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this CTA's own resources, so it may overlap the tail of the previous kernel in
+    // the stream; everything below reads operands, plan lists or workspace that kernel may have produced.
+    grid_dep_launch();
+    grid_dep_wait();
 
     const int n_ctas = gridDim.x, cta = blockIdx.x;
 #ifdef SD_TIMING
@@ -847,8 +851,17 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
         SD_CUDA_TRY(cudaFuncSetAttribute(sparsedrop_gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GEMM_SMEM));
     }
-    sparsedrop_gemm_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ta, tb, tc, g);
-    SD_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // prologue may overlap the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, sparsedrop_gemm_kernel<A_MN, B_MN>, ta, tb, tc, g));
     return SD_OK;
 }
 

@@ -11,6 +11,7 @@
 // The work is a few KB of integer traffic: the launch is latency-bound, not HBM-bound.
 #include "sd_common.h"
 #include "sd_plan.cuh"
+#include "sd_ptx.cuh"
 
 namespace sd {
 
@@ -83,6 +84,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
     unsigned char* m = in_smem ? smask : gmask;
 
     if (threadIdx.x == 0) { s_max_row = 0; s_max_col = 0; }
+    grid_dep_launch();
+    grid_dep_wait();   // the counter, a caller's mask and the plan buffer may belong to the previous kernel
     const unsigned long long offset = a.offset + (a.counter ? *a.counter : 0ull);
 
     // ---- phase 0: the drop decision of every tile (1 = dropped)
@@ -281,6 +284,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
     int* col_order = reinterpret_cast<int*>(a.plan + L.col_order);
     int* sdd_items = reinterpret_cast<int*>(a.plan + L.sdd_items);
     unsigned char* gmask = a.plan + L.mask;
+    grid_dep_launch();
+    grid_dep_wait();   // the counter, a caller's mask and the plan buffer may belong to the previous kernel
     const unsigned long long offset = a.offset + (a.counter ? *a.counter : 0ull);
     if (threadIdx.x == 0) s_max_row = 0;
     if (threadIdx.x < 40) bins[threadIdx.x] = 0;
@@ -460,11 +465,19 @@ static int launch_plan(const PlanArgs& a, void* stream) {
     if (a.rep <= 0) return fail(SD_ERR_INVALID_ARG, "block_size must be a positive multiple of 128");
     if (int64_t(a.R) * a.C > (int64_t(1) << 26))
         return fail(SD_ERR_TOO_LARGE, "plan grid %d x %d exceeds 2^26 tiles", a.R, a.C);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(kPlanThreads);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (a.C <= 32 && a.R <= kBitsMaxRows)
-        plan_bits_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+        SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, plan_bits_kernel, a));
     else
-        plan_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
-    SD_CUDA_TRY(cudaGetLastError());
+        SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, plan_kernel, a));
     return SD_OK;
 }
 

@@ -22,6 +22,14 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in
+// the stream is still draining.  grid_dep_wait() blocks until that kernel has completed and its writes are visible;
+// it must precede the first read of anything an earlier kernel produced.  grid_dep_launch() lets the NEXT kernel's
+// CTAs be scheduled as soon as resources free up.  Both are no-ops for a normally launched kernel.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
