@@ -223,6 +223,16 @@ int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int
                    int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
                    void* dx, const void* plan, int dtype, void* stream);
 
+/*
+ * Exercises the bounded device-side waits the kernels are built on, without a fault or a hang: a one-warp kernel
+ * waits on a barrier nobody arrives on and on a counter nobody increments, each for at most limit_ns (<= 1 s),
+ * gives up, and returns normally.  `words` is 4 device ints: [0] status word (first give-up code, 101),
+ * [1] the counter that stays 0, [2] bit mask (1|2 = a wait wrongly succeeded, 4|8 = its abort flag was raised),
+ * [3] elapsed microseconds.  sd_check_status(words, stream) then reports SD_ERR_TIMEOUT.  No counterpart in the
+ * reference, whose kernels have no waits to bound.
+ */
+int sd_selftest_bounded_wait(int* words, uint64_t limit_ns, void* stream);
+
 /* Synchronises the stream, reads *status and returns SD_OK or SD_ERR_TIMEOUT. */
 int sd_check_status(const int* status, void* stream);
 

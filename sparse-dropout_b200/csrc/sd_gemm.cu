@@ -376,26 +376,6 @@ __device__ __forceinline__ int tile_owner(long long total, long long first, int 
     return c;
 }
 
-// Bounded wait until a counter another CTA increments reaches `target`.
-__device__ __forceinline__ bool counter_wait(const int* counter, int target, volatile int* abort_flag, int* status, int code) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        int v;
-        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-        if (v >= target) return true;
-        if ((it & 0xff) == 0xff) {
-            if (*abort_flag) return false;
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            if (now - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                if (status) atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
 // All CTAs whose ranges intersect one output tile have parked their partial accumulators (the owner of the tile's
 // first unit in its slot 1, the others in their slot 0) and counted themselves in arrive[owner].  Once the count is
 // complete, every participant adds up a different share of the tile's 32x32 units over all partials, in CTA order

@@ -72,7 +72,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s; a whole launch is far below this
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t it = 1;; ++it) {
@@ -81,7 +81,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > kWaitLimitNs || it > (1u << 30)) {
+            if (now - t0 > limit_ns || it > (1u << 30)) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Bounded wait until a counter in global memory that another CTA increments reaches `target`.
+__device__ __forceinline__ bool counter_wait(const int* counter, int target, volatile int* abort_flag, int* status,
+                                             int code, uint64_t limit_ns = kWaitLimitNs) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= target) return true;
+        if ((it & 0xff) == 0xff) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
                 return false;

@@ -1,0 +1,38 @@
+"""Failure detection without a GPU fault: device-side waits are bounded and report through a status word.
+
+The waits of the GEMM kernel (mbarrier waits between its roles, the arrival counter of the equal-share schedule) all go
+through two helpers that give up after a time limit, record a code and let the kernel finish normally.  The self-test
+kernel runs exactly those helpers against a barrier nobody arrives on and a counter nobody increments, with a 20 ms
+limit; afterwards the context must still run kernels."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+SD_ERR_TIMEOUT = -4
+
+
+def test_bounded_waits_give_up_and_context_survives(built_lib):
+    from flash_dropout.cuda.binding_gemm import dense
+    words = torch.full((4,), -1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    assert built_lib.sd_selftest_bounded_wait(words.data_ptr(), 20_000_000, stream) == 0
+    rc = built_lib.sd_check_status(words.data_ptr(), stream)           # synchronises and reads the status word
+    assert rc == SD_ERR_TIMEOUT
+    assert b"code 101" in built_lib.sd_last_error()
+    status, counter, flags, elapsed_us = words.cpu().tolist()
+    assert status == 101 and counter == 0
+    assert flags == 4 | 8                                              # neither wait succeeded, both raised their flag
+    assert 2 * 20_000 <= elapsed_us < 2_000_000                        # two waits of >= 20 ms each, far below a hang
+    # the kernel returned normally: the same context keeps working
+    a = torch.randn(256, 256, device=DEV, dtype=torch.float16)
+    torch.testing.assert_close(dense(a, a).float(), a.float() @ a.float().T, rtol=1e-2, atol=1e-1)
+    # a clean status word reports OK
+    ok = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert built_lib.sd_check_status(ok.data_ptr(), stream) == 0
+
+
+def test_selftest_rejects_long_limits(built_lib):
+    words = torch.zeros(4, dtype=torch.int32, device=DEV)
+    assert built_lib.sd_selftest_bounded_wait(words.data_ptr(), 5_000_000_000, None) == -1
+    assert built_lib.sd_selftest_bounded_wait(None, 1000, None) == -1
