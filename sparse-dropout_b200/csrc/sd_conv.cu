@@ -64,16 +64,22 @@ __global__ void __launch_bounds__(kConvThreads) im2col_kept_rows_kernel(const un
         const int n = live ? m0 / PQ : 0, pq = m0 - n * PQ, p = pq / g.Q, q0 = pq - p * g.Q;
         const unsigned short* xn = x + (long long)n * g.C * HW;
         const int hbase = p * g.stride_h - g.pad_h, wbase = q0 - g.pad_w;
+        // (c, r*S + s) of this thread's first k-row; every pass advances k by 16 without dividing by C*R*S again
+        int c = (kb * 128 + ksub) / RS, rs = (kb * 128 + ksub) - c * RS;
+        const int c16 = 16 / RS, rs16 = 16 - c16 * RS;
 #pragma unroll 2
         for (int pass = 0; pass < 8; ++pass) {
             const int k = kb * 128 + pass * 16 + ksub;
             if (k >= g.K) break;
-            const int c = k / RS, rs = k - c * RS, r = rs / g.S, s = rs - r * g.S;
+            const int r = rs / g.S, s = rs - r * g.S;
             const int h = hbase + r * g.dil_h;
             uint32_t o[4] = {0, 0, 0, 0};
             if (live && (unsigned)h < (unsigned)g.H)
                 load8_shifted(xn + (long long)c * HW + (long long)h * g.W, wbase + s * g.dil_w, g.W, o);
             *reinterpret_cast<uint4*>(colT + (long long)k * g.ldm + m0) = make_uint4(o[0], o[1], o[2], o[3]);
+            c += c16;
+            rs += rs16;
+            if (rs >= RS) { rs -= RS; ++c; }
         }
     }
 }
@@ -178,17 +184,16 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_kernel(const unsigne
 
 // Fast col2im for unit strides with W % 8 == 0 and Q % 8 == 0: a thread owns 8 consecutive w of one (n, c, h);
 // every filter tap is one shifted 8-element window of one dcolT row, whose aligned chunks each lie in one block.
+template <bool IS_BF16>
 __global__ void __launch_bounds__(kConvThreads) col2im_kept_rows_kernel(const unsigned short* __restrict__ dcolT,
                                                                         unsigned short* __restrict__ dx, ConvGeom g,
-                                                                        const unsigned char* __restrict__ tile_mask,
-                                                                        int is_bf16) {
+                                                                        const unsigned char* __restrict__ tile_mask) {
     const int WG = g.W >> 3;
-    const long long total = (long long)g.N * g.C * g.H * WG;
+    const unsigned total = unsigned(g.N) * g.C * g.H * WG;       // the host checks that this fits 32 bits
     const int PQ = g.P * g.Q, RS = g.R * g.S;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int wg = int(i % WG);
-        long long rest = i / WG;
+        unsigned rest = i / WG;
         const int h = int(rest % g.H);
         rest /= g.H;
         const int c = int(rest % g.C), n = int(rest / g.C);
@@ -217,17 +222,29 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_rows_kernel(const un
                                        __funnelshift_r(w2, w3, sb), __funnelshift_r(w3, w4, sb)};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[2 * j] += to_float((unsigned short)(o[j] & 0xffff), is_bf16);
-                    acc[2 * j + 1] += to_float((unsigned short)(o[j] >> 16), is_bf16);
+                    if (IS_BF16) {                               // bf16 -> fp32 is a 16-bit shift
+                        acc[2 * j] += __uint_as_float(o[j] << 16);
+                        acc[2 * j + 1] += __uint_as_float(o[j] & 0xffff0000u);
+                    } else {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&o[j]));
+                        acc[2 * j] += f.x;
+                        acc[2 * j + 1] += f.y;
+                    }
                 }
             }
         }
-        uint4 out;
-        out.x = from_float(acc[0], is_bf16) | (uint32_t(from_float(acc[1], is_bf16)) << 16);
-        out.y = from_float(acc[2], is_bf16) | (uint32_t(from_float(acc[3], is_bf16)) << 16);
-        out.z = from_float(acc[4], is_bf16) | (uint32_t(from_float(acc[5], is_bf16)) << 16);
-        out.w = from_float(acc[6], is_bf16) | (uint32_t(from_float(acc[7], is_bf16)) << 16);
-        *reinterpret_cast<uint4*>(dx + i * 8) = out;
+        uint32_t out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (IS_BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                out[j] = *reinterpret_cast<uint32_t*>(&v);
+            } else {
+                __half2 v = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+                out[j] = *reinterpret_cast<uint32_t*>(&v);
+            }
+        }
+        *reinterpret_cast<uint4*>(dx + (long long)i * 8) = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
@@ -298,13 +315,17 @@ int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int
     rc = sd::sm_count_current_device(&sms);
     if (rc) return rc;
     const bool rows_path = stride_w == 1 && stride_h == 1 && (W & 7) == 0 && (g.Q & 7) == 0 &&
-                           ((reinterpret_cast<uintptr_t>(dcolT) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
+                           ((reinterpret_cast<uintptr_t>(dcolT) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0 &&
+                           (long long)N * C * H * (W / 8) < (1ll << 31);
     const long long total = (long long)N * C * H * (rows_path ? W / 8 : W);
     long long blocks = (total + sd::kConvThreads - 1) / sd::kConvThreads;
     int grid = int(blocks < (long long)sms * 16 ? blocks : (long long)sms * 16);
-    if (rows_path)
-        sd::col2im_kept_rows_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask, dtype == SD_BF16);
+    if (rows_path && dtype == SD_BF16)
+        sd::col2im_kept_rows_kernel<true><<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask);
+    else if (rows_path)
+        sd::col2im_kept_rows_kernel<false><<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask);
     else
         sd::col2im_kept_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
             static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask, dtype == SD_BF16);

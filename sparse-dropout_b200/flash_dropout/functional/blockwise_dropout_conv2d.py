@@ -13,8 +13,8 @@ Data flow (nothing goes through F.unfold):
   backward  DSD          : dW2d[Kout, K] written transposed, reduction over kept row blocks of each K tile
             SDD          : dcolT[K][M] = keep o (dy2d . W2d) / (1-p), stored column-major
             col2im_kept  : dx (NCHW) = adjoint gather over kept blocks           (HBM-bound)
-  colT is recomputed in backward from the saved input (33 MB instead of 300 MB of saved activations at
-  BASELINE's conv config).
+  By default the kept blocks of colT are saved for backward (151 MB at BASELINE's conv config, half of what an
+  unfold-based layer keeps); ``recompute_cols=True`` saves only the input (33 MB) and rebuilds colT in backward.
 """
 from __future__ import annotations
 
@@ -69,7 +69,7 @@ def col2im_kept(dcolT: torch.Tensor, x_shape, kernel_size, padding, stride, dila
 
 class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, kernel, block_size, p, padding, stride, dilation, plan):
+    def forward(ctx, input, kernel, block_size, p, padding, stride, dilation, plan, recompute_cols):
         assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
         if not (input.is_cuda and kernel.is_cuda):
             raise RuntimeError("input and kernel must be CUDA")
@@ -91,14 +91,17 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
         w2d = w2d.contiguous()
         colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg)
         y2d = dsd(colT.T[:M], w2d, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))      # (M, Kog)
-        ctx.save_for_backward(input, w2d)
+        if recompute_cols:
+            ctx.save_for_backward(input, w2d)
+        else:
+            ctx.save_for_backward(input, w2d, colT)
         ctx.plan, ctx.p = plan, p
         ctx.geom = (padding, stride, dilation, (R, S), Ko, K)
         return y2d.view(N, P, Q, Kog)[..., :Ko].permute(0, 3, 1, 2)
 
     @staticmethod
     def backward(ctx, grad_output):
-        input, w2d = ctx.saved_tensors
+        input, w2d, *saved_cols = ctx.saved_tensors
         plan, scale = ctx.plan, 1.0 / (1.0 - ctx.p)
         padding, stride, dilation, (R, S), Ko, K = ctx.geom
         N, C, H, W = input.shape
@@ -110,7 +113,7 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
         dy2d = dy2d.contiguous()
         grad_input = grad_kernel = None
         if ctx.needs_input_grad[1]:
-            colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg)
+            colT = saved_cols[0] if saved_cols else im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg)
             dw2d = torch.empty((Kog, Kg), dtype=input.dtype, device=input.device)
             dsd(colT[:, :M], dy2d.T, plan, _lib.SD_PLAN_COLS, scale, out=dw2d.T)
             grad_kernel = dw2d[:Ko, :K].reshape(Ko, C, R, S)
@@ -119,15 +122,16 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
             dcolT = torch.empty((Kg, (M + 7) & ~7), dtype=input.dtype, device=input.device)
             sdd(dy2d, w2d.T, plan, scale, out=dcolT.T[:M], zero_dropped=False)    # col2im reads kept blocks only
             grad_input = col2im_kept(dcolT, input.shape, (R, S), padding, stride, dilation, plan)
-        return grad_input, grad_kernel, None, None, None, None, None, None
+        return grad_input, grad_kernel, None, None, None, None, None, None, None
 
 
 def blockwise_dropout_conv2d(input: torch.Tensor, kernel: torch.Tensor, block_size: int, p: float,
-                             padding=(0, 0), stride=(1, 1), dilation=(1, 1), plan=None) -> torch.Tensor:
+                             padding=(0, 0), stride=(1, 1), dilation=(1, 1), plan=None,
+                             recompute_cols: bool = False) -> torch.Tensor:
     """Conv2d (no bias) whose im2col matrix is block-dropped with probability ``p``; NCHW in, NCHW-shaped out."""
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
         input, kernel = input.to(dt), kernel.to(dt)
     with torch.autocast("cuda", enabled=False):
         return BlockwiseDropoutConv2dCUDA.apply(input, kernel, block_size, p, tuple(padding), tuple(stride),
-                                                tuple(dilation), plan)
+                                                tuple(dilation), plan, recompute_cols)

@@ -54,8 +54,9 @@ def test_im2col_and_col2im_against_unfold_fold(built_lib, geom, dtype):
     assert torch.equal(dense[:K, :M].float().cpu(), want)
 
 
+@pytest.mark.parametrize("recompute", [False, True])
 @pytest.mark.parametrize("geom,Ko", [(GEOMS[0], 128), (GEOMS[1], 24), (GEOMS[2], 40), (GEOMS[4], 10)])
-def test_conv_op_against_oracle(built_lib, geom, Ko):
+def test_conv_op_against_oracle(built_lib, geom, Ko, recompute):
     import flash_dropout.functional as F
     from flash_dropout import random as sd_random
     N, C, H, W, R, S, pad, stride, dil = geom
@@ -65,7 +66,8 @@ def test_conv_op_against_oracle(built_lib, geom, Ko):
     k = (torch.randn(Ko, C, R, S, generator=g) / (C * R * S) ** 0.5).half()
     xa, ka = x.to(DEV).requires_grad_(), k.to(DEV).requires_grad_()
     sd_random.manual_seed(31, subsequence=0)
-    y = F.cuda_blockwise_dropout_conv2d(xa, ka, 128, p, padding=pad, stride=stride, dilation=dil)
+    y = F.cuda_blockwise_dropout_conv2d(xa, ka, 128, p, padding=pad, stride=stride, dilation=dil,
+                                        recompute_cols=recompute)
     P, Q = y.shape[2:]
     dy = (torch.randn(N, Ko, P, Q, generator=g) * 0.25).half()
     y.backward(dy.to(DEV))
