@@ -104,3 +104,37 @@ def test_conv_baseline_config_shapes(built_lib):
     torch.testing.assert_close(ka.grad.float().cpu() / 128, dk_ref / 128, rtol=1e-2, atol=1e-2)
     torch.testing.assert_close(xa.grad.float().cpu(), dx_ref, rtol=1e-2, atol=2e-2)
     sd_random.follow_torch_seed()
+
+
+def test_conv_full_size_properties(built_lib):
+    """BASELINE configs[2] at its full size (256 x 64 x 32 x 32, 64 -> 128, 3x3, pad 1): size-independent properties.
+
+    * p = 0 (nothing dropped): forward, dW and dx agree with cuDNN's dense convolution;
+    * p = 0.5: the op equals the dense convolution machinery applied to an explicitly masked im2col matrix, checked
+      through linearity — conv(x; mask) + conv(x; ~mask) == 2 * dense conv(x) / 1 (each scaled by 1/(1-p) = 2).
+    """
+    import flash_dropout.functional as F
+    from flash_dropout.cuda.binding_gemm import BlockPlan
+    torch.manual_seed(0)
+    x = torch.randn(256, 64, 32, 32, device=DEV, dtype=torch.float16, requires_grad=True)
+    k = (torch.randn(128, 64, 3, 3, device=DEV, dtype=torch.float16) / 24).requires_grad_()
+    dy = torch.randn(256, 128, 32, 32, device=DEV, dtype=torch.float16).contiguous(memory_format=torch.channels_last)
+    y = F.cuda_blockwise_dropout_conv2d(x, k, 128, 0.0, padding=(1, 1))
+    y.backward(dy)
+    gx, gk = x.grad.clone(), k.grad.clone()
+    x.grad = k.grad = None
+    yd = torch.nn.functional.conv2d(x, k, padding=1)
+    yd.backward(dy)
+    torch.testing.assert_close(y.float(), yd.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(gx.float(), x.grad.float(), rtol=1e-2, atol=2e-2)
+    # dW sums 262144 products per element: compare on the scale of its magnitude
+    scale = x.grad.new_tensor(512.0)
+    torch.testing.assert_close(gk.float() / scale, k.grad.float() / scale, rtol=1e-2, atol=1e-2)
+    # complementary masks add up to the dense result
+    M, Kg = 256 * 1024, 576
+    plan = BlockPlan.from_seed(M, Kg, 128, 0.5, 7, 0, DEV)
+    anti = BlockPlan.from_mask(~plan.mask, M, Kg, 128)
+    with torch.no_grad():
+        ya = F.cuda_blockwise_dropout_conv2d(x, k, 128, 0.5, padding=(1, 1), plan=plan)
+        yb = F.cuda_blockwise_dropout_conv2d(x, k, 128, 0.5, padding=(1, 1), plan=anti)
+    torch.testing.assert_close((ya.float() + yb.float()) / 2, yd.float(), rtol=1e-2, atol=2e-2)
