@@ -9,6 +9,8 @@ bf16 is accepted as well as fp16; launches go to the current stream of the tenso
 """
 from __future__ import annotations
 
+import weakref
+
 import torch
 
 from flash_dropout import _lib
@@ -66,6 +68,25 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
         return grad_input, grad_weight, None, None, None
 
 
+_last_cast = {"key": None, "ref": None}
+
+
+def _autocast_input(input: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
+    """``input.to(dt)``, shared between consecutive layers that are fed the very same tensor (the q / k / v
+    projections of an attention block): one cast forward, and one cast of the summed gradient backward."""
+    if input.dtype == dt:
+        return input
+    key = (input.data_ptr(), input._version, tuple(input.shape), tuple(input.stride()), input.dtype, dt,
+           input.requires_grad, torch.is_grad_enabled())
+    if _last_cast["key"] == key:
+        cached = _last_cast["ref"]()
+        if cached is not None:
+            return cached
+    out = input.to(dt)
+    _last_cast["key"], _last_cast["ref"] = key, weakref.ref(out)
+    return out
+
+
 def blockwise_dropout_matmul(input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
                              plan: BlockPlan | None = None) -> torch.Tensor:
     """``y = (mask o input) . weight^T / (1 - p)`` with a fresh block mask (or the given plan).
@@ -75,6 +96,6 @@ def blockwise_dropout_matmul(input: torch.Tensor, weight: torch.Tensor, block_si
     """
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
-        input, weight = input.to(dt), weight.to(dt)
+        input, weight = _autocast_input(input, dt), weight.to(dt)
     with torch.autocast("cuda", enabled=False):
         return BlockwiseDropoutMatmulCUDA.apply(input, weight, block_size, p, plan)
