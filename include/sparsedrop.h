@@ -123,11 +123,12 @@ int sd_plan_from_mask(void* plan, int R, int C, int rep, const uint8_t* mask,
  * `workspace` is optional device scratch (may be NULL).  A launch with fewer 128x256 output tiles
  * than SMs (small layers; the dW product of a conv, whose reduction runs over all N*P*Q rows) would
  * leave SMs idle if tiles were handed out whole, so with a workspace (and a reduction of at least
- * 16 K tiles) it cuts its stream of kept K tiles into equal shares per SM instead: a CTA whose
- * share begins or ends inside an output tile parks its fp32 partial tile in the workspace, and
- * the CTAs sharing a tile each add up a different part of it over all partials (in CTA order, so
- * results are reproducible).  Launches with enough tiles never touch the workspace.  It is
- * sd_workspace_bytes() bytes for the current device (8 KiB of counters + 256 KiB per SM, 37 MiB
+ * 16 K tiles) it gives every output tile a group of SMs instead, sized in proportion to the tile's
+ * kept K tiles: each CTA of a group computes one part of the tile's reduction and parks its fp32
+ * partial tile in the workspace, and the CTAs of the group each add up a different part of the
+ * tile over all partials (in CTA order, so results are reproducible).  Launches with enough tiles
+ * never touch the workspace.  It is
+ * sd_workspace_bytes() bytes for the current device (8 KiB of counters + 128 KiB per SM, 18.5 MiB
  * on a B200), 16-byte aligned, and must be passed through
  * sd_workspace_init() once before its first use (and again after a launch that reported
  * SD_ERR_TIMEOUT).  A launch leaves the flags cleared.  Launches that may overlap on the GPU
@@ -164,7 +165,7 @@ int sd_gemm_dsd(const void* A, int64_t a_rs, int64_t a_cs,
  * device-wide synchronisation an allocation implies, or a plain C caller with no allocator at hand.
  * sd_gemm_dsd() needs such a caller to allocate the workspace before it can spread a small product over
  * all SMs; this entry point computes the same product with scratch that is built into the library:
- * a file-scope device array of 16 392 KiB (8 KiB of counters + 2 x 64 partial tiles of 128 KiB) that every GPU
+ * a file-scope device array of 8 200 KiB (8 KiB of counters + 64 partial tiles of 128 KiB) that every GPU
  * which loads the library holds until the process exits.  It calls no cudaMalloc / cudaFree and no
  * allocating library routine; inputs, the plan and the output are still the caller's.
  *

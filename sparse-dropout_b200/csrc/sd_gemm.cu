@@ -23,15 +23,14 @@
 //
 // Scheduling.  With several output tiles per SM, whole tiles are dealt round-robin from a list sorted
 // heaviest row block first.  With fewer tiles than SMs and a long reduction (the dW product of a layer fed
-// thousands of rows, or of a conv whose reduction runs over all N*P*Q pixels) the unit of work becomes one
-// kept 128-wide K tile of one output tile: all units of the launch form one sequence (tiles in row-block
-// order, kept K tiles ascending) that is cut into equal contiguous ranges, one per CTA, so every SM gets the
-// same number of MMA steps.  A range may then begin or end inside an output tile.  Every CTA that computed
-// only part of a tile parks its fp32 accumulator in the workspace (slot 0: the tile its range starts inside,
-// slot 1: the tile its range ends inside) and counts itself in; after its last segment it waits, bounded, for
-// the tile's other CTAs and then adds up ITS share of the tile's 32x32 units over all parked accumulators, in
-// CTA order (so results do not depend on timing), and stores them.  The CTA that finishes last clears the
-// counters.  This needs the caller's workspace; without one, whole tiles are used throughout.
+// thousands of rows, or of a conv whose reduction runs over all N*P*Q pixels) every output tile gets a group
+// of consecutive CTAs instead: one each, and the spare CTAs dealt out in proportion to the tiles' kept K
+// tiles, so every SM gets about the same number of MMA steps.  Each CTA of a group computes one contiguous
+// part of the tile's kept K-tile list, parks its fp32 accumulator in its workspace slot and counts itself in;
+// it then waits, bounded, for the rest of the group and adds up ITS share of the tile's 32x32 units over all
+// parked accumulators, in CTA order (so results do not depend on timing), and stores them.  The CTA that
+// finishes last clears the counters.  This needs the caller's workspace; without one, whole tiles are used
+// throughout.
 //
 // Every wait is bounded (sd_ptx.cuh: mbar_wait); on expiry the CTA records a code in the status
 // word, every role leaves its loop, TMEM is freed and the kernel returns normally.
@@ -63,7 +62,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int WS_MAX_CTAS = 1024;
 constexpr size_t WS_FLAG_BYTES = 2 * WS_MAX_CTAS * sizeof(int);   // arrive[] then done[], indexed by the tile owner's CTA
 constexpr size_t WS_SLOT_FLOATS = size_t(BM) * BN;
-constexpr size_t WS_SLOT_BYTES = WS_SLOT_FLOATS * sizeof(float);   // 128 KiB; two slots per CTA
+constexpr size_t WS_SLOT_BYTES = WS_SLOT_FLOATS * sizeof(float);   // 128 KiB; one slot per CTA
 
 enum GemmMode { MODE_DENSE = 0, MODE_DSD = 1, MODE_SDD = 2 };
 enum StatusCode { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_ACC = 3, ST_EPILOGUE = 4, ST_FIXUP = 5 };
@@ -98,41 +97,42 @@ struct Seg {
     int a_row, b_row0, b_row1;   // element coordinates along the operands' MN dimension; b_row1 < 0: absent
     const int* klist;            // kept K-tile indices of the whole tile, or null for 0..nk-1
     int nk, i0, i1;
-    long long tile_end;          // unit index one past the tile's last unit
+    int owner, parts, part;      // split schedule: first CTA of the tile's group, CTAs in the group, this CTA's place
 };
 
 // Walks this CTA's share of the launch.  Every role of the CTA runs its own copy and sees the same
 // segments in the same order.  Two schedules:
 //   split == 0 : whole output tiles, dealt round-robin from a list sorted heaviest row block first
 //                (longest-processing-time order); the choice when there are several tiles per SM;
-//   split == 1 : the unit sequence cut into gridDim.x equal ranges (see the file header); the choice
-//                when there are fewer tiles than SMs, so that every SM still gets work.
+//   split == 1 : every output tile gets a group of consecutive CTAs, sized in proportion to the tile's
+//                work, and each CTA of the group one contiguous part of the tile's kept K-tile list (see
+//                the file header); the choice when there are fewer tiles than SMs and a long reduction.
 struct WorkIter {
-    long long u, u_end, total;   // split: current unit, end of this CTA's range, all units
     int t, n_tiles, stride, pass;   // whole tiles: this CTA's index, tile count, gridDim.x, next pass
     int nk_uniform;              // dense / SDD: K tiles per output tile
-    int rb, nt, i0;              // split position: row block (SDD: work item), n tile, offset inside the tile
-    int n_eff;                   // split: number of CTAs that have a range
+    int sp_rb, sp_nt, sp_owner, sp_parts, sp_part;   // split: this CTA's one segment; sp_parts == 0: none
     bool split, snake;
 
-    __device__ __forceinline__ static long long range_start(long long total, int cta, int n_ctas) {
-        return total * cta / n_ctas;
-    }
     __device__ __forceinline__ int count(const GemmArgs& g, int r) const {
         return __ldg(g.list_ptr + r + 1) - __ldg(g.list_ptr + r);
     }
-    __device__ __forceinline__ int tile_len(const GemmArgs& g) const {
-        return g.mode == MODE_DSD ? count(g, rb) : nk_uniform;
+    // Work (in half-width K-tile steps) of all tiles before `tile`, tiles counted in row-block-major order.
+    // A 256-wide tile step costs 2, the 128-wide last column tile of a ragged N costs 1.
+    __device__ __forceinline__ unsigned work_before(const GemmArgs& g, int tile, int row_weight) const {
+        if (g.mode == MODE_SDD) return unsigned(tile) * unsigned(nk_uniform);
+        const int rb = tile / g.n_col_tiles, nt = tile - rb * g.n_col_tiles;
+        if (g.mode == MODE_DENSE) return unsigned(rb * row_weight + 2 * nt) * unsigned(nk_uniform);
+        unsigned w = unsigned(row_weight) * unsigned(__ldg(g.list_ptr + rb));
+        if (nt) w += unsigned(2 * nt) * unsigned(count(g, rb));
+        return w;
     }
-    __device__ __forceinline__ void next_tile(const GemmArgs& g) {
-        i0 = 0;
-        if (g.mode == MODE_SDD) { ++rb; return; }
-        if (++nt == g.n_col_tiles) {
-            nt = 0;
-            ++rb;
-            if (g.mode == MODE_DSD)
-                while (rb < g.n_row_blocks && count(g, rb) == 0) ++rb;
-        }
+    // First CTA of tile `tile`: one CTA per tile, the spare ones dealt in proportion to the work before it.
+    __device__ __forceinline__ int group_start(const GemmArgs& g, int tile, int row_weight, unsigned total, int spare,
+                                               bool fits32) const {
+        const unsigned w = work_before(g, tile, row_weight);
+        const unsigned extra = fits32 ? (unsigned(spare) * w) / total
+                                      : unsigned((unsigned long long)spare * w / total);
+        return tile + int(extra);
     }
     __device__ void init(const GemmArgs& g, int cta, int n_ctas) {
         split = g.split != 0;
@@ -144,35 +144,30 @@ struct WorkIter {
         // alternate the direction only when row blocks differ in length; with equal tiles (dense, SDD, a mask that
         // dropped nothing) plain round-robin keeps neighbouring CTAs on neighbouring tiles in every pass
         snake = g.mode == MODE_DSD && __ldg(g.h_nnz) != g.n_row_blocks * __ldg(g.h_max);
-        u = u_end = total = 0;
-        rb = nt = i0 = 0;
-        n_eff = n_ctas;
-        if (!split) return;
-        if (g.mode == MODE_DSD) total = (long long)g.n_col_tiles * __ldg(g.list_ptr + g.n_row_blocks);
-        else total = (long long)n_tiles * nk_uniform;
-        // never more ranges than units, so no range is empty: the CTAs of a shared tile are then simply consecutive
-        n_eff = total < n_ctas ? int(total) : n_ctas;
-        if (cta >= n_eff) return;
-        u = range_start(total, cta, n_eff);
-        u_end = range_start(total, cta + 1, n_eff);
-        if (g.mode == MODE_DSD) {
-            const int v = int(u / g.n_col_tiles);
-            int lo = 0, hi = g.n_row_blocks - 1;   // first row block with list_ptr[r + 1] > v
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                if (__ldg(g.list_ptr + mid + 1) > v) hi = mid; else lo = mid + 1;
-            }
-            rb = lo;
-            const long long rem = u - (long long)g.n_col_tiles * __ldg(g.list_ptr + rb);
-            const int cnt = count(g, rb);
-            nt = int(rem / cnt);
-            i0 = int(rem - (long long)nt * cnt);
-        } else {
-            const long long tile = u / nk_uniform;
-            i0 = int(u - tile * nk_uniform);
-            if (g.mode == MODE_SDD) { rb = int(tile); }
-            else { rb = int(tile / g.n_col_tiles); nt = int(tile - (long long)rb * g.n_col_tiles); }
+        sp_rb = sp_nt = sp_owner = sp_part = 0;
+        sp_parts = 0;
+        if (!split || n_tiles == 0 || n_tiles > n_ctas) return;
+        const bool ragged = (g.n_col_tiles - 1) * BN + 128 >= g.NN;
+        const int row_weight = 2 * g.n_col_tiles - (ragged ? 1 : 0);
+        const unsigned total = work_before(g, n_tiles, row_weight);
+        if (total == 0) return;                                   // everything dropped: only zero-filling is left
+        const int spare = n_ctas - n_tiles;
+        const bool fits32 = (unsigned long long)total * unsigned(spare) <= 0xffffffffull;
+        int lo = 0, hi = n_tiles - 1;                             // last tile whose group starts at or before this CTA
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (group_start(g, mid, row_weight, total, spare, fits32) <= cta) lo = mid; else hi = mid - 1;
         }
+        const int first = group_start(g, lo, row_weight, total, spare, fits32);
+        const int next_first = lo + 1 < n_tiles ? group_start(g, lo + 1, row_weight, total, spare, fits32) : n_ctas;
+        if (g.mode == MODE_SDD) { sp_rb = lo; sp_nt = 0; }
+        else { sp_rb = lo / g.n_col_tiles; sp_nt = lo - sp_rb * g.n_col_tiles; }
+        const int nk = g.mode == MODE_DSD ? count(g, sp_rb) : nk_uniform;
+        int parts = next_first - first;
+        if (parts > nk) parts = nk;                               // never more CTAs on a tile than it has K tiles
+        sp_owner = first;
+        sp_part = cta - first;
+        sp_parts = sp_part < parts ? parts : 0;
     }
     __device__ __forceinline__ void fill(const GemmArgs& g, Seg& s, int row_block, int n_tile) const {
         if (g.mode == MODE_SDD) {
@@ -214,20 +209,18 @@ struct WorkIter {
                 if (s.nk == 0) continue;          // empty row blocks are zero-filled by the epilogue warps
                 s.i0 = 0;
                 s.i1 = s.nk;
-                s.tile_end = 0;
+                s.owner = 0; s.parts = 1; s.part = 0;
                 ++pass;
                 return true;
             }
             return false;
         }
-        if (u >= u_end) return false;
-        fill(g, s, rb, nt);
-        s.i0 = i0;
-        const long long room = u_end - u;
-        s.i1 = (room >= s.nk - i0) ? s.nk : i0 + int(room);
-        s.tile_end = u - i0 + s.nk;
-        u += s.i1 - i0;
-        if (s.i1 == s.nk) next_tile(g); else i0 = s.i1;
+        if (sp_parts == 0) return false;
+        fill(g, s, sp_rb, sp_nt);
+        s.i0 = s.nk * sp_part / sp_parts;
+        s.i1 = s.nk * (sp_part + 1) / sp_parts;
+        s.owner = sp_owner; s.parts = sp_parts; s.part = sp_part;
+        sp_parts = 0;                             // one segment per CTA
         return true;
     }
 };
@@ -366,26 +359,15 @@ __device__ unsigned long long sd_timing[1024][8];
 #define SD_STAMP(slot) do {} while (0)
 #endif
 
-// ------------------------------------------------------------------ shared tiles of the equal-share schedule
-// CTA whose unit range [range_start(c), range_start(c + 1)) contains unit `first`.
-__device__ __forceinline__ int tile_owner(long long total, long long first, int n_ctas) {
-    int c = int(first * n_ctas / total);
-    if (c >= n_ctas) c = n_ctas - 1;
-    while (c + 1 < n_ctas && WorkIter::range_start(total, c + 1, n_ctas) <= first) ++c;
-    while (c > 0 && WorkIter::range_start(total, c, n_ctas) > first) --c;
-    return c;
-}
-
-// All CTAs whose ranges intersect one output tile have parked their partial accumulators (the owner of the tile's
-// first unit in its slot 1, the others in their slot 0) and counted themselves in arrive[owner].  Once the count is
-// complete, every participant adds up a different share of the tile's 32x32 units over all partials, in CTA order
-// (so the result does not depend on timing), scales, converts and stores it.  The last participant to finish clears
-// the two counters, which leaves the workspace ready for the next launch.
-__device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, long long total, int cta, int n_ctas, int etid,
-                                   volatile int* abort_flag) {
-    const int owner = tile_owner(total, seg.tile_end - seg.nk, n_ctas);
-    const int last = tile_owner(total, seg.tile_end - 1, n_ctas);
-    const int P = last - owner + 1, my_index = cta - owner;
+// ------------------------------------------------------------------ shared tiles of the split schedule
+// The CTAs seg.owner .. seg.owner + seg.parts - 1 have each parked the partial accumulator of their part of one
+// output tile in their workspace slot and counted themselves in arrive[owner].  Once the count is complete, every
+// one of them adds up a different share of the tile's 32x32 units over all partials, in CTA order (so the result
+// does not depend on timing), scales, converts and stores it.  The last one to finish clears the two counters,
+// which leaves the workspace ready for the next launch.
+__device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int etid, volatile int* abort_flag) {
+    const int owner = seg.owner, P = seg.parts, my_index = seg.part;
+    const int last = owner + P - 1;
     int* arrive = g.ws_flags + owner;
     int* done = g.ws_flags + WS_MAX_CTAS + owner;
     bool ok = true;
@@ -409,7 +391,7 @@ __device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, long long 
             int n = 0;
             for (; pc <= last && n < 4; ++pc)
                 src[n++] = reinterpret_cast<const float4*>(
-                    g.ws_slots + (size_t(2 * pc) + (pc == owner ? 1 : 0)) * WS_SLOT_FLOATS + unit_off);
+                    g.ws_slots + size_t(pc) * WS_SLOT_FLOATS + unit_off);
             float4 v[4][2];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -619,15 +601,14 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         int acc = 0;
         uint32_t acc_phase = 0;
         Seg w;
-        // Tiles this CTA shares with others: at most the one its range starts inside (slot 0) and the one its range
-        // ends inside (slot 1).  Their partial accumulators are reduced after the segment loop.
-        Seg shared[2];
-        int n_shared = 0;
+        // Split schedule: the tile this CTA shares with the rest of its group; reduced after the segment loop.
+        Seg shared;
+        bool has_shared = false;
         const uint32_t stage_base = smem_u32(xpose) + (uint32_t(quad) << 12);   // two 2 KiB buffers per epilogue warp
         int n_stores = 0;
         bool alive = true;
         while (alive && it.next(g, w)) {
-            const bool partial = w.i0 > 0 || w.i1 < w.nk;
+            const bool partial = w.parts > 1;
             const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
             if (!epilogue_all(ok)) { alive = false; break; }     // uniform decision of the 128 epilogue threads
             tc_fence_after();
@@ -636,7 +617,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             const int nchunks = w.b_row1 >= 0 ? 8 : 4;
             const bool transposed = !partial && vec_t_ok && w.a_row + 128 <= g.MM;
             float* slot = nullptr;
-            if (partial) slot = g.ws_slots + (size_t(2 * cta) + (w.i0 > 0 ? 0 : 1)) * WS_SLOT_FLOATS;
+            if (partial) slot = g.ws_slots + size_t(cta) * WS_SLOT_FLOATS;
             // chunk c+1 is in flight from TMEM while chunk c is converted and stored
             uint32_t rbuf[2][32];
             tmem_ld_32x32(taddr, rbuf[0]);
@@ -715,8 +696,9 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             if (partial) {
                 __threadfence();                                 // partial tile visible before the arrival count
                 epilogue_sync();
-                if (etid == 0) atomicAdd(g.ws_flags + tile_owner(it.total, w.tile_end - w.nk, it.n_eff), 1);
-                shared[n_shared++] = w;
+                if (etid == 0) atomicAdd(g.ws_flags + w.owner, 1);
+                shared = w;
+                has_shared = true;
             }
         }
 #ifdef SD_TIMING
@@ -724,8 +706,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
 #endif
         if (g.tma_store && lane == 0) bulk_wait_all();           // staged results are in global memory
         __syncwarp();
-        for (int t = 0; alive && t < n_shared; ++t)
-            alive = reduce_shared_tile(g, shared[t], it.total, cta, it.n_eff, etid, abort_flag);
+        if (alive && has_shared) alive = reduce_shared_tile(g, shared, etid, abort_flag);
 #ifdef SD_TIMING
         if (etid == 0) { SD_STAMP(3); sd_timing[blockIdx.x][7] = clock64(); }
 #endif
@@ -915,11 +896,10 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         g.items = v.sdd_items; g.n_items = v.header + H_SDD_ITEMS;
         if (zero_dropped) { g.zero_pairs = v.drop_pairs; g.n_zero = v.header + H_NDROP; }
     }
-    // Schedule: with fewer output tiles than SMs, whole tiles would leave SMs idle, so the K-tile stream is
-    // cut into equal shares instead (needs the workspace).  Otherwise whole tiles, heaviest first.
+    // Schedule: with fewer output tiles than SMs, whole tiles would leave SMs idle, so each tile's
+    // reduction is split over a group of CTAs instead (needs the workspace).  Otherwise whole tiles, heaviest first.
     const long long tiles_upper = mode == MODE_SDD ? (long long)g.n_row_blocks * ((((N + 127) / 128) + 1) / 2)
                                                    : (long long)g.n_row_blocks * g.n_col_tiles;
-    const long long units_upper = tiles_upper * ((K + 127) / 128);
     if (max_ctas > 0) {
         if (tiles_upper > max_ctas)
             return fail(SD_ERR_TOO_LARGE,
@@ -938,7 +918,6 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     if (workspace && tiles_upper * 2 <= grid && k_tiles >= split_min_k_tiles) {
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(SD_ERR_LAYOUT, "workspace must be 16-byte aligned");
         if (grid > WS_MAX_CTAS) grid = WS_MAX_CTAS;
-        if (units_upper < grid) grid = int(units_upper);
         g.split = 1;
         g.ws_flags = static_cast<int*>(workspace);
         g.ws_slots = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + WS_FLAG_BYTES);
@@ -978,11 +957,11 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
 }
 
 // ------------------------------------------------------------------ built-in scratch
-// Scratch of sd_gemm_dsd_static_scratch(): the same layout as a caller's workspace (counters, then two fp32
-// partial tiles per CTA) for at most kStaticScratchSlots CTAs: 8 KiB + 2 x 64 x 128 KiB = 16 392 KiB of device
+// Scratch of sd_gemm_dsd_static_scratch(): the same layout as a caller's workspace (counters, then one fp32
+// partial tile per CTA) for at most kStaticScratchSlots CTAs: 8 KiB + 64 x 128 KiB = 8 200 KiB of device
 // memory that every GPU which loads this library holds until the process exits.
 constexpr int kStaticScratchSlots = 64;
-static __device__ __align__(256) unsigned char sd_static_scratch[WS_FLAG_BYTES + 2 * kStaticScratchSlots * WS_SLOT_BYTES];
+static __device__ __align__(256) unsigned char sd_static_scratch[WS_FLAG_BYTES + kStaticScratchSlots * WS_SLOT_BYTES];
 
 // Device address of the array on the current device.  In host code the array's name is only a stand-in for
 // the symbol, not a device pointer: the address has to be asked for, once per device, with that device current.
@@ -1040,7 +1019,7 @@ size_t sd_workspace_bytes(void) {
     int sms = 0;
     if (sd::sm_count_current_device(&sms) != SD_OK) return 0;
     if (sms > sd::WS_MAX_CTAS) sms = sd::WS_MAX_CTAS;
-    return sd::WS_FLAG_BYTES + 2 * size_t(sms) * sd::WS_SLOT_BYTES;
+    return sd::WS_FLAG_BYTES + size_t(sms) * sd::WS_SLOT_BYTES;
 }
 
 int sd_workspace_init(void* workspace, void* stream) {

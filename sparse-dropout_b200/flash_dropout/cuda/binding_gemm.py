@@ -147,7 +147,7 @@ _workspaces: dict = {}
 
 
 def workspace(device: torch.device) -> torch.Tensor:
-    """Scratch for the equal-share schedule of the GEMM kernel, one per (device, current stream).
+    """Scratch for the split schedule of the GEMM kernel, one per (device, current stream).
 
     Launches that can overlap on the GPU must not share a workspace, hence the stream in the key.
     """

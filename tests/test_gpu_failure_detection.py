@@ -1,6 +1,6 @@
 """Failure detection without a GPU fault: device-side waits are bounded and report through a status word.
 
-The waits of the GEMM kernel (mbarrier waits between its roles, the arrival counter of the equal-share schedule) all go
+The waits of the GEMM kernel (mbarrier waits between its roles, the arrival counter of the split schedule) all go
 through two helpers that give up after a time limit, record a code and let the kernel finish normally.  The self-test
 kernel runs exactly those helpers against a barrier nobody arrives on and a counter nobody increments, with a 20 ms
 limit; afterwards the context must still run kernels."""

@@ -38,7 +38,7 @@ ps = [0.0, 0.1, 0.2, 0.5, 0.9, 0.99, 0.999]
 
 @pytest.mark.parametrize("mnk,p", list(product(mnks, ps)))
 def test_blockwise_dropout_matmul_reference_grid(built_lib, mnk, p):
-    """Through the reference-shaped GEMM facade (equal-share schedule with the cached workspace)."""
+    """Through the reference-shaped GEMM facade (split schedule with the cached workspace)."""
     from flash_dropout.cuda.binding_gemm import GEMM
     M, N, K = mnk
     x, w, dy = _inputs(M, N, K, seed=0)
