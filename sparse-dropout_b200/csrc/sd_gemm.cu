@@ -10,14 +10,16 @@
 //           zero-filled by the otherwise idle epilogue warps
 //           (flash_dropout/cuda/src/matmul_sdd.cuh:18-67 launches a CTA per tile, kept or not)
 //
-// CTA = 6 warps on one SM, 128 x 256 output tile, 64-wide K stages in a 4-deep TMA ring:
+// CTA = 10 warps on one SM, 128 x 256 output tile, 64-wide K stages in a 4-deep TMA ring:
 //   warp 0    producer : one lane issues cp.async.bulk.tensor loads (no multicast) into
 //                        128B-swizzled shared memory, completion on `full` mbarriers
 //   warp 1    MMA      : one lane issues tcgen05.mma (M128 N256 K16, fp32 accumulate in TMEM),
 //                        tcgen05.commit releases ring stages and publishes accumulators
-//   warps 2-5 epilogue : tcgen05.ld the accumulator (two 256-column TMEM buffers, so the
+//   warps 2-9 epilogue : tcgen05.ld the accumulator (two 256-column TMEM buffers, so the
 //                        epilogue of tile i overlaps the main loop of tile i+1), scale, convert,
-//                        store to global memory
+//                        stage in shared memory, TMA-store to global memory.  Two warps per TMEM
+//                        lane quadrant, each with half of the tile's columns: with a short reduction
+//                        (K of a few hundred) the epilogue of a tile takes as long as its main loop
 // Both operands may be K-major (reduction dimension contiguous) or MN-major; that is the
 // (row|col)-major x (row|col)-major operand matrix of flash_dropout/cuda/src/gemm_binding.cu:51-53.
 //
@@ -53,9 +55,16 @@ constexpr int B_HALF_BYTES = B_BYTES / 2;   // one 128-row half of the B tile
 constexpr int MN_ATOM_BYTES = 64 * BK * 2;  // 64 MN-elements x 64 K-rows, one MN-major TMA box
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TILE_SMEM = STAGES * STAGE_BYTES;          // 192 KiB
-constexpr int XPOSE_BYTES = 32 * 128 * 2;                // one 32-column chunk of a tile, transposed (fp16/bf16)
-constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/ + 2 * XPOSE_BYTES;
-constexpr int GEMM_THREADS = 192;
+// Epilogue warps: four (one per TMEM lane quadrant, two staging buffers each) or eight (two per quadrant, each with
+// half of a tile's columns and one staging buffer); the launch's block size says which.  Eight shorten the epilogue
+// of a tile, which decides short reductions (K of a few hundred: the epilogue takes as long as the main loop) and
+// small launches (one tile per CTA, nothing to hide the epilogue behind); with a long reduction the four extra
+// warps only take issue slots from the producer and MMA warps.
+constexpr int MAX_EPI_WARPS = 8;
+constexpr int STAGING_BYTES = 8 * 4096;                  // TMA-store staging
+constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/ + STAGING_BYTES;
+static_assert(GEMM_SMEM <= 227 * 1024, "over the shared memory of one CTA");
+constexpr int GEMM_MAX_THREADS = 64 + MAX_EPI_WARPS * 32;
 constexpr int TMEM_COLS = 512;
 
 // Workspace of the split schedule: flags first, then one fp32 partial tile per CTA.
@@ -110,6 +119,7 @@ struct Seg {
 struct WorkIter {
     int t, n_tiles, stride, pass;   // whole tiles: this CTA's index, tile count, gridDim.x, next pass
     int nk_uniform;              // dense / SDD: K tiles per output tile
+    int full_per_row, n_full;    // whole tiles: full-width column tiles per row block, and in total
     int sp_rb, sp_nt, sp_owner, sp_parts, sp_part;   // split: this CTA's one segment; sp_parts == 0: none
     bool split, snake;
 
@@ -146,8 +156,10 @@ struct WorkIter {
         snake = g.mode == MODE_DSD && __ldg(g.h_nnz) != g.n_row_blocks * __ldg(g.h_max);
         sp_rb = sp_nt = sp_owner = sp_part = 0;
         sp_parts = 0;
-        if (!split || n_tiles == 0 || n_tiles > n_ctas) return;
         const bool ragged = (g.n_col_tiles - 1) * BN + 128 >= g.NN;
+        full_per_row = (ragged && g.n_col_tiles > 1) ? g.n_col_tiles - 1 : g.n_col_tiles;
+        n_full = g.n_row_blocks * full_per_row;
+        if (!split || n_tiles == 0 || n_tiles > n_ctas) return;
         const int row_weight = 2 * g.n_col_tiles - (ragged ? 1 : 0);
         const unsigned total = work_before(g, n_tiles, row_weight);
         if (total == 0) return;                                   // everything dropped: only zero-filling is left
@@ -203,8 +215,12 @@ struct WorkIter {
                 if (g.mode == MODE_SDD) {
                     fill(g, s, tile, 0);
                 } else {
-                    const int rbi = tile / g.n_col_tiles;
-                    fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, tile - rbi * g.n_col_tiles);
+                    // list order: row blocks heaviest first, and when the last column tile is only 128 wide (half the
+                    // work), all full-width tiles before all narrow ones, so that no CTA collects only full-width tiles
+                    int rbi, nt;
+                    if (tile < n_full) { rbi = tile / full_per_row; nt = tile - rbi * full_per_row; }
+                    else { rbi = tile - n_full; nt = g.n_col_tiles - 1; }
+                    fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, nt);
                 }
                 if (s.nk == 0) continue;          // empty row blocks are zero-filled by the epilogue warps
                 s.i0 = 0;
@@ -239,52 +255,48 @@ __device__ __forceinline__ unsigned short cvt1(float a, int is_bf16) {
     return __half_as_ushort(__float2half_rn(a));
 }
 
+// Scales 32 fp32 values and packs them into 16 words of two 16-bit results (lower half = the earlier value).
+// One branch around all sixteen conversions: fp32 -> 16-bit conversions issue at a fraction of the ALU rate, and a
+// per-value choice between the two formats would run both.
+__device__ __forceinline__ void convert_chunk(const uint32_t (&r)[32], float scale, int is_bf16, uint32_t (&p)[16]) {
+    if (is_bf16) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;"
+                         : "=r"(p[j])
+                         : "f"(__uint_as_float(r[2 * j + 1]) * scale), "f"(__uint_as_float(r[2 * j]) * scale));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            asm volatile("cvt.rn.f16x2.f32 %0, %1, %2;"
+                         : "=r"(p[j])
+                         : "f"(__uint_as_float(r[2 * j + 1]) * scale), "f"(__uint_as_float(r[2 * j]) * scale));
+    }
+}
+
 // Thread holds 32 consecutive fp32 values of output row `row`, columns [col, col+32).
 __device__ __forceinline__ void store_chunk(const GemmArgs& g, bool vec_ok, int row, int col, const uint32_t (&r)[32]) {
     if (row >= g.MM || col >= g.NN) return;
     unsigned short* C = static_cast<unsigned short*>(g.C);
     if (vec_ok && col + 32 <= g.NN) {
         uint4* dst = reinterpret_cast<uint4*>(C + (long long)row * g.c_rs + col);
+        uint32_t p[16];
+        convert_chunk(r, g.scale, g.is_bf16, p);
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = pack2(__uint_as_float(r[8 * v + 0]) * g.scale, __uint_as_float(r[8 * v + 1]) * g.scale, g.is_bf16);
-            o.y = pack2(__uint_as_float(r[8 * v + 2]) * g.scale, __uint_as_float(r[8 * v + 3]) * g.scale, g.is_bf16);
-            o.z = pack2(__uint_as_float(r[8 * v + 4]) * g.scale, __uint_as_float(r[8 * v + 5]) * g.scale, g.is_bf16);
-            o.w = pack2(__uint_as_float(r[8 * v + 6]) * g.scale, __uint_as_float(r[8 * v + 7]) * g.scale, g.is_bf16);
-            dst[v] = o;
-        }
+        for (int v = 0; v < 4; ++v) dst[v] = make_uint4(p[4 * v], p[4 * v + 1], p[4 * v + 2], p[4 * v + 3]);
     } else {
         // ragged edge, unaligned rows, or a column-major result (consecutive lanes = consecutive
         // rows, so a column-major store is a 64-byte contiguous segment per warp instruction)
+        uint32_t p[16];
+        convert_chunk(r, g.scale, g.is_bf16, p);
 #pragma unroll
         for (int j = 0; j < 32; ++j)
             if (col + j < g.NN)
-                C[(long long)row * g.c_rs + (long long)(col + j) * g.c_cs] = cvt1(__uint_as_float(r[j]) * g.scale, g.is_bf16);
+                C[(long long)row * g.c_rs + (long long)(col + j) * g.c_cs] = (unsigned short)(p[j >> 1] >> (16 * (j & 1)));
     }
 }
 
-// Column-major result (row stride 1): the 32-column chunk is transposed through shared memory so that global
-// stores are 256-byte rows of the result instead of 2-byte scalars.  `xs` is XPOSE_BYTES of shared memory owned
-// by the epilogue group; all 128 epilogue threads call this together.
-__device__ __forceinline__ void store_chunk_transposed(const GemmArgs& g, unsigned short* xs, int etid, int row0, int col,
-                                                       const uint32_t (&r)[32]) {
-    // xs[j][k]: j = column inside the chunk, k = row inside the tile
-#pragma unroll
-    for (int j = 0; j < 32; ++j) xs[j * 128 + etid] = cvt1(__uint_as_float(r[j]) * g.scale, g.is_bf16);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    unsigned short* C = static_cast<unsigned short*>(g.C);
-    const int kc = (etid & 15) * 8, jsub = etid >> 4;
-#pragma unroll
-    for (int pass = 0; pass < 4; ++pass) {
-        const int j = pass * 8 + jsub;
-        if (col + j < g.NN && row0 + kc < g.MM)
-            *reinterpret_cast<uint4*>(C + (long long)(col + j) * g.c_cs + row0 + kc) =
-                *reinterpret_cast<const uint4*>(xs + j * 128 + kc);
-    }
-}
-
-// Zero a 128 x 128 output tile with the 128 epilogue threads (tid in [0,128)).
+// Zero a 128 x 128 output tile with 128 threads (tid in [0,128)): one half of the epilogue group.
 __device__ __forceinline__ void zero_tile(const GemmArgs& g, bool vec_ok, bool vec_t_ok, int tid, int row0, int col0) {
     unsigned short* C = static_cast<unsigned short*>(g.C);
     if (vec_ok && row0 + 128 <= g.MM && col0 + 128 <= g.NN) {
@@ -311,17 +323,26 @@ __device__ __forceinline__ void zero_tile(const GemmArgs& g, bool vec_ok, bool v
 }
 
 // ------------------------------------------------------------------ epilogue-group helpers
-// The four epilogue warps (128 threads) synchronise on named barrier 1, never on barrier 0.
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ bool epilogue_all(bool ok) {
+// Before a warp refills a TMA-store staging buffer: the store that last used it has read it.
+__device__ __forceinline__ void wait_staging_free(bool two_bufs, int n_stores, int lane) {
+    if (n_stores < (two_bufs ? 2 : 1)) return;
+    if (lane == 0) {
+        if (two_bufs) bulk_wait_read<1>(); else bulk_wait_read<0>();
+    }
+    __syncwarp();
+}
+
+// The epilogue warps synchronise on named barrier 1, never on barrier 0.
+__device__ __forceinline__ void epilogue_sync(int n_threads) { asm volatile("bar.sync 1, %0;" ::"r"(n_threads) : "memory"); }
+__device__ __forceinline__ bool epilogue_all(bool ok, int n_threads) {
     uint32_t r;
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(r)
-        : "r"(uint32_t(ok))
+        : "r"(uint32_t(ok)), "r"(n_threads)
         : "memory");
     return r != 0;
 }
@@ -350,7 +371,7 @@ __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_f
 
 #ifdef SD_TIMING
 // Development aid (not compiled into the product): per-CTA timestamps of one launch.
-__device__ unsigned long long sd_timing[1024][8];
+__device__ unsigned long long sd_timing[1024][16];
 #define SD_STAMP(slot)                                                                     \
     do {                                                                                   \
         sd_timing[blockIdx.x][slot] = global_timer_ns();                                   \
@@ -365,67 +386,59 @@ __device__ unsigned long long sd_timing[1024][8];
 // one of them adds up a different share of the tile's 32x32 units over all partials, in CTA order (so the result
 // does not depend on timing), scales, converts and stores it.  The last one to finish clears the two counters,
 // which leaves the workspace ready for the next launch.
-__device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int etid, volatile int* abort_flag) {
+__device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int eidx, int epi_threads, volatile int* abort_flag) {
     const int owner = seg.owner, P = seg.parts, my_index = seg.part;
     const int last = owner + P - 1;
     int* arrive = g.ws_flags + owner;
     int* done = g.ws_flags + WS_MAX_CTAS + owner;
     bool ok = true;
-    if (etid == 0) ok = counter_wait(arrive, P, abort_flag, g.status, ST_FIXUP);
-    if (!epilogue_all(ok)) return false;
+    if (eidx == 0) ok = counter_wait(arrive, P, abort_flag, g.status, ST_FIXUP);
+    if (!epilogue_all(ok, epi_threads)) return false;
 #ifdef SD_TIMING
-    if (etid == 0) SD_STAMP(5);
+    if (eidx == 0) SD_STAMP(5);
 #endif
     const int n_units = (seg.b_row1 >= 0 ? 8 : 4) * 4;
     unsigned short* C = static_cast<unsigned short*>(g.C);
     const bool quad_ok = g.c_cs == 1 && (g.c_rs & 3) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 7) == 0;
-    // A unit is 8 four-column pieces x 32 rows of 16 bytes.  All 128 threads share each unit (two pieces per thread) and keep the
-    // loads of four partial tiles in flight at once, so the depth of the dependent chain is P / 4 round trips.
+    // A unit is 8 four-column pieces x 32 rows of 16 bytes, shared by all epilogue threads.  The loads of four partial
+    // tiles are kept in flight at once, so the depth of the dependent chain is P / 4 round trips.
     for (int uu = my_index; uu < n_units; uu += P) {
-        const int c = uu >> 2, q = uu & 3;
-        float4 acc2[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-        const size_t unit_off = size_t(uu) * 1024 + size_t(etid) * 4;
+      const int c = uu >> 2, q = uu & 3;
+      for (int e = eidx; e < 256; e += epi_threads) {            // piece index inside the unit: [4-column piece][row]
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const size_t unit_off = size_t(uu) * 1024 + size_t(e) * 4;
         int pc = owner;
         while (pc <= last) {
             const float4* src[4];
             int n = 0;
             for (; pc <= last && n < 4; ++pc)
-                src[n++] = reinterpret_cast<const float4*>(
-                    g.ws_slots + size_t(pc) * WS_SLOT_FLOATS + unit_off);
-            float4 v[4][2];
+                src[n++] = reinterpret_cast<const float4*>(g.ws_slots + size_t(pc) * WS_SLOT_FLOATS + unit_off);
+            float4 v[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                if (i < n) { v[i][0] = __ldcg(src[i]); v[i][1] = __ldcg(src[i] + 128); }
+                if (i < n) v[i] = __ldcg(src[i]);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                if (i < n) {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        acc2[h].x += v[i][h].x; acc2[h].y += v[i][h].y; acc2[h].z += v[i][h].z; acc2[h].w += v[i][h].w;
-                    }
-                }
+                if (i < n) { acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w; }
         }
+        const int row = seg.a_row + q * 32 + (e & 31);
+        const int col = (c < 4 ? seg.b_row0 + c * 32 : seg.b_row1 + (c - 4) * 32) + (e >> 5) * 4;
+        if (row >= g.MM || col >= g.NN) continue;
+        const float f[4] = {acc.x * g.scale, acc.y * g.scale, acc.z * g.scale, acc.w * g.scale};
+        if (quad_ok && col + 4 <= g.NN) {
+            uint2 o;
+            o.x = pack2(f[0], f[1], g.is_bf16);
+            o.y = pack2(f[2], f[3], g.is_bf16);
+            *reinterpret_cast<uint2*>(C + (long long)row * g.c_rs + col) = o;
+        } else {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int e = etid + 128 * h;                        // piece index inside the unit: [4-column piece][row]
-            const int row = seg.a_row + q * 32 + (e & 31);
-            const int col = (c < 4 ? seg.b_row0 + c * 32 : seg.b_row1 + (c - 4) * 32) + (e >> 5) * 4;
-            if (row >= g.MM || col >= g.NN) continue;
-            const float f[4] = {acc2[h].x * g.scale, acc2[h].y * g.scale, acc2[h].z * g.scale, acc2[h].w * g.scale};
-            if (quad_ok && col + 4 <= g.NN) {
-                uint2 o;
-                o.x = pack2(f[0], f[1], g.is_bf16);
-                o.y = pack2(f[2], f[3], g.is_bf16);
-                *reinterpret_cast<uint2*>(C + (long long)row * g.c_rs + col) = o;
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (col + j < g.NN) C[(long long)row * g.c_rs + (long long)(col + j) * g.c_cs] = cvt1(f[j], g.is_bf16);
-            }
+            for (int j = 0; j < 4; ++j)
+                if (col + j < g.NN) C[(long long)row * g.c_rs + (long long)(col + j) * g.c_cs] = cvt1(f[j], g.is_bf16);
         }
+      }
     }
-    epilogue_sync();                                             // every thread has read its share
-    if (etid == 0) {
+    epilogue_sync(epi_threads);                                  // every thread has read its share
+    if (eidx == 0) {
         __threadfence();
         if (atomicAdd(done, 1) == P - 1) {
             flag_set(arrive, 0);
@@ -437,22 +450,25 @@ __device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int etid, 
 
 // ------------------------------------------------------------------ the kernel
 template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_MAX_THREADS, 1)
 sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                        const __grid_constant__ CUtensorMap tmapC, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t tiles = (raw_addr + 1023u) & ~1023u;   // 128B swizzle atoms need 1024-byte alignment
     uint8_t* aligned = smem_raw + (tiles - raw_addr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + TILE_SMEM + 2 * XPOSE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + TILE_SMEM + STAGING_BYTES);
     // bars[0..3] full, [4..7] empty, [8..9] tmem_full, [10..11] tmem_empty, [12] unused
     const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
-    unsigned short* xpose = reinterpret_cast<unsigned short*>(aligned + TILE_SMEM);   // 16 KiB epilogue staging, 1024-aligned
+    uint8_t* staging = aligned + TILE_SMEM;   // 32 KiB of TMA-store staging, 1024-aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SD_TIMING
+    if (threadIdx.x == 0) SD_STAMP(8);
+#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -461,7 +477,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, 4);
+            mbar_init(bar_tempty + 8 * a, (blockDim.x >> 5) - 2);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -576,21 +592,26 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         }
         __syncwarp();
     } else {
-        // ============================== epilogue (warps 2..5 own TMEM lane quadrants 2,3,0,1)
-        const int quad = warp & 3;
+        // ============================== epilogue
+        // Warps 2..5 and 6..9 own TMEM lane quadrants 2,3,0,1 (a warp reaches only the 32 lanes of quadrant warp % 4);
+        // the first four take the lower half of a tile's column chunks, the other four the upper half.
+        const int epi_warps = (blockDim.x >> 5) - 2, epi_halves = epi_warps >> 2, epi_threads = epi_warps << 5;
+        const bool two_bufs = epi_warps == 4;
+        const int quad = warp & 3, half = (warp - 2) >> 2;       // half is 0 throughout with four epilogue warps
         const int etid = quad * 32 + lane;   // 0..127, also the row inside the tile this thread owns
+        const int eidx = half * 128 + etid;  // 0..255, index inside the epilogue group
         const bool aligned16 = (reinterpret_cast<uintptr_t>(g.C) & 15) == 0;
         const bool vec_ok = g.c_cs == 1 && (g.c_rs & 7) == 0 && aligned16;      // row-major result, 16-byte rows
         const bool vec_t_ok = g.c_rs == 1 && (g.c_cs & 7) == 0 && aligned16;    // column-major result
         // Output that no unit covers is zero-filled here, before the first accumulator is ready.
         if (g.mode == MODE_SDD && g.n_zero) {
             const int nz = __ldg(g.n_zero);
-            for (int z = cta; z < nz; z += n_ctas)
+            for (int z = epi_halves * cta + half; z < nz; z += epi_halves * n_ctas)
                 zero_tile(g, vec_ok, vec_t_ok, etid, __ldg(g.zero_pairs + 2 * z) * 128, __ldg(g.zero_pairs + 2 * z + 1) * 128);
         } else if (g.mode == MODE_DSD) {
             // row blocks with nothing kept: their 128x128 output tiles are spread over all CTAs
             const int ncol = (g.NN + 127) >> 7;
-            for (int z = cta; z < g.n_row_blocks * ncol; z += n_ctas) {
+            for (int z = epi_halves * cta + half; z < g.n_row_blocks * ncol; z += epi_halves * n_ctas) {
                 const int rb = z / ncol;
                 if (__ldg(g.list_ptr + rb + 1) == __ldg(g.list_ptr + rb))
                     zero_tile(g, vec_ok, vec_t_ok, etid, rb * 128, (z - rb * ncol) * 128);
@@ -604,28 +625,22 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         // Split schedule: the tile this CTA shares with the rest of its group; reduced after the segment loop.
         Seg shared;
         bool has_shared = false;
-        const uint32_t stage_base = smem_u32(xpose) + (uint32_t(quad) << 12);   // two 2 KiB buffers per epilogue warp
+        const uint32_t stage_base = smem_u32(staging) + uint32_t(warp - 2) * (two_bufs ? 8192u : 4096u);   // this warp's staging
         int n_stores = 0;
         bool alive = true;
         while (alive && it.next(g, w)) {
             const bool partial = w.parts > 1;
             const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
-            if (!epilogue_all(ok)) { alive = false; break; }     // uniform decision of the 128 epilogue threads
+            if (!epilogue_all(ok, epi_threads)) { alive = false; break; }     // uniform decision of all epilogue threads
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
             const int row = w.a_row + etid;
-            const int nchunks = w.b_row1 >= 0 ? 8 : 4;
-            const bool transposed = !partial && vec_t_ok && w.a_row + 128 <= g.MM;
+            const int nchunks = (w.b_row1 >= 0 ? 8 : 4) >> (epi_halves - 1);   // this warp's share: chunks [c0, c0 + nchunks)
+            const int c0 = half * nchunks;
             float* slot = nullptr;
             if (partial) slot = g.ws_slots + size_t(cta) * WS_SLOT_FLOATS;
-            // chunk c+1 is in flight from TMEM while chunk c is converted and stored
-            uint32_t rbuf[2][32];
-            tmem_ld_32x32(taddr, rbuf[0]);
-            tmem_ld_wait();
-#pragma unroll 2
-            for (int c = 0; c < nchunks; ++c) {
-                uint32_t (&r)[32] = rbuf[c & 1];
-                if (c + 1 < nchunks) tmem_ld_32x32(taddr + (c + 1) * 32, rbuf[(c + 1) & 1]);
+            // One chunk: 32 rows x 32 fp32 columns in r, thread = row.  `odd` chunks close a pair.
+            auto process = [&](const int c, const uint32_t (&r)[32]) {
                 const int col = c < 4 ? w.b_row0 + c * 32 : w.b_row1 + (c - 4) * 32;
                 if (partial) {
                     // unit (chunk c, quadrant) = 32 rows x 32 fp32 columns stored as [4-column piece][row]: each warp
@@ -634,58 +649,66 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
 #pragma unroll
                     for (int v = 0; v < 8; ++v) __stcg(dst + v * 32, make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
                 } else if (g.tma_store == 1) {
-                    // this warp's 32 rows x 32 columns go to its own 2 KiB staging buffer (64-byte rows, 16-byte pieces
-                    // XOR-swizzled as CU_TENSOR_MAP_SWIZZLE_64B expects) and from there to global memory by one TMA store
-                    const uint32_t buf = stage_base + ((n_stores & 1) << 11);
-                    if (n_stores >= 2) {
-                        if (lane == 0) bulk_wait_read<1>();      // the store that last used this buffer has read it
-                        __syncwarp();
-                    }
-                    const uint32_t rowaddr = buf + lane * 64, sw = (lane >> 1) & 3;
+                    // Two chunks (32 rows x 64 columns) share the 4 KiB staging buffer of 128-byte rows, 16-byte pieces
+                    // XOR-swizzled as CU_TENSOR_MAP_SWIZZLE_128B expects, and leave by one TMA store: the proxy fence and
+                    // the store's issue cost a few hundred cycles, so they are paid once per pair.
+                    const uint32_t buf = stage_base + (two_bufs ? ((n_stores & 1) << 12) : 0);
+                    if (!(c & 1)) wait_staging_free(two_bufs, n_stores, lane);
+                    const uint32_t rowaddr = buf + lane * 128, sw = lane & 7, piece0 = (c & 1) << 2;
+                    uint32_t p[16];
+                    convert_chunk(r, g.scale, g.is_bf16, p);
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const uint32_t p0 = pack2(__uint_as_float(r[8 * v + 0]) * g.scale, __uint_as_float(r[8 * v + 1]) * g.scale, g.is_bf16);
-                        const uint32_t p1 = pack2(__uint_as_float(r[8 * v + 2]) * g.scale, __uint_as_float(r[8 * v + 3]) * g.scale, g.is_bf16);
-                        const uint32_t p2 = pack2(__uint_as_float(r[8 * v + 4]) * g.scale, __uint_as_float(r[8 * v + 5]) * g.scale, g.is_bf16);
-                        const uint32_t p3 = pack2(__uint_as_float(r[8 * v + 6]) * g.scale, __uint_as_float(r[8 * v + 7]) * g.scale, g.is_bf16);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((v ^ sw) << 4)), "r"(p0), "r"(p1),
-                                     "r"(p2), "r"(p3)
+                    for (int v = 0; v < 4; ++v)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + (((piece0 + v) ^ sw) << 4)),
+                                     "r"(p[4 * v]), "r"(p[4 * v + 1]), "r"(p[4 * v + 2]), "r"(p[4 * v + 3])
                                      : "memory");
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tmapC, buf, col, w.a_row + quad * 32);
-                        bulk_commit();
-                    }
-                    ++n_stores;
+                    if (c & 1) {
+                        fence_proxy_async();
+                                                __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmapC, buf, col - 32, w.a_row + quad * 32);
+                            bulk_commit();
+                        }
+                        ++n_stores;
+                                            }
                 } else if (g.tma_store == 2) {
-                    // column-major result = row-major transpose: the warp's 32 rows x 32 columns are staged as
-                    // [column][row] (64-byte rows of the transpose, same swizzle) and stored by one TMA store
-                    const uint32_t buf = stage_base + ((n_stores & 1) << 11);
-                    if (n_stores >= 2) {
-                        if (lane == 0) bulk_wait_read<1>();
-                        __syncwarp();
-                    }
-                    const uint32_t lane_off = ((lane & 7) << 1), chunk = lane >> 3;
+                    // column-major result = row-major transpose: the warp's 32 rows x 64 columns are staged as
+                    // [column][row] (64-byte rows of the transpose, CU_TENSOR_MAP_SWIZZLE_64B) and stored by one TMA store
+                    const uint32_t buf = stage_base + (two_bufs ? ((n_stores & 1) << 12) : 0);
+                    if (!(c & 1)) wait_staging_free(two_bufs, n_stores, lane);
+                    const uint32_t hbuf = buf + ((c & 1) << 11), lane_off = ((lane & 7) << 1), chunk = lane >> 3;
+                    uint32_t p[16];
+                    convert_chunk(r, g.scale, g.is_bf16, p);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const uint32_t addr = buf + j * 64 + (((chunk ^ ((j >> 1) & 3))) << 4) + lane_off;
-                        asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(cvt1(__uint_as_float(r[j]) * g.scale, g.is_bf16))
+                        const uint32_t addr = hbuf + j * 64 + (((chunk ^ ((j >> 1) & 3))) << 4) + lane_off;
+                        asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"((unsigned short)(p[j >> 1] >> (16 * (j & 1))))
                                      : "memory");
                     }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tmapC, buf, w.a_row + quad * 32, col);
-                        bulk_commit();
+                    if (c & 1) {
+                        fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmapC, buf, w.a_row + quad * 32, col - 32);
+                            bulk_commit();
+                        }
+                        ++n_stores;
                     }
-                    ++n_stores;
-                } else if (transposed) {
-                    store_chunk_transposed(g, xpose + (c & 1) * (XPOSE_BYTES / 2), etid, w.a_row, col, r);
                 } else {
                     store_chunk(g, vec_ok, row, col, r);
                 }
+            };
+            // chunk c+1 is in flight from TMEM while chunk c is converted and stored; chunks come in pairs (c0 and the
+            // chunk count are even), even ones through rbuf[0] and odd ones through rbuf[1]
+            uint32_t rbuf[2][32];
+            tmem_ld_32x32(taddr + c0 * 32, rbuf[0]);
+            tmem_ld_wait();
+            for (int c = c0; c < c0 + nchunks; c += 2) {
+                tmem_ld_32x32(taddr + (c + 1) * 32, rbuf[1]);
+                process(c, rbuf[0]);
+                tmem_ld_wait();
+                if (c + 2 < c0 + nchunks) tmem_ld_32x32(taddr + (c + 2) * 32, rbuf[0]);
+                process(c + 1, rbuf[1]);
                 tmem_ld_wait();
             }
             tc_fence_before();
@@ -695,20 +718,20 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             if (acc == 0) acc_phase ^= 1;
             if (partial) {
                 __threadfence();                                 // partial tile visible before the arrival count
-                epilogue_sync();
-                if (etid == 0) atomicAdd(g.ws_flags + w.owner, 1);
+                epilogue_sync(epi_threads);
+                if (eidx == 0) atomicAdd(g.ws_flags + w.owner, 1);
                 shared = w;
                 has_shared = true;
             }
         }
 #ifdef SD_TIMING
-        if (etid == 0) SD_STAMP(4);
+        if (eidx == 0) SD_STAMP(4);
 #endif
         if (g.tma_store && lane == 0) bulk_wait_all();           // staged results are in global memory
         __syncwarp();
-        if (alive && has_shared) alive = reduce_shared_tile(g, shared, etid, abort_flag);
+        if (alive && has_shared) alive = reduce_shared_tile(g, shared, eidx, epi_threads, abort_flag);
 #ifdef SD_TIMING
-        if (etid == 0) { SD_STAMP(3); sd_timing[blockIdx.x][7] = clock64(); }
+        if (eidx == 0) { SD_STAMP(3); sd_timing[blockIdx.x][7] = clock64(); }
 #endif
         __syncwarp();
     }
@@ -718,6 +741,9 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+#ifdef SD_TIMING
+        if (lane == 0) SD_STAMP(9);
+#endif
     }
 }
 
@@ -800,7 +826,7 @@ static int make_operand_map(CUtensorMap* out, bool* mn_major, const char* name, 
 
 template <bool A_MN, bool B_MN>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& g, int grid,
-                          cudaStream_t st) {
+                          int epi_warps, cudaStream_t st) {
     static bool configured[64] = {};
     int dev = 0;
     SD_CUDA_TRY(cudaGetDevice(&dev));
@@ -814,7 +840,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(64 + 32 * epi_warps);
     cfg.dynamicSmemBytes = GEMM_SMEM;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -931,10 +957,10 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         EncodeTiledFn enc = encode_tiled_fn();
         cuuint64_t dims[2] = {cuuint64_t(N), cuuint64_t(M)};
         cuuint64_t strides[1] = {cuuint64_t(M > 1 ? c_rs * 2 : ((int64_t(N) * 2 + 15) & ~int64_t(15)))};
-        cuuint32_t box[2] = {32u, 32u};
+        cuuint32_t box[2] = {64u, 32u};
         cuuint32_t estr[2] = {1u, 1u};
         CUresult r = enc(&tc, dtype == SD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C,
-                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled(C) failed with CUresult %d", int(r));
         g.tma_store = 1;
@@ -942,7 +968,7 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         EncodeTiledFn enc = encode_tiled_fn();
         cuuint64_t dims[2] = {cuuint64_t(M), cuuint64_t(N)};            // the transpose, row-major [N][M]
         cuuint64_t strides[1] = {cuuint64_t(N > 1 ? c_cs * 2 : ((int64_t(M) * 2 + 15) & ~int64_t(15)))};
-        cuuint32_t box[2] = {32u, 32u};
+        cuuint32_t box[2] = {32u, 64u};
         cuuint32_t estr[2] = {1u, 1u};
         CUresult r = enc(&tc, dtype == SD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C,
                          dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
@@ -950,10 +976,18 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         if (r != CUDA_SUCCESS) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled(C^T) failed with CUresult %d", int(r));
         g.tma_store = 2;
     }
-    if (!a_mn && !b_mn) return launch_variant<false, false>(ta, tb, tc, g, grid, st);
-    if (!a_mn && b_mn) return launch_variant<false, true>(ta, tb, tc, g, grid, st);
-    if (a_mn && !b_mn) return launch_variant<true, false>(ta, tb, tc, g, grid, st);
-    return launch_variant<true, true>(ta, tb, tc, g, grid, st);
+    // Epilogue warps (see MAX_EPI_WARPS): four when whole tiles have a long reduction to hide the epilogue behind,
+    // eight otherwise.
+    static const int epi_warps_env = [] {
+        const char* e = getenv("SD_EPI_WARPS");            // tuning knob: 4 or 8 forces the choice
+        const int v = e ? atoi(e) : 0;
+        return (v == 4 || v == 8) ? v : 0;
+    }();
+    const int epi_warps = epi_warps_env ? epi_warps_env : ((!g.split && k_tiles >= 24) ? 4 : MAX_EPI_WARPS);
+    if (!a_mn && !b_mn) return launch_variant<false, false>(ta, tb, tc, g, grid, epi_warps, st);
+    if (!a_mn && b_mn) return launch_variant<false, true>(ta, tb, tc, g, grid, epi_warps, st);
+    if (a_mn && !b_mn) return launch_variant<true, false>(ta, tb, tc, g, grid, epi_warps, st);
+    return launch_variant<true, true>(ta, tb, tc, g, grid, epi_warps, st);
 }
 
 // ------------------------------------------------------------------ built-in scratch
@@ -1042,9 +1076,9 @@ int sd_gemm_dsd_static_scratch(const void* A, int64_t a_rs, int64_t a_cs, const 
 }
 
 #ifdef SD_TIMING
-int sd_debug_timing(unsigned long long* host_out /* [1024][8] */) {
+int sd_debug_timing(unsigned long long* host_out /* [1024][16] */) {
     SD_CUDA_TRY(cudaDeviceSynchronize());
-    SD_CUDA_TRY(cudaMemcpyFromSymbol(host_out, sd::sd_timing, sizeof(unsigned long long) * 1024 * 8));
+    SD_CUDA_TRY(cudaMemcpyFromSymbol(host_out, sd::sd_timing, sizeof(unsigned long long) * 1024 * 16));
     return SD_OK;
 }
 #endif
