@@ -84,6 +84,55 @@ __global__ void __launch_bounds__(kConvThreads) im2col_kept_rows_kernel(const un
     }
 }
 
+// Fastest im2col: filters 3 wide with unit horizontal stride and dilation and one column of padding (so Q == W),
+// rows of 8..128 pixels that divide 128.  The three taps s = 0, 1, 2 of one (c, r) read the same input row shifted
+// by -1, 0, +1: a thread loads the aligned 8-pixel chunk once, borrows the one pixel on either side from its
+// neighbour lanes (which own the neighbouring chunks of the same image row) and writes three k-rows.
+__global__ void __launch_bounds__(kConvThreads) im2col_kept_s3_kernel(const unsigned short* __restrict__ x,
+                                                                      unsigned short* __restrict__ colT, ConvGeom g,
+                                                                      const int* __restrict__ kept_pairs,
+                                                                      const int* __restrict__ n_kept) {
+    const int total = kept_pairs ? __ldg(n_kept) : g.Rb * g.Cb;
+    const int mgrp = threadIdx.x & 15, tsub = threadIdx.x >> 4;
+    const int PQ = g.P * g.Q, HW = g.H * g.W;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        const int mb = kept_pairs ? __ldg(kept_pairs + 2 * t) : t / g.Cb;
+        const int kb = kept_pairs ? __ldg(kept_pairs + 2 * t + 1) : t - (t / g.Cb) * g.Cb;
+        const int m0 = mb * 128 + mgrp * 8;
+        const bool in_ld = m0 < g.ldm;                   // all lanes stay in the loop: they trade pixels below
+        const bool live = m0 < g.M;                      // M % 8 == 0 here, so the group is all in or all out
+        const int n = live ? m0 / PQ : 0, pq = m0 - n * PQ, p = pq / g.Q, q0 = pq - p * g.Q;
+        const unsigned short* xn = x + (long long)n * g.C * HW;
+        const int hbase = p * g.stride_h - g.pad_h;
+        const bool has_left = q0 > 0, has_right = q0 + 8 < g.Q;
+        const int k_lo = kb * 128, k_hi = min(k_lo + 128, g.K);
+        // (c, r) pairs whose three k-rows 3 * (c * R + r) + s touch [k_lo, k_hi); the same number of passes for
+        // every thread, because the shuffles below need whole warps
+        const int cr_end = (k_hi + 2) / 3;
+        for (int cr0 = k_lo / 3; cr0 < cr_end; cr0 += 16) {
+            const int cr = cr0 + tsub;
+            const bool valid = cr < cr_end;
+            const int c = cr / g.R, r = cr - c * g.R;
+            const int h = hbase + r * g.dil_h;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (valid && live && (unsigned)h < (unsigned)g.H)
+                v = __ldg(reinterpret_cast<const uint4*>(xn + (long long)c * HW + (long long)h * g.W + q0));
+            uint32_t left = __shfl_up_sync(0xffffffffu, v.w, 1), right = __shfl_down_sync(0xffffffffu, v.x, 1);
+            if (!has_left) left = 0;
+            if (!has_right) right = 0;
+            if (!valid || !in_ld) continue;
+            const uint32_t a0 = __funnelshift_r(v.x, v.y, 16), a1 = __funnelshift_r(v.y, v.z, 16),
+                           a2 = __funnelshift_r(v.z, v.w, 16);
+            unsigned short* dst = colT + (long long)(3 * cr) * g.ldm + m0;
+            if (3 * cr >= k_lo)
+                *reinterpret_cast<uint4*>(dst) = make_uint4(__funnelshift_r(left, v.x, 16), a0, a1, a2);
+            if (3 * cr + 1 >= k_lo && 3 * cr + 1 < k_hi) *reinterpret_cast<uint4*>(dst + g.ldm) = v;
+            if (3 * cr + 2 < k_hi)
+                *reinterpret_cast<uint4*>(dst + 2 * g.ldm) = make_uint4(a0, a1, a2, __funnelshift_r(v.w, right, 16));
+        }
+    }
+}
+
 // One CTA per kept block (grid-stride): 128 k-rows x 128 m-columns of colT.  Thread t owns the 8 consecutive m
 // starting at (t % 16) * 8 and visits k-rows (t / 16) + 16 * pass.
 __global__ void __launch_bounds__(kConvThreads) im2col_kept_kernel(const unsigned short* __restrict__ x,
@@ -248,6 +297,166 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_rows_kernel(const un
     }
 }
 
+// Fastest col2im: the adjoint of im2col_kept_s3_kernel under the same conditions plus unit vertical stride.  A thread
+// owns 8 consecutive w of one (n, c, h) and reads, for each of the R x 3 taps, the aligned 8-pixel chunk of the tap's
+// dcolT row; taps s = 0 and s = 2 are that chunk shifted by one pixel, the pixel that falls off going to the
+// neighbour lane (which owns the neighbouring 8 pixels of the same image row).
+template <bool IS_BF16>
+__global__ void __launch_bounds__(kConvThreads) col2im_kept_s3_kernel(const unsigned short* __restrict__ dcolT,
+                                                                      unsigned short* __restrict__ dx, ConvGeom g,
+                                                                      const unsigned char* __restrict__ tile_mask) {
+    const int WG = g.W >> 3;                                     // lanes per image row; divides 32
+    const unsigned total = unsigned(g.N) * g.C * g.H * WG;       // the host checks that this fits 32 bits
+    const unsigned total_up = (total + 31u) & ~31u;              // whole warps run the loop: they trade pixels
+    const int PQ = g.P * g.Q;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total_up; i += gridDim.x * blockDim.x) {
+        const bool live = i < total;
+        const int wg = int(i % WG);
+        unsigned rest = i / WG;
+        const int h = int(rest % g.H);
+        rest /= g.H;
+        const int c = live ? int(rest % g.C) : 0, n = live ? int(rest / g.C) : 0;
+        const bool has_left = wg > 0, has_right = wg + 1 < WG;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < g.R; ++r) {
+            const int p = h + g.pad_h - r * g.dil_h;
+            const bool row_ok = live && (unsigned)p < (unsigned)g.P;
+            const long long m = (long long)n * PQ + (long long)p * g.Q + wg * 8;
+            const int k0 = (c * g.R + r) * 3;
+            float f[3][8];
+#pragma unroll
+            for (int s = 0; s < 3; ++s) {
+                const int k = k0 + s;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (row_ok && !(tile_mask && tile_mask[(m >> 7) * g.Cb + (k >> 7)]))
+                    v = __ldg(reinterpret_cast<const uint4*>(dcolT + (long long)k * g.ldm + m));
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (IS_BF16) {                               // bf16 -> fp32 is a 16-bit shift
+                        f[s][2 * j] = __uint_as_float(wv[j] << 16);
+                        f[s][2 * j + 1] = __uint_as_float(wv[j] & 0xffff0000u);
+                    } else {
+                        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&wv[j]));
+                        f[s][2 * j] = t.x;
+                        f[s][2 * j + 1] = t.y;
+                    }
+                }
+            }
+            // dx[w] += dcol[s][q = w + 1 - s]: tap 0 reads one pixel to the right, tap 2 one to the left
+            float from_right = __shfl_down_sync(0xffffffffu, f[0][0], 1);
+            float from_left = __shfl_up_sync(0xffffffffu, f[2][7], 1);
+            if (!has_right) from_right = 0.f;
+            if (!has_left) from_left = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[j] += f[1][j];
+                acc[j] += j < 7 ? f[0][j + 1] : from_right;
+                acc[j] += j > 0 ? f[2][j - 1] : from_left;
+            }
+        }
+        if (!live) continue;
+        uint32_t out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (IS_BF16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                out[j] = *reinterpret_cast<uint32_t*>(&v);
+            } else {
+                __half2 v = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+                out[j] = *reinterpret_cast<uint32_t*>(&v);
+            }
+        }
+        *reinterpret_cast<uint4*>(dx + (long long)i * 8) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
+// The same for 3 x 3 filters, unrolled over all nine taps: first the nine block-mask bytes, then the nine chunk loads
+// (independent of one another, so one memory round trip covers them all), then the arithmetic.
+template <bool IS_BF16>
+__global__ void __launch_bounds__(kConvThreads) col2im_kept_3x3_kernel(const unsigned short* __restrict__ dcolT,
+                                                                       unsigned short* __restrict__ dx, ConvGeom g,
+                                                                       const unsigned char* __restrict__ tile_mask) {
+    const int WG = g.W >> 3, wg_bits = 31 - __clz(WG);           // lanes per image row: a power of two up to 16
+    const unsigned total = unsigned(g.N) * g.C * g.H * WG;       // the host checks that this fits 32 bits
+    const unsigned total_up = (total + 31u) & ~31u;              // whole warps run the loop: they trade pixels
+    const int PQ = g.P * g.Q;
+    const long long tap_step = g.ldm, row_step = 3 * g.ldm - (long long)g.dil_h * g.Q;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total_up; i += gridDim.x * blockDim.x) {
+        const bool live = i < total;
+        const int wg = int(i & (WG - 1));
+        unsigned rest = i >> wg_bits;
+        const int h = int(rest % g.H);
+        rest /= g.H;
+        const int c = live ? int(rest % g.C) : 0, n = live ? int(rest / g.C) : 0;
+        const int p0 = h + g.pad_h, k0 = c * 9;
+        const long long m0 = (long long)n * PQ + wg * 8;
+        const unsigned short* src0 = dcolT + (long long)k0 * g.ldm + m0 + (long long)p0 * g.Q;   // tap (0, 0)
+        bool ok[9];
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int p = p0 - r * g.dil_h;
+            const bool row_ok = live && (unsigned)p < (unsigned)g.P;
+            const int mrow = int((m0 + (long long)p * g.Q) >> 7) * g.Cb;
+#pragma unroll
+            for (int s = 0; s < 3; ++s)
+                ok[3 * r + s] = row_ok && !(tile_mask && __ldg(tile_mask + mrow + ((k0 + 3 * r + s) >> 7)));
+        }
+        uint4 v[9];
+#pragma unroll
+        for (int r = 0; r < 3; ++r)
+#pragma unroll
+            for (int s = 0; s < 3; ++s)
+                v[3 * r + s] = ok[3 * r + s] ? __ldg(reinterpret_cast<const uint4*>(src0 + r * row_step + s * tap_step))
+                                             : make_uint4(0, 0, 0, 0);
+        const bool has_left = wg > 0, has_right = wg + 1 < WG;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            float f[3][8];
+#pragma unroll
+            for (int s = 0; s < 3; ++s) {
+                const uint32_t wv[4] = {v[3 * r + s].x, v[3 * r + s].y, v[3 * r + s].z, v[3 * r + s].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (IS_BF16) {                               // bf16 -> fp32 is a 16-bit shift
+                        f[s][2 * j] = __uint_as_float(wv[j] << 16);
+                        f[s][2 * j + 1] = __uint_as_float(wv[j] & 0xffff0000u);
+                    } else {
+                        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&wv[j]));
+                        f[s][2 * j] = t.x;
+                        f[s][2 * j + 1] = t.y;
+                    }
+                }
+            }
+            // dx[w] += dcol[s][q = w + 1 - s]: tap 0 reads one pixel to the right, tap 2 one to the left
+            float from_right = __shfl_down_sync(0xffffffffu, f[0][0], 1);
+            float from_left = __shfl_up_sync(0xffffffffu, f[2][7], 1);
+            if (!has_right) from_right = 0.f;
+            if (!has_left) from_left = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[j] += f[1][j];
+                acc[j] += j < 7 ? f[0][j + 1] : from_right;
+                acc[j] += j > 0 ? f[2][j - 1] : from_left;
+            }
+        }
+        if (!live) continue;
+        uint32_t out[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (IS_BF16) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                out[j] = *reinterpret_cast<uint32_t*>(&t);
+            } else {
+                __half2 t = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+                out[j] = *reinterpret_cast<uint32_t*>(&t);
+            }
+        }
+        *reinterpret_cast<uint4*>(dx + (long long)i * 8) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
 static int make_geom(ConvGeom* g, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
                      int stride_w, int dil_h, int dil_w, int64_t ldm, int k_gemm) {
     if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || R <= 0 || S <= 0)
@@ -291,7 +500,11 @@ int sd_im2col_kept(const void* x, int N, int C, int H, int W, int R, int S, int 
     long long blocks = (long long)g.Rb * g.Cb;
     int grid = int(blocks < (long long)sms * 8 ? blocks : (long long)sms * 8);
     const bool rows_path = stride_w == 1 && (W & 7) == 0 && (g.Q & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-    if (rows_path)
+    const bool s3_path = rows_path && S == 3 && dil_w == 1 && pad_w == 1 && W <= 128 && 128 % W == 0;
+    if (s3_path)
+        sd::im2col_kept_s3_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(x), static_cast<unsigned short*>(colT), g, pairs, n_kept);
+    else if (rows_path)
         sd::im2col_kept_rows_kernel<<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
             static_cast<const unsigned short*>(x), static_cast<unsigned short*>(colT), g, pairs, n_kept);
     else
@@ -320,7 +533,20 @@ int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int
     const long long total = (long long)N * C * H * (rows_path ? W / 8 : W);
     long long blocks = (total + sd::kConvThreads - 1) / sd::kConvThreads;
     int grid = int(blocks < (long long)sms * 16 ? blocks : (long long)sms * 16);
-    if (rows_path && dtype == SD_BF16)
+    const bool s3_path = rows_path && S == 3 && dil_w == 1 && pad_w == 1 && W <= 128 && 128 % W == 0;
+    if (s3_path && R == 3 && dtype == SD_BF16)
+        sd::col2im_kept_3x3_kernel<true><<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask);
+    else if (s3_path && R == 3)
+        sd::col2im_kept_3x3_kernel<false><<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask);
+    else if (s3_path && dtype == SD_BF16)
+        sd::col2im_kept_s3_kernel<true><<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask);
+    else if (s3_path)
+        sd::col2im_kept_s3_kernel<false><<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask);
+    else if (rows_path && dtype == SD_BF16)
         sd::col2im_kept_rows_kernel<true><<<grid, sd::kConvThreads, 0, static_cast<cudaStream_t>(stream)>>>(
             static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask);
     else if (rows_path)

@@ -16,6 +16,8 @@ GEOMS = [  # N, C, H, W, R, S, padding, stride, dilation
     (2, 8, 10, 10, 3, 3, (2, 2), (1, 2), (2, 2)),
     (1, 64, 32, 32, 3, 3, (1, 1), (1, 1), (1, 1)),
     (4, 3, 13, 11, 5, 5, (2, 2), (2, 2), (1, 1)),
+    (3, 6, 12, 8, 2, 3, (0, 1), (1, 1), (2, 1)),      # 3-wide filter fast paths: 8-pixel rows, M = 240, R = 2, dilated rows
+    (1, 20, 6, 64, 3, 3, (1, 1), (2, 1), (1, 1)),     # 64-pixel rows, vertical stride 2, K = 180 splits a tap triple
 ]
 
 
