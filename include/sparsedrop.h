@@ -202,6 +202,17 @@ int sd_gemm_sdd_kept(const void* A, int64_t a_rs, int64_t a_cs,
                      int M, int N, int K, const void* plan,
                      float scale, int dtype, void* workspace, int* status, void* stream);
 
+/* Same as sd_gemm_sdd_kept for a plan that describes the TRANSPOSE of the result: the plan's grid is
+ * ceil(N/128) x ceil(M/128) and its kept pair (r, c) is the result's 128x128 tile (c, r).  One tile per
+ * work item.  The convolution's input gradient uses it to produce the K-outer matrix dcolT[K, M] =
+ * W^T . dY^T row-major (a plain TMA store) from the plan of the M x K im2col matrix, instead of
+ * computing dcol[M, K] and storing it transposed.  No counterpart in the reference. */
+int sd_gemm_sdd_kept_t(const void* A, int64_t a_rs, int64_t a_cs,
+                       const void* B, int64_t b_rs, int64_t b_cs,
+                       void* C, int64_t c_rs, int64_t c_cs,
+                       int M, int N, int K, const void* plan,
+                       float scale, int dtype, void* workspace, int* status, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Convolution stages.  The im2col matrix of flash_dropout/functional/im2col_conv2d.py:17-20
  * (M = N*P*Q rows, K = C*R*S columns, k = c*R*S + r*S + s) is kept K-outer: colT[k][m], 16-bit,

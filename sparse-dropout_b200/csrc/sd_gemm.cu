@@ -89,8 +89,9 @@ struct GemmArgs {
     const int* order;                // DSD: row blocks sorted by kept count, heaviest first
     const int* h_nnz;                // DSD: plan header entries: kept tiles, and the largest kept count of a row block
     const int* h_max;
-    const int* items;                // SDD: (row block, col tile 0, col tile 1 or -1)
+    const int* items;                // SDD: (row block, col tile 0, col tile 1 or -1); with sdd_t: (col block, row block)
     const int* n_items;
+    int sdd_t;                       // SDD whose plan describes the transposed result: one kept 128x128 tile per item
     const int* zero_pairs;           // SDD: dropped (row block, col tile) pairs
     const int* n_zero;
     int* status;
@@ -182,7 +183,14 @@ struct WorkIter {
         sp_parts = sp_part < parts ? parts : 0;
     }
     __device__ __forceinline__ void fill(const GemmArgs& g, Seg& s, int row_block, int n_tile) const {
-        if (g.mode == MODE_SDD) {
+        if (g.mode == MODE_SDD && g.sdd_t) {
+            // kept (row, col) pair of the plan's grid = tile (col, row) of the result
+            s.a_row = __ldg(g.items + 2 * row_block + 1) * 128;
+            s.b_row0 = __ldg(g.items + 2 * row_block) * 128;
+            s.b_row1 = -1;
+            s.nk = nk_uniform;
+            s.klist = nullptr;
+        } else if (g.mode == MODE_SDD) {
             const int mb = __ldg(g.items + 3 * row_block), c0 = __ldg(g.items + 3 * row_block + 1),
                       c1 = __ldg(g.items + 3 * row_block + 2);
             s.a_row = mb * 128;
@@ -853,7 +861,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
 }
 
 struct PlanView {
-    const int *header, *row_ptr, *col_idx, *col_ptr, *row_idx, *row_order, *col_order, *sdd_items, *drop_pairs;
+    const int *header, *row_ptr, *col_idx, *col_ptr, *row_idx, *row_order, *col_order, *sdd_items, *drop_pairs, *kept_pairs;
 };
 static PlanView view_plan(const void* plan, int R, int C) {
     const sd_plan_layout L = plan_layout(R, C);
@@ -868,13 +876,14 @@ static PlanView view_plan(const void* plan, int R, int C) {
     v.col_order = reinterpret_cast<const int*>(b + L.col_order);
     v.sdd_items = reinterpret_cast<const int*>(b + L.sdd_items);
     v.drop_pairs = reinterpret_cast<const int*>(b + L.drop_pairs);
+    v.kept_pairs = reinterpret_cast<const int*>(b + L.kept_pairs);
     return v;
 }
 
 static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
                     void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
                     float scale, int dtype, void* workspace, int* status, void* stream, int max_ctas = 0,
-                    bool zero_dropped = true) {
+                    bool zero_dropped = true, bool sdd_t = false) {
     if (M <= 0 || N <= 0 || K <= 0) return fail(SD_ERR_INVALID_ARG, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
     if (dtype != SD_F16 && dtype != SD_BF16) return fail(SD_ERR_INVALID_ARG, "dtype must be SD_F16 or SD_BF16");
     if (!C) return fail(SD_ERR_INVALID_ARG, "C is null");
@@ -917,6 +926,11 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
             g.list_ptr = v.col_ptr; g.list_idx = v.row_idx; g.order = v.col_order;
             g.h_nnz = v.header + H_NNZ; g.h_max = v.header + H_MAX_COL;
         }
+    } else if (mode == MODE_SDD && sdd_t) {
+        // the plan's grid is (N/128) x (M/128): the transpose of the result's; one item per kept pair
+        PlanView v = view_plan(plan, (N + 127) / 128, g.n_row_blocks);
+        g.items = v.kept_pairs; g.n_items = v.header + H_NNZ;
+        g.sdd_t = 1;
     } else if (mode == MODE_SDD) {
         PlanView v = view_plan(plan, g.n_row_blocks, (N + 127) / 128);
         g.items = v.sdd_items; g.n_items = v.header + H_SDD_ITEMS;
@@ -924,8 +938,9 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     }
     // Schedule: with fewer output tiles than SMs, whole tiles would leave SMs idle, so each tile's
     // reduction is split over a group of CTAs instead (needs the workspace).  Otherwise whole tiles, heaviest first.
-    const long long tiles_upper = mode == MODE_SDD ? (long long)g.n_row_blocks * ((((N + 127) / 128) + 1) / 2)
-                                                   : (long long)g.n_row_blocks * g.n_col_tiles;
+    const long long tiles_upper = (mode == MODE_SDD && sdd_t) ? (long long)g.n_row_blocks * ((N + 127) / 128)
+                                  : mode == MODE_SDD        ? (long long)g.n_row_blocks * ((((N + 127) / 128) + 1) / 2)
+                                                            : (long long)g.n_row_blocks * g.n_col_tiles;
     if (max_ctas > 0) {
         if (tiles_upper > max_ctas)
             return fail(SD_ERR_TOO_LARGE,
@@ -1047,6 +1062,13 @@ int sd_gemm_sdd_kept(const void* A, int64_t a_rs, int64_t a_cs, const void* B, i
                      void* workspace, int* status, void* stream) {
     return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
                         workspace, status, stream, 0, /*zero_dropped=*/false);
+}
+
+int sd_gemm_sdd_kept_t(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
+                       int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, float scale, int dtype,
+                       void* workspace, int* status, void* stream) {
+    return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
+                        workspace, status, stream, 0, /*zero_dropped=*/false, /*sdd_t=*/true);
 }
 
 size_t sd_workspace_bytes(void) {

@@ -21,7 +21,7 @@ SD_PLAN_ROWS, SD_PLAN_COLS = 0, 1
 #: every symbol include/sparsedrop.h declares
 EXPORTS = (
     "sd_version", "sd_last_error", "sd_plan_bytes", "sd_plan_offsets", "sd_plan_from_seed", "sd_plan_from_seed_counter",
-    "sd_plan_from_mask", "sd_workspace_bytes", "sd_workspace_init", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd", "sd_gemm_sdd_kept",
+    "sd_plan_from_mask", "sd_workspace_bytes", "sd_workspace_init", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd", "sd_gemm_sdd_kept", "sd_gemm_sdd_kept_t",
     "sd_gemm_dsd_static_scratch", "sd_im2col_kept", "sd_col2im_kept", "sd_selftest_bounded_wait", "sd_check_status",
 )
 
@@ -65,6 +65,8 @@ def lib() -> C.CDLL:
     L.sd_gemm_sdd.argtypes = mat * 3 + [i32, i32, i32, vp, f32, i32, vp, vp, vp]
     L.sd_gemm_sdd_kept.restype = i32
     L.sd_gemm_sdd_kept.argtypes = L.sd_gemm_sdd.argtypes
+    L.sd_gemm_sdd_kept_t.restype = i32
+    L.sd_gemm_sdd_kept_t.argtypes = L.sd_gemm_sdd.argtypes
     L.sd_gemm_dsd_static_scratch.restype = i32
     L.sd_gemm_dsd_static_scratch.argtypes = mat * 3 + [i32, i32, i32, vp, i32, f32, i32, vp, vp]
     L.sd_im2col_kept.restype = i32

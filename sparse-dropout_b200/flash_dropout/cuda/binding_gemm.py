@@ -255,6 +255,22 @@ def sdd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float,
     return Cm
 
 
+def sdd_kept_t(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float, out: torch.Tensor,
+               ws="auto") -> torch.Tensor:
+    """Kept tiles of ``scale * (A @ B.T)`` for a plan that describes the transpose of the result (grid
+    ``ceil(N/128) x ceil(M/128)``); dropped tiles of ``out`` are left untouched."""
+    dt = _check_pair(A, B)
+    M, N = A.size(0), B.size(0)
+    if (plan.R, plan.C) != (ceil(N / TILE), ceil(M / TILE)):
+        raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the transposed output {(N, M)}")
+    Cm = _out(A, B, out)
+    with _on_device(A.device):
+        _lib.check(_lib.lib().sd_gemm_sdd_kept_t(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),
+                                                 float(scale), dt, _ws_ptr(ws, A.device), None,
+                                                 _lib.stream_ptr(A.device)))
+    return Cm
+
+
 @cache
 class GEMM:
     """Drop-in for the reference's ``GEMM`` wrapper (flash_dropout/cuda/binding_gemm.py:7-47)."""

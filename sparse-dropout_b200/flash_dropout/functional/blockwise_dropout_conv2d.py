@@ -24,7 +24,7 @@ import torch
 
 from flash_dropout import _lib
 from flash_dropout import random as sd_random
-from flash_dropout.cuda.binding_gemm import BlockPlan, _on_device, dsd, sdd
+from flash_dropout.cuda.binding_gemm import BlockPlan, _on_device, dsd, sdd_kept_t
 
 from .im2col_conv2d import conv_output_size
 
@@ -120,7 +120,8 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
             del colT
         if ctx.needs_input_grad[0]:
             dcolT = torch.empty((Kg, (M + 7) & ~7), dtype=input.dtype, device=input.device)
-            sdd(dy2d, w2d.T, plan, scale, out=dcolT.T[:M], zero_dropped=False)    # col2im reads kept blocks only
+            # dcolT = w2d.T @ dy2d.T on the kept blocks, written row-major; col2im reads kept blocks only
+            sdd_kept_t(w2d.T, dy2d, plan, scale, out=dcolT[:, :M])
             grad_input = col2im_kept(dcolT, input.shape, (R, S), padding, stride, dilation, plan)
         return grad_input, grad_kernel, None, None, None, None, None, None, None
 

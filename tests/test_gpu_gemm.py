@@ -106,7 +106,7 @@ def test_all_operand_layouts(built_lib, la, lb):
 def test_ragged_shapes_and_bf16(built_lib, M, N, K, p, dtype):
     """Shapes that are not multiples of 128 (the reference asserts divisibility, matmul_dsd.cuh:87-95)."""
     from flash_dropout import _lib
-    from flash_dropout.cuda.binding_gemm import BlockPlan, dsd, sdd
+    from flash_dropout.cuda.binding_gemm import BlockPlan, dsd, sdd, sdd_kept_t
     x, w, dy = _inputs(M, N, K, seed=5, dtype=dtype)
     mask_np = pm.block_mask(M, K, 128, p, seed=6)
     y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, 128, p, w, dy)
@@ -119,6 +119,9 @@ def test_ragged_shapes_and_bf16(built_lib, M, N, K, p, dtype):
     dW = torch.full((N, K), float("nan"), device=DEV, dtype=dtype)
     dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, s, out=dW.T)          # transposed store straight into dW[N, K]
     torch.testing.assert_close(dW.float().cpu(), dw_ref, **tol)
+    dXT = torch.zeros((K, M), device=DEV, dtype=dtype)            # dX^T = W^T . dY^T from the plan of the M x K mask
+    sdd_kept_t(B.T, dC, plan, s, out=dXT)
+    torch.testing.assert_close(dXT.T.float().cpu(), dx_ref, **tol)
 
 
 def test_block_size_larger_than_tile(built_lib):
