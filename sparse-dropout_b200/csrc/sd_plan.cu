@@ -47,6 +47,40 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int& 
     return warp_sums[warp] + incl - v;
 }
 
+// The same for two values per thread in one pass (three barriers instead of six): both sums must stay below 2^31.
+// pair_sums is 33 64-bit words of shared memory.
+__device__ __forceinline__ void block_exclusive_scan_pair(int a, int b, unsigned long long* pair_sums, int& off_a,
+                                                          int& off_b, int& total_a, int& total_b) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned long long v = (unsigned long long)(unsigned)a | ((unsigned long long)(unsigned)b << 32);
+    unsigned long long incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+    }
+    __syncthreads();   // protects pair_sums against a previous call's readers
+    if (lane == 31) pair_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const unsigned long long w = pair_sums[lane];
+        unsigned long long wi = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned long long n = __shfl_up_sync(0xffffffffu, wi, d);
+            if (lane >= d) wi += n;
+        }
+        pair_sums[lane] = wi - w;   // exclusive warp offsets
+        if (lane == 31) pair_sums[32] = wi;
+    }
+    __syncthreads();
+    const unsigned long long tot = pair_sums[32], mine = pair_sums[warp] + incl - v;
+    total_a = int(unsigned(tot));
+    total_b = int(unsigned(tot >> 32));
+    off_a = int(unsigned(mine));
+    off_b = int(unsigned(mine >> 32));
+}
+
 struct PlanArgs {
     unsigned char* plan;
     int R, C, rep;
@@ -259,12 +293,20 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
 // a popcount of that word, so all lists are written in parallel, a warp per row.  Same outputs as plan_kernel.
 constexpr int kBitsMaxRows = 3072;
 
+#ifdef SD_TIMING
+__device__ long long sd_plan_timing[16];
+#define SD_PSTAMP(i) do { if (threadIdx.x == 0) sd_plan_timing[i] = clock64(); } while (0)
+#else
+#define SD_PSTAMP(i) do {} while (0)
+#endif
+
 __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) {
     __shared__ unsigned keepmask[kBitsMaxRows];
     __shared__ int s_row_ptr[kBitsMaxRows];
     __shared__ int s_item_ptr[kBitsMaxRows];
-    __shared__ int warp_sums[33];
+    __shared__ unsigned long long pair_sums[33];
     __shared__ int col_chunk[32][33];
+    __shared__ int s_col_total[32];
     __shared__ int s_col_ptr[33];
     __shared__ int bins[40];
     __shared__ int s_max_row;
@@ -289,6 +331,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
     const unsigned long long offset = a.offset + (a.counter ? *a.counter : 0ull);
     if (threadIdx.x == 0) s_max_row = 0;
     if (threadIdx.x < 40) bins[threadIdx.x] = 0;
+    SD_PSTAMP(0);
 
     // ---- the drop decisions, one tile per thread; kept tiles set their bit in the row word
     for (int r = threadIdx.x; r < R; r += kPlanThreads) keepmask[r] = 0u;
@@ -307,6 +350,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         if (!drop) atomicOr(&keepmask[r], 1u << c);
     }
     __syncthreads();
+    SD_PSTAMP(1);
 
     // ---- row offsets: thread t owns rows [t*rpt, (t+1)*rpt)
     int nnz, n_items;
@@ -320,8 +364,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
             items += (cnt + 1) >> 1;
             mx = max(mx, cnt);
         }
-        int kept_off = block_exclusive_scan(kept, warp_sums, nnz);
-        int item_off = block_exclusive_scan(items, warp_sums, n_items);
+        int kept_off, item_off;
+        block_exclusive_scan_pair(kept, items, pair_sums, kept_off, item_off, nnz, n_items);
         if (mx) atomicMax(&s_max_row, mx);
         for (int r = r0; r < r1; ++r) {
             const int cnt = __popc(keepmask[r]);
@@ -334,6 +378,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         if (threadIdx.x == 0) row_ptr[R] = nnz;
     }
     __syncthreads();
+    SD_PSTAMP(2);
 
     // ---- row lists, one tile per thread: positions are popcounts of the row word below this column
     for (int i = threadIdx.x; i < R * C; i += kPlanThreads) {
@@ -359,6 +404,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         }
     }
 
+    SD_PSTAMP(3);
     // ---- columns: warp w owns the row chunk [w*rpw, (w+1)*rpw); lane = column
     const int rpw = (R + 31) / 32;
     const int cr0 = min(R, warp * rpw), cr1 = min(R, cr0 + rpw);
@@ -368,13 +414,22 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         col_chunk[warp][lane] = cnt;
     }
     __syncthreads();
-    if (warp == 0) {
-        int total = 0;
-        for (int w = 0; w < 32; ++w) {                           // exclusive prefix over the row chunks of this column
-            const int c = col_chunk[w][lane];
-            col_chunk[w][lane] = total;
-            total += c;
+    SD_PSTAMP(4);
+    {   // warp w turns the chunk counts of column w into an exclusive prefix over the row chunks (lane = row chunk)
+        const int cnt = col_chunk[lane][warp];
+        int incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += n;
         }
+        col_chunk[lane][warp] = incl - cnt;
+        if (lane == 31) s_col_total[warp] = incl;
+    }
+    __syncthreads();
+    // three independent jobs on the column totals, one warp each
+    if (warp == 0) {
+        const int total = s_col_total[lane];
         int incl = total;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -385,7 +440,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         if (lane == 31) s_col_ptr[32] = incl;
         if (lane < C) col_ptr[lane] = incl - total;
         if (lane == C - 1) col_ptr[C] = incl;
+    } else if (warp == 1) {
         // column order, heaviest first (stable)
+        const int total = s_col_total[lane];
         int rank = 0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
@@ -393,7 +450,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
             rank += (j < C) && ((other > total) || (other == total && j < lane));
         }
         if (lane < C) col_order[rank] = lane;
-        int mxc = lane < C ? total : 0;
+    } else if (warp == 2) {
+        int mxc = lane < C ? s_col_total[lane] : 0;
 #pragma unroll
         for (int d = 16; d; d >>= 1) mxc = max(mxc, __shfl_xor_sync(0xffffffffu, mxc, d));
         if (lane == 0) {
@@ -408,12 +466,14 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         }
     }
     __syncthreads();
+    SD_PSTAMP(5);
     if (lane < C) {
         int off = s_col_ptr[lane] + col_chunk[warp][lane];
         for (int r = cr0; r < cr1; ++r)
             if ((keepmask[r] >> lane) & 1u) row_idx[off++] = r;
     }
 
+    SD_PSTAMP(6);
     // ---- row order, heaviest first (stable rank sort for short lists, counting sort otherwise)
     if (R <= 64) {
         if (int(threadIdx.x) < R) {
@@ -457,6 +517,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
             }
         }
     }
+    SD_PSTAMP(7);
 }
 
 static int launch_plan(const PlanArgs& a, void* stream) {
@@ -484,6 +545,14 @@ static int launch_plan(const PlanArgs& a, void* stream) {
 }  // namespace sd
 
 extern "C" {
+
+#ifdef SD_TIMING
+int sd_debug_plan_timing(long long* host_out /* [16] */) {
+    SD_CUDA_TRY(cudaDeviceSynchronize());
+    SD_CUDA_TRY(cudaMemcpyFromSymbol(host_out, sd::sd_plan_timing, sizeof(long long) * 16));
+    return SD_OK;
+}
+#endif
 
 size_t sd_plan_bytes(int R, int C) {
     if (R <= 0 || C <= 0) return 0;
