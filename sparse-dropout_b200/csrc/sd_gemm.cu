@@ -6,8 +6,9 @@
 //   DSD   : per 128-row block of A, only the K tiles on that block's kept list
 //           (flash_dropout/cuda/src/matmul_dsd.cuh:18-68 re-reads a bool mask every k-step and
 //           `continue`s; here the producer warp never even visits a dropped tile)
-//   SDD   : only kept 128x128 output tiles are computed, two per work item; dropped tiles are
-//           zero-filled by the otherwise idle epilogue warps
+//   SDD   : only kept 128x128 output tiles are computed, two per work item (one per item when
+//           that would leave half the SMs idle); dropped tiles are zero-filled by the otherwise
+//           idle epilogue warps
 //           (flash_dropout/cuda/src/matmul_sdd.cuh:18-67 launches a CTA per tile, kept or not)
 //
 // CTA = 10 warps on one SM, 128 x 256 output tile, 64-wide K stages in a 4-deep TMA ring:
@@ -89,9 +90,10 @@ struct GemmArgs {
     const int* order;                // DSD: row blocks sorted by kept count, heaviest first
     const int* h_nnz;                // DSD: plan header entries: kept tiles, and the largest kept count of a row block
     const int* h_max;
-    const int* items;                // SDD: (row block, col tile 0, col tile 1 or -1); with sdd_t: (col block, row block)
+    const int* items;                // SDD: (row block, col tile 0, col tile 1 or -1); with sdd_single: kept (row, col) pairs
     const int* n_items;
-    int sdd_t;                       // SDD whose plan describes the transposed result: one kept 128x128 tile per item
+    int sdd_single;                  // SDD with one kept 128x128 tile per item: 1 = the plan's (row, col) is the result's
+                                     // tile (row, col); 2 = the plan describes the transposed result: tile (col, row)
     const int* zero_pairs;           // SDD: dropped (row block, col tile) pairs
     const int* n_zero;
     int* status;
@@ -183,10 +185,10 @@ struct WorkIter {
         sp_parts = sp_part < parts ? parts : 0;
     }
     __device__ __forceinline__ void fill(const GemmArgs& g, Seg& s, int row_block, int n_tile) const {
-        if (g.mode == MODE_SDD && g.sdd_t) {
-            // kept (row, col) pair of the plan's grid = tile (col, row) of the result
-            s.a_row = __ldg(g.items + 2 * row_block + 1) * 128;
-            s.b_row0 = __ldg(g.items + 2 * row_block) * 128;
+        if (g.mode == MODE_SDD && g.sdd_single) {
+            const int pr = __ldg(g.items + 2 * row_block), pc = __ldg(g.items + 2 * row_block + 1);
+            s.a_row = (g.sdd_single == 2 ? pc : pr) * 128;
+            s.b_row0 = (g.sdd_single == 2 ? pr : pc) * 128;
             s.b_row1 = -1;
             s.nk = nk_uniform;
             s.klist = nullptr;
@@ -930,15 +932,23 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         // the plan's grid is (N/128) x (M/128): the transpose of the result's; one item per kept pair
         PlanView v = view_plan(plan, (N + 127) / 128, g.n_row_blocks);
         g.items = v.kept_pairs; g.n_items = v.header + H_NNZ;
-        g.sdd_t = 1;
+        g.sdd_single = 2;
     } else if (mode == MODE_SDD) {
         PlanView v = view_plan(plan, g.n_row_blocks, (N + 127) / 128);
-        g.items = v.sdd_items; g.n_items = v.header + H_SDD_ITEMS;
+        // paired items halve the A traffic; with so few of them that half the SMs would idle, one tile per item
+        // puts twice as many SMs to work
+        const long long pairs_upper = (long long)g.n_row_blocks * ((((N + 127) / 128) + 1) / 2);
+        if (pairs_upper * 2 <= sms) {
+            g.items = v.kept_pairs; g.n_items = v.header + H_NNZ;
+            g.sdd_single = 1;
+        } else {
+            g.items = v.sdd_items; g.n_items = v.header + H_SDD_ITEMS;
+        }
         if (zero_dropped) { g.zero_pairs = v.drop_pairs; g.n_zero = v.header + H_NDROP; }
     }
     // Schedule: with fewer output tiles than SMs, whole tiles would leave SMs idle, so each tile's
     // reduction is split over a group of CTAs instead (needs the workspace).  Otherwise whole tiles, heaviest first.
-    const long long tiles_upper = (mode == MODE_SDD && sdd_t) ? (long long)g.n_row_blocks * ((N + 127) / 128)
+    const long long tiles_upper = (mode == MODE_SDD && g.sdd_single) ? (long long)g.n_row_blocks * ((N + 127) / 128)
                                   : mode == MODE_SDD        ? (long long)g.n_row_blocks * ((((N + 127) / 128) + 1) / 2)
                                                             : (long long)g.n_row_blocks * g.n_col_tiles;
     if (max_ctas > 0) {
