@@ -425,7 +425,27 @@ def run_conv(args) -> None:
         ts.sort()
         return ts[len(ts) // 2]
 
-    t_sparse, t_dense, t_unfold = timeit(sparse_step), timeit(dense_step), timeit(unfold_step)
+    def graphed(fn):
+        """fn captured in a CUDA graph (after warm-up on a side stream); masks stay fresh through the device counter."""
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            fn()
+        return graph.replay
+
+    # The step is ~10 launches behind ~0.3 ms of Python: timed eagerly it is bound by the host, so the headline is
+    # the replay of a captured step (both arms), with the eager times beside it.
+    eager_sparse, eager_dense = timeit(sparse_step), timeit(dense_step)
+    t_unfold = timeit(unfold_step) if not args.no_extras else None
+    if sd_random.device_counter(dev) is None:
+        sd_random.enable_device_counter(dev)
+    t_sparse, t_dense = timeit(graphed(sparse_step)), timeit(graphed(dense_step))
     plan = BlockPlan.from_seed(M, K, BLOCK, p, SEED, 0, dev)
     mask = plan.tile_mask.cpu()
     widths = torch.tensor([128, 128, 128, 128, 64])            # last K block is 64 wide (576 = 4.5 blocks)
@@ -436,9 +456,11 @@ def run_conv(args) -> None:
         "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": t_sparse, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": "BASELINE configs[2]: Conv2d 64->128 3x3 pad 1, input 256x64x32x32 fp16, 128x128 blocks "
-                               "on the im2col matrix (262144 x 576), p=0.5, fwd+bwd", "l2": "256 MB flush between steps"},
+                               "on the im2col matrix (262144 x 576), p=0.5, fwd+bwd", "l2": "256 MB flush between steps",
+                   "step": "CUDA graph replay of forward + backward"},
         "compare_ms": {"sparsedrop_im2col_kept+dsd/sdd": t_sparse, "cudnn_dense_conv_fwd_bwd": t_dense,
-                       "torch_unfold+sparsedrop_linear": t_unfold},
+                       "sparsedrop_eager": eager_sparse, "cudnn_dense_eager": eager_dense,
+                       "torch_unfold+sparsedrop_linear_eager": t_unfold},
         "gpu_launches": 6 * steps}))
 
 
