@@ -1,5 +1,5 @@
 // Block-plan kernel: draws (or reads) the drop mask of an R x C grid of 128x128 tiles and
-// compacts it, in one single-CTA launch, into every index list the GEMM kernels walk
+// compacts it, in one launch (one CTA; a cluster of eight for grids of thousands of tiles), into every index list the GEMM kernels walk
 // (CSR, CSC, kept/dropped pair lists, heaviest-first orders, paired SDD work items).
 //
 // Replaces, device-side and without any host synchronisation:
@@ -9,9 +9,15 @@
 //   mask.T                        flash_dropout/functional/blockwise_dropout_matmul_cuda.py:50 (CSC form)
 //
 // The work is a few KB of integer traffic: the launch is latency-bound, not HBM-bound.
+#include <cooperative_groups.h>
+
+#include <cstdlib>
+
 #include "sd_common.h"
 #include "sd_plan.cuh"
 #include "sd_ptx.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace sd {
 
@@ -520,6 +526,247 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
     SD_PSTAMP(7);
 }
 
+// The same plan from a cluster of kPlanClusterSize CTAs, for grids of thousands of tiles, where one SM is bound by
+// the instructions it has to issue (a Philox draw and three list entries per tile).  CTA g owns a contiguous slice
+// of the rows and does everything plan_bits_kernel does on that slice; what one slice must know of the others -
+// kept tiles, work items, kept tiles per column and rows per kept count in the slices before it, and the totals -
+// is exchanged once through distributed shared memory.
+constexpr int kPlanClusterSize = 8;
+
+struct PlanSliceTotals {
+    int nnz, items, max_row;
+    int col[32];      // kept tiles of the slice in each column
+    int bins[34];     // rows of the slice by C - kept count
+};
+
+__global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_cluster_kernel(PlanArgs a) {
+    __shared__ unsigned keepmask[kBitsMaxRows];
+    __shared__ int s_row_ptr[kBitsMaxRows];
+    __shared__ int s_item_ptr[kBitsMaxRows];
+    __shared__ unsigned long long pair_sums[33];
+    __shared__ int col_chunk[32][33];
+    __shared__ int s_col_base[32];
+    __shared__ int bins[40];
+    __shared__ PlanSliceTotals mine;
+    __shared__ int s_base[4];          // kept tiles / work items before this slice; kept tiles / items of all slices
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int G = int(cluster.num_blocks()), gi = int(cluster.block_rank());
+    const int R = a.R, C = a.C, rep = a.rep;
+    const int Cm = (C + rep - 1) / rep;
+    const int r_lo = int((long long)R * gi / G), r_hi = int((long long)R * (gi + 1) / G), Rn = r_hi - r_lo;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const sd_plan_layout L = plan_layout(R, C);
+    int* header = reinterpret_cast<int*>(a.plan + L.header);
+    int* row_ptr = reinterpret_cast<int*>(a.plan + L.row_ptr);
+    int* col_idx = reinterpret_cast<int*>(a.plan + L.col_idx);
+    int* col_ptr = reinterpret_cast<int*>(a.plan + L.col_ptr);
+    int* row_idx = reinterpret_cast<int*>(a.plan + L.row_idx);
+    int* kept_pairs = reinterpret_cast<int*>(a.plan + L.kept_pairs);
+    int* drop_pairs = reinterpret_cast<int*>(a.plan + L.drop_pairs);
+    int* row_order = reinterpret_cast<int*>(a.plan + L.row_order);
+    int* col_order = reinterpret_cast<int*>(a.plan + L.col_order);
+    int* sdd_items = reinterpret_cast<int*>(a.plan + L.sdd_items);
+    unsigned char* gmask = a.plan + L.mask;
+    grid_dep_launch();
+    grid_dep_wait();   // the counter, a caller's mask and the plan buffer may belong to the previous kernel
+    const unsigned long long offset = a.offset + (a.counter ? *a.counter : 0ull);
+    if (threadIdx.x == 0) mine.max_row = 0;
+    if (threadIdx.x < 34) mine.bins[threadIdx.x] = 0;
+
+    // ---- the drop decisions of the slice, one tile per thread; kept tiles set their bit in the row word
+    for (int r = threadIdx.x; r < Rn; r += kPlanThreads) keepmask[r] = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < Rn * C; i += kPlanThreads) {
+        const int rl = i / C, c = i - rl * C, r = r_lo + rl;
+        const int lr = r / rep, lc = c / rep;
+        bool drop;
+        if (a.from_seed) {
+            drop = philox_drop(a.seed, offset, (unsigned long long)lr * Cm + lc, a.p);
+            if (a.mask_out && r == lr * rep && c == lc * rep) a.mask_out[(long long)lr * Cm + lc] = drop;
+        } else {
+            drop = a.mask_in[lr * a.mask_rs + lc * a.mask_cs] != 0;
+        }
+        gmask[(long long)r * C + c] = drop;
+        if (!drop) atomicOr(&keepmask[rl], 1u << c);
+    }
+    __syncthreads();
+
+    // ---- offsets of the slice's rows relative to the slice: thread t owns rows [t*rpt, (t+1)*rpt) of it
+    {
+        const int rpt = (Rn + kPlanThreads - 1) / kPlanThreads;
+        const int r0 = min(Rn, int(threadIdx.x) * rpt), r1 = min(Rn, r0 + rpt);
+        int kept = 0, items = 0, mx = 0;
+        for (int r = r0; r < r1; ++r) {
+            const int cnt = __popc(keepmask[r]);
+            kept += cnt;
+            items += (cnt + 1) >> 1;
+            mx = max(mx, cnt);
+        }
+        int kept_off, item_off, nnz, n_items;
+        block_exclusive_scan_pair(kept, items, pair_sums, kept_off, item_off, nnz, n_items);
+        if (mx) atomicMax(&mine.max_row, mx);
+        for (int r = r0; r < r1; ++r) {
+            const int cnt = __popc(keepmask[r]);
+            s_row_ptr[r] = kept_off;
+            s_item_ptr[r] = item_off;
+            kept_off += cnt;
+            item_off += (cnt + 1) >> 1;
+        }
+        if (threadIdx.x == 0) { mine.nnz = nnz; mine.items = n_items; }
+    }
+    // ---- kept tiles per column: warp w counts the row chunk [w*rpw, (w+1)*rpw) of the slice; lane = column
+    const int rpw = (Rn + 31) / 32;
+    const int cr0 = min(Rn, warp * rpw), cr1 = min(Rn, cr0 + rpw);
+    {
+        int cnt = 0;
+        for (int r = cr0; r < cr1; ++r) cnt += (keepmask[r] >> lane) & 1u;
+        col_chunk[warp][lane] = cnt;
+    }
+    // ---- rows of the slice by kept count (lanes of a warp that share a count add to it once)
+    const int rounds = (Rn + kPlanThreads - 1) / kPlanThreads;
+    for (int k = 0; k < rounds; ++k) {
+        const int r = k * kPlanThreads + threadIdx.x;
+        const unsigned live = __ballot_sync(0xffffffffu, r < Rn);
+        if (r < Rn) {
+            const int key = C - __popc(keepmask[r]);
+            const unsigned peers = __match_any_sync(live, key);
+            if (lane == __ffs(peers) - 1) atomicAdd(&mine.bins[key], __popc(peers));
+        }
+    }
+    __syncthreads();
+    {   // warp w turns the chunk counts of column w into an exclusive prefix over the row chunks (lane = row chunk)
+        const int cnt = col_chunk[lane][warp];
+        int incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += n;
+        }
+        col_chunk[lane][warp] = incl - cnt;
+        if (lane == 31) mine.col[warp] = incl;
+    }
+    cluster.sync();    // every slice's totals are complete and visible to the whole cluster
+
+    // ---- what the other slices contribute
+    if (warp == 0) {
+        int before = 0, all = 0;                     // column `lane`
+        for (int g = 0; g < G; ++g) {
+            const int v = cluster.map_shared_rank(&mine, g)->col[lane];
+            if (g < gi) before += v;
+            all += v;
+        }
+        int incl = all;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += n;
+        }
+        s_col_base[lane] = incl - all + before;      // where this slice's rows start in column `lane`'s list
+        if (gi == 0) {
+            if (lane < C) col_ptr[lane] = incl - all;
+            if (lane == C - 1) col_ptr[C] = incl;
+            int rank = 0;                            // column order, heaviest first (stable)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int other = __shfl_sync(0xffffffffu, all, j);
+                rank += (j < C) && ((other > all) || (other == all && j < lane));
+            }
+            if (lane < C) col_order[rank] = lane;
+            int mxc = lane < C ? all : 0;
+#pragma unroll
+            for (int d = 16; d; d >>= 1) mxc = max(mxc, __shfl_xor_sync(0xffffffffu, mxc, d));
+            if (lane == 0) header[H_MAX_COL] = mxc;
+        }
+    } else if (warp == 1) {
+        // rows by kept count: bin `lane` (and bin 32 by lane 0 on a second turn) of all slices
+        int start_here = 0;
+        for (int turn = 0; turn < 2; ++turn) {
+            const int key = turn * 32 + lane;
+            int before = 0, all = 0;
+            if (key <= C)
+                for (int g = 0; g < G; ++g) {
+                    const int v = cluster.map_shared_rank(&mine, g)->bins[key];
+                    if (g < gi) before += v;
+                    all += v;
+                }
+            int incl = all;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += n;
+            }
+            if (key <= C) bins[key] = start_here + incl - all + before;
+            start_here += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    } else if (warp == 2 && lane == 0) {
+        int nnz_before = 0, items_before = 0, nnz_all = 0, items_all = 0, max_row = 0;
+        for (int g = 0; g < G; ++g) {
+            const PlanSliceTotals* t = cluster.map_shared_rank(&mine, g);
+            if (g < gi) { nnz_before += t->nnz; items_before += t->items; }
+            nnz_all += t->nnz;
+            items_all += t->items;
+            max_row = max(max_row, t->max_row);
+        }
+        s_base[0] = nnz_before; s_base[1] = items_before; s_base[2] = nnz_all; s_base[3] = items_all;
+        if (gi == 0) {
+            header[H_NNZ] = nnz_all;
+            header[H_SDD_ITEMS] = items_all;
+            header[H_NDROP] = R * C - nnz_all;
+            header[H_R] = R;
+            header[H_C] = C;
+            header[H_MAX_ROW] = max_row;
+            row_ptr[R] = nnz_all;
+            if (a.counter) *a.counter = offset - a.offset + 1;   // every CTA read it before the cluster barrier
+        }
+    }
+    cluster.sync();    // nobody reads another CTA's shared memory after this point; also a CTA-wide barrier
+
+    // ---- row lists of the slice, one tile per thread: positions are popcounts of the row word below this column
+    const int nnz_before = s_base[0], items_before = s_base[1];
+    for (int r = threadIdx.x; r < Rn; r += kPlanThreads) row_ptr[r_lo + r] = nnz_before + s_row_ptr[r];
+    for (int i = threadIdx.x; i < Rn * C; i += kPlanThreads) {
+        const int rl = i / C, c = i - rl * C, r = r_lo + rl;
+        const unsigned mask = keepmask[rl];
+        const int base = nnz_before + s_row_ptr[rl];
+        const int j = __popc(mask & ((1u << c) - 1u));           // kept tiles left of this column
+        if ((mask >> c) & 1u) {
+            col_idx[base + j] = c;
+            *reinterpret_cast<int2*>(kept_pairs + 2 * (base + j)) = make_int2(r, c);
+            if ((j & 1) == 0) {                                  // first tile of a pair: its partner is the next kept column
+                const unsigned above = c == 31 ? 0u : mask & ~((2u << c) - 1u);
+                int* it = sdd_items + 3 * (items_before + s_item_ptr[rl] + (j >> 1));
+                it[0] = r;
+                it[1] = c;
+                it[2] = above ? __ffs(above) - 1 : -1;
+            }
+        } else {
+            const int d = r * C - base + (c - j);                // dropped tiles before this one
+            *reinterpret_cast<int2*>(drop_pairs + 2 * d) = make_int2(r, c);
+        }
+    }
+    // ---- column lists: warp = row chunk of the slice, lane = column
+    if (lane < C) {
+        int off = s_col_base[lane] + col_chunk[warp][lane];
+        for (int r = cr0; r < cr1; ++r)
+            if ((keepmask[r] >> lane) & 1u) row_idx[off++] = r_lo + r;
+    }
+    // ---- row order, heaviest first: counting sort on the kept count, the bins already offset for this slice
+    for (int k = 0; k < rounds; ++k) {
+        const int r = k * kPlanThreads + threadIdx.x;
+        const unsigned live = __ballot_sync(0xffffffffu, r < Rn);
+        if (r < Rn) {
+            const int key = C - __popc(keepmask[r]);
+            const unsigned peers = __match_any_sync(live, key);
+            const int leader = __ffs(peers) - 1;
+            int base = 0;
+            if (lane == leader) base = atomicAdd(&bins[key], __popc(peers));
+            base = __shfl_sync(peers, base, leader);
+            row_order[base + __popc(peers & ((1u << lane) - 1u))] = r_lo + r;
+        }
+    }
+}
+
 static int launch_plan(const PlanArgs& a, void* stream) {
     if (!a.plan) return fail(SD_ERR_INVALID_ARG, "plan buffer is null");
     if (a.R <= 0 || a.C <= 0) return fail(SD_ERR_INVALID_ARG, "plan grid must be positive (R=%d, C=%d)", a.R, a.C);
@@ -535,7 +782,28 @@ static int launch_plan(const PlanArgs& a, void* stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (a.C <= 32 && a.R <= kBitsMaxRows)
+    static const int cluster_min_tiles = [] {
+        const char* e = getenv("SD_PLAN_CLUSTER_MIN_TILES");   // tuning knob: smallest grid that gets the cluster kernel
+        return e ? atoi(e) : 1024;      // below ~1000 tiles the single CTA (4-6 us) beats the cluster's ~6.3 us floor
+    }();
+    static const int cluster_min_rows = [] {
+        const char* e = getenv("SD_PLAN_CLUSTER_MIN_ROWS");
+        return e ? atoi(e) : 8 * kPlanClusterSize;
+    }();
+    if (a.C <= 32 && a.R >= cluster_min_rows && a.R >= kPlanClusterSize && int64_t(a.R) * a.C >= cluster_min_tiles &&
+        a.R <= kBitsMaxRows * kPlanClusterSize) {
+        // thousands of tiles: a cluster of CTAs, each with a slice of the rows
+        cudaLaunchAttribute cattr[2];
+        cattr[0] = attr[0];
+        cattr[1].id = cudaLaunchAttributeClusterDimension;
+        cattr[1].val.clusterDim.x = kPlanClusterSize;
+        cattr[1].val.clusterDim.y = 1;
+        cattr[1].val.clusterDim.z = 1;
+        cfg.gridDim = dim3(kPlanClusterSize);
+        cfg.attrs = cattr;
+        cfg.numAttrs = 2;
+        SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, plan_bits_cluster_kernel, a));
+    } else if (a.C <= 32 && a.R <= kBitsMaxRows)
         SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, plan_bits_kernel, a));
     else
         SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, plan_kernel, a));

@@ -21,6 +21,8 @@ CASES = [  # (M, K, block_size, p, seed, offset)
     # beyond the 32-column / 3072-row fast path: the general kernel (wide, and tall)
     (1024, 8192, 128, 0.5, 10, 0), (640, 5120, 128, 0.3, 11, 1), (524288, 384, 128, 0.5, 12, 0),
     (393216, 4096, 128, 0.5, 13, 2),      # exactly 3072 rows x 32 columns: largest grid of the fast path
+    # thousands of tiles: the cluster kernel (row slices that do not divide evenly; replicated logical blocks)
+    (33024, 2048, 128, 0.5, 14, 1), (65536, 2048, 256, 0.3, 15, 0), (131072, 4096, 128, 0.9, 16, 3),
 ]
 
 
