@@ -235,6 +235,39 @@ int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int
                    int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
                    void* dx, const void* plan, int dtype, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Panel layout of the im2col matrix: [ceil(M/128)][k_gemm][128] — panel b holds pixels m = 128*b ..
+ * 128*b+127, its row k their k-th im2col entries — so a kept 128x128 block is one contiguous 32 KB
+ * run instead of 128 runs of 256 bytes at a stride of ldm.  k_gemm must be a multiple of 64 (rows
+ * K..k_gemm-1 zero), the base 16-byte aligned; the plan is ceil(M/128) x ceil(k_gemm/128) as before.
+ * The four functions below are the panel forms of sd_im2col_kept, sd_col2im_kept, sd_gemm_dsd with the
+ * im2col matrix as its A operand, and sd_gemm_sdd_kept_t with it as the result.  No counterpart in the
+ * reference.
+ * ------------------------------------------------------------------------------------------ */
+int sd_im2col_kept_panels(const void* x, int N, int C, int H, int W, int R, int S,
+                          int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                          void* col_panels, int k_gemm, const void* plan, void* stream);
+
+int sd_col2im_kept_panels(const void* dcol_panels, int k_gemm, int N, int C, int H, int W, int R, int S,
+                          int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                          void* dx, const void* plan, int dtype, void* stream);
+
+/* DSD with the panel matrix P (pixels x kg) as A.  SD_PLAN_ROWS: C[pixels, N] = scale * (keep o col) . B^T with
+ * B[N, kg] (the convolution's forward); SD_PLAN_COLS: C[kg, N] = scale * (keep o col)^T . B^T with B[N, pixels]
+ * (its weight gradient). */
+int sd_gemm_dsd_panels(const void* P, int pixels, int kg,
+                       const void* B, int64_t b_rs, int64_t b_cs,
+                       void* C, int64_t c_rs, int64_t c_cs, int N,
+                       const void* plan, int plan_side,
+                       float scale, int dtype, void* workspace, int* status, void* stream);
+
+/* Kept tiles of P[kg, pixels] = scale * A . B^T (A[kg, K], B[pixels, K]) written into the panel matrix P; the
+ * plan is the one of the pixels x kg matrix (sd_gemm_sdd_kept_t).  Dropped blocks of P are left untouched. */
+int sd_gemm_sdd_kept_t_panels(const void* A, int64_t a_rs, int64_t a_cs,
+                              const void* B, int64_t b_rs, int64_t b_cs,
+                              void* P, int kg, int pixels, int K, const void* plan,
+                              float scale, int dtype, void* workspace, int* status, void* stream);
+
 /*
  * Exercises the bounded device-side waits the kernels are built on, without a fault or a hang: a one-warp kernel
  * waits on a barrier nobody arrives on and on a counter nobody increments, each for at most limit_ns (<= 1 s),

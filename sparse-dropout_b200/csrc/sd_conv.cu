@@ -21,9 +21,17 @@ struct ConvGeom {
     int N, C, H, W, R, S, P, Q;
     int pad_h, pad_w, stride_h, stride_w, dil_h, dil_w;
     int M, K;           // N*P*Q, C*R*S
-    long long ldm;      // leading dimension of colT (>= M, multiple of 8)
+    long long ldm;      // columns of colT that exist (>= M, multiple of 8)
     int Rb, Cb;         // plan grid: ceil(M/128) x ceil(K/128) (K as the GEMM sees it)
+    long long kstride;  // elements from one k-row to the next: ldm, or 128 in the panel layout
+    long long pstride;  // panel layout ([M/128][k_gemm][128], a kept block is one 32 KB run): elements per panel; else 0
 };
+
+// Offset of element (k, m) of the K-outer im2col matrix.  Eight consecutive m starting at a multiple of 8 are
+// contiguous in either layout.
+__device__ __forceinline__ long long col_off(const ConvGeom& g, long long k, long long m) {
+    return g.pstride ? (m >> 7) * g.pstride + k * 128 + (m & 127) : k * g.ldm + m;
+}
 
 constexpr int kConvThreads = 256;
 
@@ -76,7 +84,7 @@ __global__ void __launch_bounds__(kConvThreads) im2col_kept_rows_kernel(const un
             uint32_t o[4] = {0, 0, 0, 0};
             if (live && (unsigned)h < (unsigned)g.H)
                 load8_shifted(xn + (long long)c * HW + (long long)h * g.W, wbase + s * g.dil_w, g.W, o);
-            *reinterpret_cast<uint4*>(colT + (long long)k * g.ldm + m0) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(colT + col_off(g, k, m0)) = make_uint4(o[0], o[1], o[2], o[3]);
             c += c16;
             rs += rs16;
             if (rs >= RS) { rs -= RS; ++c; }
@@ -123,12 +131,12 @@ __global__ void __launch_bounds__(kConvThreads) im2col_kept_s3_kernel(const unsi
             if (!valid || !in_ld) continue;
             const uint32_t a0 = __funnelshift_r(v.x, v.y, 16), a1 = __funnelshift_r(v.y, v.z, 16),
                            a2 = __funnelshift_r(v.z, v.w, 16);
-            unsigned short* dst = colT + (long long)(3 * cr) * g.ldm + m0;
+            unsigned short* dst = colT + col_off(g, 3 * cr, m0);
             if (3 * cr >= k_lo)
                 *reinterpret_cast<uint4*>(dst) = make_uint4(__funnelshift_r(left, v.x, 16), a0, a1, a2);
-            if (3 * cr + 1 >= k_lo && 3 * cr + 1 < k_hi) *reinterpret_cast<uint4*>(dst + g.ldm) = v;
+            if (3 * cr + 1 >= k_lo && 3 * cr + 1 < k_hi) *reinterpret_cast<uint4*>(dst + g.kstride) = v;
             if (3 * cr + 2 < k_hi)
-                *reinterpret_cast<uint4*>(dst + 2 * g.ldm) = make_uint4(a0, a1, a2, __funnelshift_r(v.w, right, 16));
+                *reinterpret_cast<uint4*>(dst + 2 * g.kstride) = make_uint4(a0, a1, a2, __funnelshift_r(v.w, right, 16));
         }
     }
 }
@@ -183,7 +191,7 @@ __global__ void __launch_bounds__(kConvThreads) im2col_kept_kernel(const unsigne
             o.y = v[2] | (uint32_t(v[3]) << 16);
             o.z = v[4] | (uint32_t(v[5]) << 16);
             o.w = v[6] | (uint32_t(v[7]) << 16);
-            *reinterpret_cast<uint4*>(colT + (long long)k * g.ldm + m0) = o;
+            *reinterpret_cast<uint4*>(colT + col_off(g, k, m0)) = o;
         }
     }
 }
@@ -224,7 +232,7 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_kernel(const unsigne
                 if (q >= g.Q) continue;
                 const int m = n * PQ + p * g.Q + q, k = c * RS + r * g.S + s;
                 if (tile_mask && tile_mask[(m >> 7) * g.Cb + (k >> 7)]) continue;
-                acc += to_float(__ldg(dcolT + (long long)k * g.ldm + m), is_bf16);
+                acc += to_float(__ldg(dcolT + col_off(g, k, m)), is_bf16);
             }
         }
         dx[i] = from_float(acc, is_bf16);
@@ -255,13 +263,14 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_rows_kernel(const un
                 const int q0 = wg * 8 + g.pad_w - s * g.dil_w;        // output column that w = wg*8 fed through tap s
                 const int a = q0 & ~7, sh = q0 - a;
                 const long long mrow = (long long)n * PQ + (long long)p * g.Q;
-                const unsigned short* row = dcolT + (long long)k * g.ldm + mrow;
+                const unsigned short* rowa = dcolT + col_off(g, k, mrow + a);           // used only when the chunk exists
+                const unsigned short* rowb = dcolT + col_off(g, k, mrow + a + 8);
                 // chunk validity: inside [0, Q) and in a kept block
                 uint4 c0 = make_uint4(0, 0, 0, 0), c1 = make_uint4(0, 0, 0, 0);
                 if (a >= 0 && a < g.Q && !(tile_mask && tile_mask[((mrow + a) >> 7) * g.Cb + (k >> 7)]))
-                    c0 = __ldg(reinterpret_cast<const uint4*>(row + a));
+                    c0 = __ldg(reinterpret_cast<const uint4*>(rowa));
                 if (sh && a + 8 >= 0 && a + 8 < g.Q && !(tile_mask && tile_mask[((mrow + a + 8) >> 7) * g.Cb + (k >> 7)]))
-                    c1 = __ldg(reinterpret_cast<const uint4*>(row + a + 8));
+                    c1 = __ldg(reinterpret_cast<const uint4*>(rowb));
                 uint32_t w0 = c0.x, w1 = c0.y, w2 = c0.z, w3 = c0.w, w4 = c1.x, w5 = c1.y, w6 = c1.z, w7 = c1.w;
                 const int ws = sh >> 1;
                 if (ws & 1) { w0 = w1; w1 = w2; w2 = w3; w3 = w4; w4 = w5; w5 = w6; w6 = w7; }
@@ -329,7 +338,7 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_s3_kernel(const unsi
                 const int k = k0 + s;
                 uint4 v = make_uint4(0, 0, 0, 0);
                 if (row_ok && !(tile_mask && tile_mask[(m >> 7) * g.Cb + (k >> 7)]))
-                    v = __ldg(reinterpret_cast<const uint4*>(dcolT + (long long)k * g.ldm + m));
+                    v = __ldg(reinterpret_cast<const uint4*>(dcolT + col_off(g, k, m)));
                 const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -381,7 +390,7 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_3x3_kernel(const uns
     const unsigned total = unsigned(g.N) * g.C * g.H * WG;       // the host checks that this fits 32 bits
     const unsigned total_up = (total + 31u) & ~31u;              // whole warps run the loop: they trade pixels
     const int PQ = g.P * g.Q;
-    const long long tap_step = g.ldm, row_step = 3 * g.ldm - (long long)g.dil_h * g.Q;
+    const long long tap_step = g.kstride;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total_up; i += gridDim.x * blockDim.x) {
         const bool live = i < total;
         const int wg = int(i & (WG - 1));
@@ -391,13 +400,15 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_3x3_kernel(const uns
         const int c = live ? int(rest % g.C) : 0, n = live ? int(rest / g.C) : 0;
         const int p0 = h + g.pad_h, k0 = c * 9;
         const long long m0 = (long long)n * PQ + wg * 8;
-        const unsigned short* src0 = dcolT + (long long)k0 * g.ldm + m0 + (long long)p0 * g.Q;   // tap (0, 0)
+        const unsigned short* src[3];                             // tap (r, 0) of each filter row
         bool ok[9];
 #pragma unroll
         for (int r = 0; r < 3; ++r) {
             const int p = p0 - r * g.dil_h;
             const bool row_ok = live && (unsigned)p < (unsigned)g.P;
-            const int mrow = int((m0 + (long long)p * g.Q) >> 7) * g.Cb;
+            const long long m = m0 + (long long)p * g.Q;
+            src[r] = dcolT + col_off(g, k0 + 3 * r, m);
+            const int mrow = int(m >> 7) * g.Cb;
 #pragma unroll
             for (int s = 0; s < 3; ++s)
                 ok[3 * r + s] = row_ok && !(tile_mask && __ldg(tile_mask + mrow + ((k0 + 3 * r + s) >> 7)));
@@ -407,7 +418,7 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_3x3_kernel(const uns
         for (int r = 0; r < 3; ++r)
 #pragma unroll
             for (int s = 0; s < 3; ++s)
-                v[3 * r + s] = ok[3 * r + s] ? __ldg(reinterpret_cast<const uint4*>(src0 + r * row_step + s * tap_step))
+                v[3 * r + s] = ok[3 * r + s] ? __ldg(reinterpret_cast<const uint4*>(src[r] + s * tap_step))
                                              : make_uint4(0, 0, 0, 0);
         const bool has_left = wg > 0, has_right = wg + 1 < WG;
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -458,7 +469,7 @@ __global__ void __launch_bounds__(kConvThreads) col2im_kept_3x3_kernel(const uns
 }
 
 static int make_geom(ConvGeom* g, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
-                     int stride_w, int dil_h, int dil_w, int64_t ldm, int k_gemm) {
+                     int stride_w, int dil_h, int dil_w, int64_t ldm, int k_gemm, bool panels = false) {
     if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || R <= 0 || S <= 0)
         return fail(SD_ERR_INVALID_ARG, "conv sizes must be positive");
     if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0)
@@ -468,24 +479,23 @@ static int make_geom(ConvGeom* g, int N, int C, int H, int W, int R, int S, int 
     if (P <= 0 || Q <= 0) return fail(SD_ERR_INVALID_ARG, "the filter does not fit the padded input");
     const long long M = (long long)N * P * Q, K = (long long)C * R * S;
     if (M > (1ll << 30) || K > (1ll << 30)) return fail(SD_ERR_TOO_LARGE, "im2col matrix too large (M=%lld, K=%lld)", M, K);
+    if (panels) ldm = ((M + 127) / 128) * 128;      // whole panels exist
     if (ldm < M || (ldm & 7)) return fail(SD_ERR_LAYOUT, "ldm (%lld) must be >= N*P*Q (%lld) and a multiple of 8", (long long)ldm, M);
     if (k_gemm < K) return fail(SD_ERR_INVALID_ARG, "k_gemm (%d) must be >= C*R*S (%lld)", k_gemm, K);
     *g = ConvGeom{N, C, H, W, R, S, P, Q, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, int(M), int(K), ldm,
-                  int((M + 127) / 128), (k_gemm + 127) / 128};
+                  int((M + 127) / 128), (k_gemm + 127) / 128, panels ? 128 : ldm, panels ? (long long)k_gemm * 128 : 0};
     return SD_OK;
 }
 
 }  // namespace sd
 
-extern "C" {
-
-int sd_im2col_kept(const void* x, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
-                   int stride_w, int dil_h, int dil_w, void* colT, int64_t ldm, int k_gemm, const void* plan,
-                   void* stream) {
+static int im2col_kept_impl(const void* x, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
+                            int stride_w, int dil_h, int dil_w, void* colT, int64_t ldm, int k_gemm, const void* plan,
+                            void* stream, bool panels) {
     if (!x || !colT) return sd::fail(SD_ERR_INVALID_ARG, "x or colT is null");
     if ((reinterpret_cast<uintptr_t>(colT) & 15)) return sd::fail(SD_ERR_LAYOUT, "colT must be 16-byte aligned");
     sd::ConvGeom g;
-    int rc = sd::make_geom(&g, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, ldm, k_gemm);
+    int rc = sd::make_geom(&g, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, ldm, k_gemm, panels);
     if (rc) return rc;
     const int *pairs = nullptr, *n_kept = nullptr;
     if (plan) {
@@ -514,13 +524,13 @@ int sd_im2col_kept(const void* x, int N, int C, int H, int W, int R, int S, int 
     return SD_OK;
 }
 
-int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int H, int W, int R, int S, int pad_h,
-                   int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, void* dx, const void* plan, int dtype,
-                   void* stream) {
+static int col2im_kept_impl(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int H, int W, int R, int S, int pad_h,
+                            int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, void* dx, const void* plan,
+                            int dtype, void* stream, bool panels) {
     if (!dcolT || !dx) return sd::fail(SD_ERR_INVALID_ARG, "dcolT or dx is null");
     if (dtype != SD_F16 && dtype != SD_BF16) return sd::fail(SD_ERR_INVALID_ARG, "dtype must be SD_F16 or SD_BF16");
     sd::ConvGeom g;
-    int rc = sd::make_geom(&g, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, ldm, k_gemm);
+    int rc = sd::make_geom(&g, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, ldm, k_gemm, panels);
     if (rc) return rc;
     const unsigned char* mask = nullptr;
     if (plan) mask = static_cast<const unsigned char*>(plan) + sd::plan_layout(g.Rb, g.Cb).mask;
@@ -557,6 +567,36 @@ int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int
             static_cast<const unsigned short*>(dcolT), static_cast<unsigned short*>(dx), g, mask, dtype == SD_BF16);
     SD_CUDA_TRY(cudaGetLastError());
     return SD_OK;
+}
+
+extern "C" {
+
+int sd_im2col_kept(const void* x, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
+                   int stride_w, int dil_h, int dil_w, void* colT, int64_t ldm, int k_gemm, const void* plan,
+                   void* stream) {
+    return im2col_kept_impl(x, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, colT, ldm, k_gemm, plan,
+                            stream, false);
+}
+
+int sd_im2col_kept_panels(const void* x, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
+                          int stride_w, int dil_h, int dil_w, void* col_panels, int k_gemm, const void* plan,
+                          void* stream) {
+    return im2col_kept_impl(x, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, col_panels, 0, k_gemm,
+                            plan, stream, true);
+}
+
+int sd_col2im_kept(const void* dcolT, int64_t ldm, int k_gemm, int N, int C, int H, int W, int R, int S, int pad_h,
+                   int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, void* dx, const void* plan, int dtype,
+                   void* stream) {
+    return col2im_kept_impl(dcolT, ldm, k_gemm, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, dx,
+                            plan, dtype, stream, false);
+}
+
+int sd_col2im_kept_panels(const void* dcol_panels, int k_gemm, int N, int C, int H, int W, int R, int S, int pad_h,
+                          int pad_w, int stride_h, int stride_w, int dil_h, int dil_w, void* dx, const void* plan,
+                          int dtype, void* stream) {
+    return col2im_kept_impl(dcol_panels, 0, k_gemm, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+                            dx, plan, dtype, stream, true);
 }
 
 }  // extern "C"

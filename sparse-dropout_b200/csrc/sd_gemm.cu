@@ -98,6 +98,8 @@ struct GemmArgs {
     const int* n_zero;
     int* status;
     uint32_t idesc256, idesc128;
+    int a_panel_kg, c_panel_kg;      // > 0: A / C is the conv's im2col matrix stored in panels of 128 pixels, each panel
+                                     // [kg][128] (kg a multiple of 64); the tensor map then describes [panels*kg][128]
     int split;                       // 1: equal unit ranges with fix-up (needs the workspace); 0: whole tiles
     int tma_store;                   // result written by TMA from a swizzled staging buffer: 1 row-major, 2 column-major
     float* ws_slots;
@@ -533,7 +535,16 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                         const uint32_t full = bar_full + 8 * stage;
                         mbar_arrive_expect_tx(full, tx);
                         const uint32_t sA = tiles + stage * STAGE_BYTES, sB = sA + A_BYTES;
-                        if (!A_MN) {
+                        if (g.a_panel_kg) {
+                            // panels: the 128 pixels of a block are one panel's columns, its k-rows are consecutive rows
+                            if (!A_MN) {                         // A = colT, rows = k, reduction over pixels
+                                tma_load_2d(sA, &tmapA, full, k & 127, (k >> 7) * g.a_panel_kg + w.a_row);
+                            } else {                             // A = col, rows = pixels, reduction over k
+                                const int y = (w.a_row >> 7) * g.a_panel_kg + k;
+                                tma_load_2d(sA, &tmapA, full, 0, y);
+                                tma_load_2d(sA + MN_ATOM_BYTES, &tmapA, full, 64, y);
+                            }
+                        } else if (!A_MN) {
                             tma_load_2d(sA, &tmapA, full, k, w.a_row);
                         } else {
                             tma_load_2d(sA, &tmapA, full, w.a_row, k);
@@ -676,7 +687,11 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                         fence_proxy_async();
                                                 __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&tmapC, buf, col - 32, w.a_row + quad * 32);
+                            if (!g.c_panel_kg)
+                                tma_store_2d(&tmapC, buf, col - 32, w.a_row + quad * 32);
+                            else if (w.a_row + quad * 32 < g.MM)   // rows past the last k would land in the next panel
+                                tma_store_2d(&tmapC, buf, col - 32 - w.b_row0,
+                                             (w.b_row0 >> 7) * g.c_panel_kg + w.a_row + quad * 32);
                             bulk_commit();
                         }
                         ++n_stores;
@@ -885,7 +900,10 @@ static PlanView view_plan(const void* plan, int R, int C) {
 static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
                     void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
                     float scale, int dtype, void* workspace, int* status, void* stream, int max_ctas = 0,
-                    bool zero_dropped = true, bool sdd_t = false) {
+                    bool zero_dropped = true, bool sdd_t = false, int panels = 0) {
+    // panels: 1 = A is the conv's im2col matrix in panels of 128 pixels ([pixels/128][kg][128]); DSD with the plan's
+    // rows = pixel blocks: side ROWS means A[M = pixels, K = kg], side COLS means A[M = kg, K = pixels].
+    // 2 = C[M = kg, N = pixels] is stored that way (SDD for the transposed plan).  kg must be a multiple of 64.
     if (M <= 0 || N <= 0 || K <= 0) return fail(SD_ERR_INVALID_ARG, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
     if (dtype != SD_F16 && dtype != SD_BF16) return fail(SD_ERR_INVALID_ARG, "dtype must be SD_F16 or SD_BF16");
     if (!C) return fail(SD_ERR_INVALID_ARG, "C is null");
@@ -896,8 +914,29 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
 
     CUtensorMap ta, tb;
     bool a_mn = false, b_mn = false;
-    int rc = make_operand_map(&ta, &a_mn, "A", A, a_rs, a_cs, M, K, dtype);
+    int rc;
+    int a_panel_kg = 0, c_panel_kg = 0;
+    if (panels == 1) {
+        const bool rows_are_pixels = plan_side == SD_PLAN_ROWS;
+        const int pixels = rows_are_pixels ? M : K, kg = rows_are_pixels ? K : M;
+        if (kg & 63) return fail(SD_ERR_LAYOUT, "panel layout needs a k extent that is a multiple of 64 (got %d)", kg);
+        const long long all_rows = (long long)((pixels + 127) / 128) * kg;
+        if (all_rows > (1ll << 31) - 1) return fail(SD_ERR_TOO_LARGE, "panel matrix too large");
+        // the panels form one row-major [panels * kg][128] matrix; as an operand: 128 "MN" columns x all_rows, MN-major
+        // (boxes of 64 x 64), or all_rows x 128, K-major (boxes of 64 x 128)
+        rc = rows_are_pixels ? make_operand_map(&ta, &a_mn, "A", A, 1, 128, 128, int(all_rows), dtype)
+                             : make_operand_map(&ta, &a_mn, "A", A, 128, 1, int(all_rows), 128, dtype);
+        a_panel_kg = kg;
+    } else {
+        rc = make_operand_map(&ta, &a_mn, "A", A, a_rs, a_cs, M, K, dtype);
+    }
     if (rc) return rc;
+    if (panels == 2) {
+        if (M & 63) return fail(SD_ERR_LAYOUT, "panel layout needs a k extent that is a multiple of 64 (got %d)", M);
+        if (reinterpret_cast<uintptr_t>(C) & 15) return fail(SD_ERR_LAYOUT, "C must be 16-byte aligned");
+        c_panel_kg = M;
+        c_rs = 128; c_cs = 1;    // only the TMA path below writes C
+    }
     rc = make_operand_map(&tb, &b_mn, "B", B, b_rs, b_cs, N, K, dtype);
     if (rc) return rc;
 
@@ -912,6 +951,8 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     g.status = status;
     g.idesc256 = make_idesc(128, 256, g.is_bf16, a_mn, b_mn);
     g.idesc128 = make_idesc(128, 128, g.is_bf16, a_mn, b_mn);
+    g.a_panel_kg = a_panel_kg;
+    g.c_panel_kg = c_panel_kg;
 
     int sms = 0;
     rc = sm_count_current_device(&sms);
@@ -966,7 +1007,7 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         const char* e = getenv("SD_SPLIT_MIN_KTILES");   // tuning knob: minimum reduction length (in 128-wide K tiles)
         return e ? atoi(e) : 16;
     }();
-    if (workspace && tiles_upper * 2 <= grid && k_tiles >= split_min_k_tiles) {
+    if (workspace && tiles_upper * 2 <= grid && k_tiles >= split_min_k_tiles && !c_panel_kg) {
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(SD_ERR_LAYOUT, "workspace must be 16-byte aligned");
         if (grid > WS_MAX_CTAS) grid = WS_MAX_CTAS;
         g.split = 1;
@@ -978,7 +1019,20 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Row-major result with 16-byte rows: written by TMA (clipped at the ragged edge); otherwise by the warps.
     CUtensorMap tc = ta;
-    if (c_cs == 1 && (c_rs & 7) == 0 && c_rs >= N && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+    if (c_panel_kg) {
+        EncodeTiledFn enc = encode_tiled_fn();
+        const long long all_rows = (long long)((N + 127) / 128) * c_panel_kg;
+        if (all_rows > (1ll << 31) - 1) return fail(SD_ERR_TOO_LARGE, "panel matrix too large");
+        cuuint64_t dims[2] = {128u, cuuint64_t(all_rows)};
+        cuuint64_t strides[1] = {256u};
+        cuuint32_t box[2] = {64u, 32u};
+        cuuint32_t estr[2] = {1u, 1u};
+        CUresult r = enc(&tc, dtype == SD_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C,
+                         dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled(C panels) failed with CUresult %d", int(r));
+        g.tma_store = 1;
+    } else if (c_cs == 1 && (c_rs & 7) == 0 && c_rs >= N && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
         EncodeTiledFn enc = encode_tiled_fn();
         cuuint64_t dims[2] = {cuuint64_t(N), cuuint64_t(M)};
         cuuint64_t strides[1] = {cuuint64_t(M > 1 ? c_rs * 2 : ((int64_t(N) * 2 + 15) & ~int64_t(15)))};
@@ -1079,6 +1133,23 @@ int sd_gemm_sdd_kept_t(const void* A, int64_t a_rs, int64_t a_cs, const void* B,
                        void* workspace, int* status, void* stream) {
     return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
                         workspace, status, stream, 0, /*zero_dropped=*/false, /*sdd_t=*/true);
+}
+
+int sd_gemm_dsd_panels(const void* P, int pixels, int kg, const void* B, int64_t b_rs, int64_t b_cs, void* C,
+                       int64_t c_rs, int64_t c_cs, int N, const void* plan, int plan_side, float scale, int dtype,
+                       void* workspace, int* status, void* stream) {
+    if (plan_side != SD_PLAN_ROWS && plan_side != SD_PLAN_COLS)
+        return sd::fail(SD_ERR_INVALID_ARG, "plan_side must be SD_PLAN_ROWS or SD_PLAN_COLS");
+    const int M = plan_side == SD_PLAN_ROWS ? pixels : kg, K = plan_side == SD_PLAN_ROWS ? kg : pixels;
+    return sd::run_gemm(sd::MODE_DSD, P, 0, 0, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, plan_side, scale, dtype,
+                        workspace, status, stream, 0, true, false, /*panels=*/1);
+}
+
+int sd_gemm_sdd_kept_t_panels(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
+                              void* P, int kg, int pixels, int K, const void* plan, float scale, int dtype,
+                              void* workspace, int* status, void* stream) {
+    return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, P, 128, 1, kg, pixels, K, plan, 0, scale, dtype,
+                        workspace, status, stream, 0, /*zero_dropped=*/false, /*sdd_t=*/true, /*panels=*/2);
 }
 
 size_t sd_workspace_bytes(void) {

@@ -22,7 +22,8 @@ SD_PLAN_ROWS, SD_PLAN_COLS = 0, 1
 EXPORTS = (
     "sd_version", "sd_last_error", "sd_plan_bytes", "sd_plan_offsets", "sd_plan_from_seed", "sd_plan_from_seed_counter",
     "sd_plan_from_mask", "sd_workspace_bytes", "sd_workspace_init", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd", "sd_gemm_sdd_kept", "sd_gemm_sdd_kept_t",
-    "sd_gemm_dsd_static_scratch", "sd_im2col_kept", "sd_col2im_kept", "sd_selftest_bounded_wait", "sd_check_status",
+    "sd_gemm_dsd_static_scratch", "sd_im2col_kept", "sd_col2im_kept", "sd_im2col_kept_panels", "sd_col2im_kept_panels",
+    "sd_gemm_dsd_panels", "sd_gemm_sdd_kept_t_panels", "sd_selftest_bounded_wait", "sd_check_status",
 )
 
 
@@ -73,6 +74,14 @@ def lib() -> C.CDLL:
     L.sd_im2col_kept.argtypes = [vp] + [i32] * 12 + [vp, i64, i32, vp, vp]
     L.sd_col2im_kept.restype = i32
     L.sd_col2im_kept.argtypes = [vp, i64, i32] + [i32] * 12 + [vp, vp, i32, vp]
+    L.sd_im2col_kept_panels.restype = i32
+    L.sd_im2col_kept_panels.argtypes = [vp] + [i32] * 12 + [vp, i32, vp, vp]
+    L.sd_col2im_kept_panels.restype = i32
+    L.sd_col2im_kept_panels.argtypes = [vp, i32] + [i32] * 12 + [vp, vp, i32, vp]
+    L.sd_gemm_dsd_panels.restype = i32
+    L.sd_gemm_dsd_panels.argtypes = [vp, i32, i32] + mat * 2 + [i32, vp, i32, f32, i32, vp, vp, vp]
+    L.sd_gemm_sdd_kept_t_panels.restype = i32
+    L.sd_gemm_sdd_kept_t_panels.argtypes = mat * 2 + [vp, i32, i32, i32, vp, f32, i32, vp, vp, vp]
     L.sd_selftest_bounded_wait.restype = i32
     L.sd_selftest_bounded_wait.argtypes = [vp, u64, vp]
     L.sd_workspace_bytes.restype = C.c_size_t

@@ -271,6 +271,56 @@ def sdd_kept_t(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float, 
     return Cm
 
 
+def _check_panels(P: torch.Tensor, pixels: int) -> tuple[int, int]:
+    """(kg, dtype code) of a panel matrix ``[ceil(pixels/128)][kg][128]`` (see ``sd_im2col_kept_panels``)."""
+    if P.dim() != 3 or P.size(2) != TILE or not P.is_contiguous() or P.size(0) != ceil(pixels / TILE):
+        raise RuntimeError(f"panel matrix must be contiguous [ceil({pixels}/128)][kg][128], got {tuple(P.shape)}")
+    if P.size(1) % 64:
+        raise RuntimeError(f"panel matrix needs kg % 64 == 0, got {P.size(1)}")
+    return P.size(1), _lib.dtype_code(P.dtype)
+
+
+def dsd_panels(P: torch.Tensor, pixels: int, B: torch.Tensor, plan: BlockPlan, side: int, scale: float,
+               out: torch.Tensor | None = None, ws="auto") -> torch.Tensor:
+    """``dsd`` with the conv's im2col matrix, stored in panels, as A: ``col`` (pixels x kg) for ``SD_PLAN_ROWS``,
+    ``col.T`` for ``SD_PLAN_COLS``; the plan is the one of the pixels x kg matrix."""
+    kg, dt = _check_panels(P, pixels)
+    _check_operand(B, "B")
+    if B.dtype != P.dtype or B.device != P.device:
+        raise RuntimeError("panel matrix and B must share dtype and device")
+    if (plan.R, plan.C) != (ceil(pixels / TILE), ceil(kg / TILE)):
+        raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the {pixels} x {kg} im2col matrix")
+    M, K = (pixels, kg) if side == _lib.SD_PLAN_ROWS else (kg, pixels)
+    if B.size(1) != K:
+        raise RuntimeError(f"B must have {K} columns, got {tuple(B.shape)}")
+    N = B.size(0)
+    Cm = out if out is not None else torch.empty((M, N), dtype=P.dtype, device=P.device)
+    if tuple(Cm.shape) != (M, N):
+        raise RuntimeError(f"out must be {(M, N)}, got {tuple(Cm.shape)}")
+    with _on_device(P.device):
+        _lib.check(_lib.lib().sd_gemm_dsd_panels(P.data_ptr(), pixels, kg, *_mat(B), *_mat(Cm), N, plan.buf.data_ptr(),
+                                                 side, float(scale), dt, _ws_ptr(ws, P.device), None,
+                                                 _lib.stream_ptr(P.device)))
+    return Cm
+
+
+def sdd_kept_t_panels(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float, out: torch.Tensor,
+                      ws="auto") -> torch.Tensor:
+    """``sdd_kept_t`` whose result ``(kg x pixels)`` is written into the panel matrix ``out``."""
+    dt = _check_pair(A, B)
+    kg, pixels = A.size(0), B.size(0)
+    okg, odt = _check_panels(out, pixels)
+    if okg != kg or odt != dt or out.device != A.device:
+        raise RuntimeError("out must be a panel matrix of A's dtype and device with kg = A.size(0)")
+    if (plan.R, plan.C) != (ceil(pixels / TILE), ceil(kg / TILE)):
+        raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the {pixels} x {kg} im2col matrix")
+    with _on_device(A.device):
+        _lib.check(_lib.lib().sd_gemm_sdd_kept_t_panels(*_mat(A), *_mat(B), out.data_ptr(), kg, pixels, A.size(1),
+                                                        plan.buf.data_ptr(), float(scale), dt,
+                                                        _ws_ptr(ws, A.device), None, _lib.stream_ptr(A.device)))
+    return out
+
+
 @cache
 class GEMM:
     """Drop-in for the reference's ``GEMM`` wrapper (flash_dropout/cuda/binding_gemm.py:7-47)."""

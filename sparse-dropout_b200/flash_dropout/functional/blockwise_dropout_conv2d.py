@@ -6,12 +6,13 @@ flash_dropout/functional/im2col_conv2d.py:17-20 — M = N*P*Q rows, K = C*R*S co
 k = c*R*S + r*S + s — gets one Bernoulli(p) drop decision per block_size x block_size block
 (K zero-padded to the next multiple of the block), then the linear with the kernel viewed (Kout, CRS).
 
-Data flow (nothing goes through F.unfold):
-  forward   im2col_kept  : x (NCHW) -> kept blocks of colT[K][M]                 (HBM-bound gather)
-            DSD          : y2d[M, Kout] = (keep o colT^T) . W2d^T / (1-p)        (colT^T is an MN-major operand)
+Data flow (nothing goes through F.unfold).  The K-outer im2col matrix is kept in panels of 128 pixels,
+colP[ceil(M/128)][K64][128], so that every kept 128x128 block is one contiguous 32 KB run:
+  forward   im2col_kept  : x (NCHW) -> kept blocks of colP                       (HBM-bound gather)
+            DSD          : y2d[M, Kout] = (keep o col) . W2d^T / (1-p)           (col is an MN-major operand)
             y is returned as an NCHW-shaped view of y2d (channels_last strides), no permute copy
   backward  DSD          : dW2d[Kout, K] written transposed, reduction over kept row blocks of each K tile
-            SDD          : dcolT[K][M] = keep o (dy2d . W2d) / (1-p), stored column-major
+            SDD          : kept blocks of dcolP = W2d^T . dy2d^T / (1-p)         (plan of the transposed result)
             col2im_kept  : dx (NCHW) = adjoint gather over kept blocks           (HBM-bound)
   By default the kept blocks of colT are saved for backward (151 MB at BASELINE's conv config, half of what an
   unfold-based layer keeps); ``recompute_cols=True`` saves only the input (33 MB) and rebuilds colT in backward.
@@ -24,7 +25,7 @@ import torch
 
 from flash_dropout import _lib
 from flash_dropout import random as sd_random
-from flash_dropout.cuda.binding_gemm import BlockPlan, _on_device, dsd, sdd_kept_t
+from flash_dropout.cuda.binding_gemm import BlockPlan, _on_device, dsd_panels, sdd_kept_t_panels
 
 from .im2col_conv2d import conv_output_size
 
@@ -33,13 +34,30 @@ def _round8(v: int) -> int:
     return (v + 7) & ~7
 
 
+def _round64(v: int) -> int:
+    return (v + 63) & ~63
+
+
 def im2col_kept(x: torch.Tensor, kernel_size, padding, stride, dilation, plan: BlockPlan | None,
-                k_gemm: int | None = None) -> torch.Tensor:
-    """colT[k_gemm][ldm] (K-outer im2col matrix) with only the plan's kept blocks filled in."""
+                k_gemm: int | None = None, panels: bool = False) -> torch.Tensor:
+    """K-outer im2col matrix with only the plan's kept blocks filled in: ``colT[k_gemm][ldm]``, or with ``panels``
+    ``[ceil(M/128)][k_gemm][128]`` (a kept block is then one contiguous run; ``k_gemm`` a multiple of 64)."""
     N, C, H, W = x.shape
     R, S = kernel_size
     P, Q = conv_output_size(H, W, R, S, padding, stride, dilation)
     M, K = N * P * Q, C * R * S
+    if panels:
+        k_gemm = k_gemm or _round64(K)
+        colP = torch.empty((ceil(M / 128), k_gemm, 128), dtype=x.dtype, device=x.device)
+        if k_gemm > K:
+            colP[:, K:].zero_()
+        x = x.contiguous()
+        with _on_device(x.device):
+            _lib.check(_lib.lib().sd_im2col_kept_panels(
+                x.data_ptr(), N, C, H, W, R, S, padding[0], padding[1], stride[0], stride[1], dilation[0],
+                dilation[1], colP.data_ptr(), k_gemm, plan.buf.data_ptr() if plan is not None else None,
+                _lib.stream_ptr(x.device)))
+        return colP
     k_gemm = k_gemm or _round8(K)
     ldm = _round8(M)
     colT = torch.empty((k_gemm, ldm), dtype=x.dtype, device=x.device)
@@ -56,9 +74,19 @@ def im2col_kept(x: torch.Tensor, kernel_size, padding, stride, dilation, plan: B
 
 def col2im_kept(dcolT: torch.Tensor, x_shape, kernel_size, padding, stride, dilation,
                 plan: BlockPlan | None) -> torch.Tensor:
+    """Adjoint of ``im2col_kept``; a 3-D ``dcolT`` is taken as the panel layout."""
     N, C, H, W = x_shape
     R, S = kernel_size
     dx = torch.empty(x_shape, dtype=dcolT.dtype, device=dcolT.device)
+    if dcolT.dim() == 3:
+        if not dcolT.is_contiguous() or dcolT.size(2) != 128:
+            raise RuntimeError("a panel matrix must be contiguous [ceil(M/128)][k_gemm][128]")
+        with _on_device(dcolT.device):
+            _lib.check(_lib.lib().sd_col2im_kept_panels(
+                dcolT.data_ptr(), dcolT.size(1), N, C, H, W, R, S, padding[0], padding[1], stride[0], stride[1],
+                dilation[0], dilation[1], dx.data_ptr(), plan.buf.data_ptr() if plan is not None else None,
+                _lib.dtype_code(dcolT.dtype), _lib.stream_ptr(dcolT.device)))
+        return dx
     with _on_device(dcolT.device):
         _lib.check(_lib.lib().sd_col2im_kept(
             dcolT.data_ptr(), dcolT.stride(0), dcolT.size(0), N, C, H, W, R, S, padding[0], padding[1], stride[0],
@@ -82,15 +110,15 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
             raise RuntimeError(f"kernel expects {Ck} input channels, input has {C}")
         P, Q = conv_output_size(H, W, R, S, padding, stride, dilation)
         M, K = N * P * Q, C * R * S
-        Kg, Kog = _round8(K), _round8(Ko)
+        Kg, Kog = _round64(K), _round8(Ko)       # the im2col matrix is kept in panels: k extent a multiple of 64
         if plan is None:
             plan = BlockPlan.draw(M, Kg, block_size, p, input.device)
         w2d = kernel.reshape(Ko, K)
         if Kg != K or Kog != Ko:                         # 16-byte rows for TMA; zero padding changes nothing
             w2d = torch.nn.functional.pad(w2d, (0, Kg - K, 0, Kog - Ko))
         w2d = w2d.contiguous()
-        colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg)
-        y2d = dsd(colT.T[:M], w2d, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))      # (M, Kog)
+        colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg, panels=True)
+        y2d = dsd_panels(colT, M, w2d, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))   # (M, Kog)
         if recompute_cols:
             ctx.save_for_backward(input, w2d)
         else:
@@ -113,15 +141,16 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
         dy2d = dy2d.contiguous()
         grad_input = grad_kernel = None
         if ctx.needs_input_grad[1]:
-            colT = saved_cols[0] if saved_cols else im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg)
+            colT = saved_cols[0] if saved_cols else im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg,
+                                                                 panels=True)
             dw2d = torch.empty((Kog, Kg), dtype=input.dtype, device=input.device)
-            dsd(colT[:, :M], dy2d.T, plan, _lib.SD_PLAN_COLS, scale, out=dw2d.T)
+            dsd_panels(colT, M, dy2d.T, plan, _lib.SD_PLAN_COLS, scale, out=dw2d.T)
             grad_kernel = dw2d[:Ko, :K].reshape(Ko, C, R, S)
             del colT
         if ctx.needs_input_grad[0]:
-            dcolT = torch.empty((Kg, (M + 7) & ~7), dtype=input.dtype, device=input.device)
-            # dcolT = w2d.T @ dy2d.T on the kept blocks, written row-major; col2im reads kept blocks only
-            sdd_kept_t(w2d.T, dy2d, plan, scale, out=dcolT[:, :M])
+            dcolT = torch.empty((ceil(M / 128), Kg, 128), dtype=input.dtype, device=input.device)
+            # dcolT = w2d.T @ dy2d.T on the kept blocks, written into panels; col2im reads kept blocks only
+            sdd_kept_t_panels(w2d.T, dy2d, plan, scale, out=dcolT)
             grad_input = col2im_kept(dcolT, input.shape, (R, S), padding, stride, dilation, plan)
         return grad_input, grad_kernel, None, None, None, None, None, None, None
 

@@ -23,7 +23,8 @@ GEOMS = [  # N, C, H, W, R, S, padding, stride, dilation
 
 @pytest.mark.parametrize("geom", GEOMS)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_im2col_and_col2im_against_unfold_fold(built_lib, geom, dtype):
+@pytest.mark.parametrize("panels", [False, True])
+def test_im2col_and_col2im_against_unfold_fold(built_lib, geom, dtype, panels):
     """Bit-exact data movement: every kept block equals the unfold matrix, dropped blocks are left alone;
     col2im equals fold of the masked matrix (fp32 sum of at most R*S 16-bit values, rounded once)."""
     from flash_dropout.cuda.binding_gemm import BlockPlan
@@ -35,24 +36,27 @@ def test_im2col_and_col2im_against_unfold_fold(built_lib, geom, dtype):
     K, PQ = cols.shape[1], cols.shape[2]
     M = N * PQ
     want = cols.permute(1, 0, 2).reshape(K, M)                                           # colT
-    Kg = (K + 7) & ~7
+    Kg = (K + 63) & ~63 if panels else (K + 7) & ~7
+    Mp = (M + 127) // 128 * 128 if panels else (M + 7) & ~7                              # columns that exist
+    flat = (lambda t: t.permute(1, 0, 2).reshape(Kg, Mp)) if panels else (lambda t: t)  # panels -> colT[k][m]
+    to_layout = (lambda t: t.view(Kg, Mp // 128, 128).permute(1, 0, 2).contiguous()) if panels else (lambda t: t)
     for p in (0.0, 0.5):
         mask = pm.block_mask(M, Kg, 128, p, seed=5)
         plan = BlockPlan.from_mask(torch.from_numpy(mask).to(DEV), M, Kg, 128)
         colT = torch.full((Kg, (M + 7) & ~7), 7.0, dtype=dtype, device=DEV)              # sentinel in dropped blocks
-        got = im2col_kept(x.to(DEV), (R, S), pad, stride, dil, plan, Kg)
+        got = flat(im2col_kept(x.to(DEV), (R, S), pad, stride, dil, plan, Kg, panels=panels))
         keep = md._keep_matrix(mask, M, Kg, 128).T.bool()[:K]                            # (K, M)
         assert torch.equal(got[:K, :M].float().cpu()[keep], want[keep])
         if Kg > K:
             assert (got[K:] == 0).all()
         # adjoint on a random cotangent
-        dcol = torch.randn(Kg, (M + 7) & ~7, generator=g).to(dtype)
+        dcol = torch.randn(Kg, Mp, generator=g).to(dtype)
         dcol_masked = dcol[:K, :M].float() * keep
         want_dx = TF.fold(dcol_masked.view(K, N, PQ).permute(1, 0, 2), (H, W), (R, S), padding=pad, stride=stride,
                           dilation=dil)
-        got_dx = col2im_kept(dcol.to(DEV), (N, C, H, W), (R, S), pad, stride, dil, plan)
+        got_dx = col2im_kept(to_layout(dcol.to(DEV)), (N, C, H, W), (R, S), pad, stride, dil, plan)
         torch.testing.assert_close(got_dx.float().cpu(), want_dx.to(dtype).float(), rtol=2e-2, atol=2e-2)
-    dense = im2col_kept(x.to(DEV), (R, S), pad, stride, dil, None, Kg)
+    dense = flat(im2col_kept(x.to(DEV), (R, S), pad, stride, dil, None, Kg, panels=panels))
     assert torch.equal(dense[:K, :M].float().cpu(), want)
 
 
