@@ -912,6 +912,8 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     if (mode == MODE_DSD && plan_side != SD_PLAN_ROWS && plan_side != SD_PLAN_COLS)
         return fail(SD_ERR_INVALID_ARG, "plan_side must be SD_PLAN_ROWS or SD_PLAN_COLS");
 
+    if (panels == 2 && (M & 63))
+        return fail(SD_ERR_LAYOUT, "panel layout needs a k extent that is a multiple of 64 (got %d)", M);
     CUtensorMap ta, tb;
     bool a_mn = false, b_mn = false;
     int rc;
@@ -932,7 +934,6 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     }
     if (rc) return rc;
     if (panels == 2) {
-        if (M & 63) return fail(SD_ERR_LAYOUT, "panel layout needs a k extent that is a multiple of 64 (got %d)", M);
         if (reinterpret_cast<uintptr_t>(C) & 15) return fail(SD_ERR_LAYOUT, "C must be 16-byte aligned");
         c_panel_kg = M;
         c_rs = 128; c_cs = 1;    // only the TMA path below writes C

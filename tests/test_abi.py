@@ -64,5 +64,14 @@ def test_argument_validation_without_a_gpu(built_lib):
         == SD_ERR_INVALID_ARG
     assert built_lib.sd_gemm_sdd(a, 128, 1, a, 128, 1, None, 128, 1, 128, 128, 128, a, 1.0, 0, None, None, None) \
         == SD_ERR_INVALID_ARG
+    # panel forms: the k extent of the panel matrix must be a multiple of 64
+    assert built_lib.sd_gemm_dsd_panels(a, 256, 100, a, 128, 1, a, 128, 1, 128, a, 0, 1.0, 0, None, None, None) \
+        == SD_ERR_LAYOUT
+    assert b"multiple of 64" in built_lib.sd_last_error()
+    assert built_lib.sd_gemm_dsd_panels(a, 256, 128, a, 128, 1, a, 128, 1, 128, a, 3, 1.0, 0, None, None, None) \
+        == SD_ERR_INVALID_ARG
+    assert built_lib.sd_gemm_sdd_kept_t_panels(a, 1, 136, a, 128, 1, a, 136, 256, 128, a, 1.0, 0, None, None, None) \
+        == SD_ERR_LAYOUT
+    assert built_lib.sd_im2col_kept_panels(None, 1, 1, 8, 8, 3, 3, 1, 1, 1, 1, 1, 1, a, 64, None, None) == SD_ERR_INVALID_ARG
     assert built_lib.sd_check_status(None, None) == SD_ERR_INVALID_ARG
     assert built_lib.sd_workspace_init(None, None) == SD_ERR_INVALID_ARG
