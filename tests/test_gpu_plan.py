@@ -23,6 +23,8 @@ CASES = [  # (M, K, block_size, p, seed, offset)
     (393216, 4096, 128, 0.5, 13, 2),      # exactly 3072 rows x 32 columns: largest grid of the fast path
     # thousands of tiles: the cluster kernel (row slices that do not divide evenly; replicated logical blocks)
     (33024, 2048, 128, 0.5, 14, 1), (65536, 2048, 256, 0.3, 15, 0), (131072, 4096, 128, 0.9, 16, 3),
+    (1048576, 512, 128, 0.5, 17, 0),      # 8192 x 4: slices of 1024 rows
+    (3276800, 128, 128, 0.5, 18, 0),      # 25600 rows: past the cluster kernel's 24576, the general kernel again
 ]
 
 
