@@ -11,9 +11,12 @@
 //           idle epilogue warps
 //           (flash_dropout/cuda/src/matmul_sdd.cuh:18-67 launches a CTA per tile, kept or not)
 //
-// CTA = 10 warps on one SM, 128 x 256 output tile, 64-wide K stages in a 4-deep TMA ring:
-//   warp 0    producer : one lane issues cp.async.bulk.tensor loads (no multicast) into
-//                        128B-swizzled shared memory, completion on `full` mbarriers
+// CTA = 7 or 11 warps on one SM, 128 x 256 output tile, 64-wide K stages in a 4-deep TMA ring:
+//   warp 0 and the last warp
+//             producers: one lane of each issues cp.async.bulk.tensor loads (no multicast) into
+//                        128B-swizzled shared memory - warp 0 the A tiles, the last warp the B tiles
+//                        (one thread issues a load only every ~110 cycles) - completion on `full`
+//                        mbarriers
 //   warp 1    MMA      : one lane issues tcgen05.mma (M128 N256 K16, fp32 accumulate in TMEM),
 //                        tcgen05.commit releases ring stages and publishes accumulators
 //   warps 2-9 epilogue : tcgen05.ld the accumulator (two 256-column TMEM buffers, so the
@@ -65,7 +68,7 @@ constexpr int MAX_EPI_WARPS = 8;
 constexpr int STAGING_BYTES = 8 * 4096;                  // TMA-store staging
 constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/ + STAGING_BYTES;
 static_assert(GEMM_SMEM <= 227 * 1024, "over the shared memory of one CTA");
-constexpr int GEMM_MAX_THREADS = 64 + MAX_EPI_WARPS * 32;
+constexpr int GEMM_MAX_THREADS = 96 + MAX_EPI_WARPS * 32;   // producer A, MMA, epilogue warps, producer B
 constexpr int TMEM_COLS = 512;
 
 // Workspace of the split schedule: flags first, then one fp32 partial tile per CTA.
@@ -484,12 +487,12 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_full + 8 * s, 2);                         // the A producer and the B producer
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, (blockDim.x >> 5) - 2);   // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8 * a, (blockDim.x >> 5) - 3);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -515,8 +518,13 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     if (threadIdx.x == 0) { SD_STAMP(0); sd_timing[blockIdx.x][6] = clock64(); }
 #endif
 
-    if (warp == 0) {
-        // ============================== producer
+    const int b_producer_warp = (blockDim.x >> 5) - 1;
+    if (warp == 0 || warp == b_producer_warp) {
+        // ============================== producers: warp 0 loads the A tiles, the last warp the B tiles.  Two threads
+        // because one thread issues a tensor load only every ~110 cycles: the six loads of a stage with both operands
+        // MN-major, or the index walk between the short tiles of a conv, would otherwise sit on the critical path.
+        // Each arrives on the stage's `full` barrier with its own byte count.
+        const bool loads_a = warp == 0;
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
@@ -525,7 +533,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             it.init(g, cta, n_ctas);
             Seg w;
             while (ok && it.next(g, w)) {
-                const uint32_t tx = A_BYTES + (w.b_row1 >= 0 ? B_BYTES : B_HALF_BYTES);
+                const uint32_t tx = loads_a ? A_BYTES : (w.b_row1 >= 0 ? B_BYTES : B_HALF_BYTES);
                 for (int i = w.i0; ok && i < w.i1; ++i) {
                     const int kb = w.klist ? __ldg(w.klist + i) : i;
                     for (int h = 0; h < 2; ++h) {
@@ -535,22 +543,23 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                         const uint32_t full = bar_full + 8 * stage;
                         mbar_arrive_expect_tx(full, tx);
                         const uint32_t sA = tiles + stage * STAGE_BYTES, sB = sA + A_BYTES;
-                        if (g.a_panel_kg) {
-                            // panels: the 128 pixels of a block are one panel's columns, its k-rows are consecutive rows
-                            if (!A_MN) {                         // A = colT, rows = k, reduction over pixels
-                                tma_load_2d(sA, &tmapA, full, k & 127, (k >> 7) * g.a_panel_kg + w.a_row);
-                            } else {                             // A = col, rows = pixels, reduction over k
-                                const int y = (w.a_row >> 7) * g.a_panel_kg + k;
-                                tma_load_2d(sA, &tmapA, full, 0, y);
-                                tma_load_2d(sA + MN_ATOM_BYTES, &tmapA, full, 64, y);
+                        if (loads_a) {
+                            if (g.a_panel_kg) {
+                                // panels: the 128 pixels of a block are one panel's columns, its k-rows consecutive rows
+                                if (!A_MN) {                     // A = colT, rows = k, reduction over pixels
+                                    tma_load_2d(sA, &tmapA, full, k & 127, (k >> 7) * g.a_panel_kg + w.a_row);
+                                } else {                         // A = col, rows = pixels, reduction over k
+                                    const int y = (w.a_row >> 7) * g.a_panel_kg + k;
+                                    tma_load_2d(sA, &tmapA, full, 0, y);
+                                    tma_load_2d(sA + MN_ATOM_BYTES, &tmapA, full, 64, y);
+                                }
+                            } else if (!A_MN) {
+                                tma_load_2d(sA, &tmapA, full, k, w.a_row);
+                            } else {
+                                tma_load_2d(sA, &tmapA, full, w.a_row, k);
+                                tma_load_2d(sA + MN_ATOM_BYTES, &tmapA, full, w.a_row + 64, k);
                             }
-                        } else if (!A_MN) {
-                            tma_load_2d(sA, &tmapA, full, k, w.a_row);
-                        } else {
-                            tma_load_2d(sA, &tmapA, full, w.a_row, k);
-                            tma_load_2d(sA + MN_ATOM_BYTES, &tmapA, full, w.a_row + 64, k);
-                        }
-                        if (!B_MN) {
+                        } else if (!B_MN) {
                             tma_load_2d(sB, &tmapB, full, k, w.b_row0);
                             if (w.b_row1 >= 0) tma_load_2d(sB + B_HALF_BYTES, &tmapB, full, k, w.b_row1);
                         } else {
@@ -565,7 +574,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                     }
                 }
             }
-            SD_STAMP(1);
+            if (loads_a) SD_STAMP(1);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -616,7 +625,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         // ============================== epilogue
         // Warps 2..5 and 6..9 own TMEM lane quadrants 2,3,0,1 (a warp reaches only the 32 lanes of quadrant warp % 4);
         // the first four take the lower half of a tile's column chunks, the other four the upper half.
-        const int epi_warps = (blockDim.x >> 5) - 2, epi_halves = epi_warps >> 2, epi_threads = epi_warps << 5;
+        const int epi_warps = (blockDim.x >> 5) - 3, epi_halves = epi_warps >> 2, epi_threads = epi_warps << 5;
         const bool two_bufs = epi_warps == 4;
         const int quad = warp & 3, half = (warp - 2) >> 2;       // half is 0 throughout with four epilogue warps
         const int etid = quad * 32 + lane;   // 0..127, also the row inside the tile this thread owns
@@ -865,7 +874,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(64 + 32 * epi_warps);
+    cfg.blockDim = dim3(96 + 32 * epi_warps);
     cfg.dynamicSmemBytes = GEMM_SMEM;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
