@@ -42,8 +42,8 @@ METRIC = "DSD/SDD useful TFLOP/s (DSD fwd + SDD dX + DSD dW on kept 128x128 bloc
 WORKLOAD = ("BASELINE configs[1]: SparseDrop linear fwd+bwd, M=N=K=4096, fp16 in / fp32 acc, 128x128 blocks, "
             "p=0.5, x,W,dy~N(0,K^-1/2), per-step Philox mask (seed 0, offset=step)")
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch at this workload (mean of the step's three launches:
-# 59.9 / 90.5 / 60.9 MB), from the ncu capture summarised in profiles/gemm_kernel_4096_p05.md.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 70.4e6
+# 60.3 / 92.2 / 63.1 MB), from the ncu capture summarised in profiles/gemm_kernel_4096_p05.md.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 71.9e6
 
 
 def measured_peaks() -> tuple[float, str]:
