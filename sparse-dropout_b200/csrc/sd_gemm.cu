@@ -128,6 +128,7 @@ struct WorkIter {
     int t, n_tiles, stride, pass;   // whole tiles: this CTA's index, tile count, gridDim.x, next pass
     int nk_uniform;              // dense / SDD: K tiles per output tile
     int full_per_row, n_full;    // whole tiles: full-width column tiles per row block, and in total
+    int whole_entries, n_entries;   // whole tiles: list entries that are whole tiles, and all entries (see init)
     int sp_rb, sp_nt, sp_owner, sp_parts, sp_part;   // split: this CTA's one segment; sp_parts == 0: none
     bool split, snake;
 
@@ -167,6 +168,17 @@ struct WorkIter {
         const bool ragged = (g.n_col_tiles - 1) * BN + 128 >= g.NN;
         full_per_row = (ragged && g.n_col_tiles > 1) ? g.n_col_tiles - 1 : g.n_col_tiles;
         n_full = g.n_row_blocks * full_per_row;
+        // Whole tiles fill the grid wave by wave.  When the last, partial wave holds at most half as many tiles as
+        // there are CTAs, its tiles are handed out as two 128-wide halves each: twice as many SMs share that wave and
+        // its length drops from one tile to one half tile (a half costs ~0.8 of a tile, its A operand is not halved,
+        // so a fuller last wave is better left whole).  The halves need no exchange between CTAs.
+        whole_entries = n_tiles;
+        {
+            const int waves = n_tiles / n_ctas, rest = n_tiles - waves * n_ctas;
+            if (waves >= 1 && rest > 0 && 2 * rest <= n_ctas && !(g.mode == MODE_SDD && g.sdd_single))
+                whole_entries = waves * n_ctas;
+        }
+        n_entries = whole_entries + 2 * (n_tiles - whole_entries);
         if (!split || n_tiles == 0 || n_tiles > n_ctas) return;
         const int row_weight = 2 * g.n_col_tiles - (ragged ? 1 : 0);
         const unsigned total = work_before(g, n_tiles, row_weight);
@@ -224,9 +236,11 @@ struct WorkIter {
             // pass j hands out tiles [j*stride, (j+1)*stride) of the heaviest-first list; with unequal row blocks,
             // forwards on even passes and backwards on odd ones, so the CTA that got the heaviest tile of one pass
             // gets the lightest of the next
-            for (; pass * stride < n_tiles; ++pass) {
-                const int tile = pass * stride + ((snake && (pass & 1)) ? stride - 1 - t : t);
-                if (tile >= n_tiles) continue;
+            for (; pass * stride < n_entries; ++pass) {
+                const int entry = pass * stride + ((snake && (pass & 1)) ? stride - 1 - t : t);
+                if (entry >= n_entries) continue;
+                const int tile = entry < whole_entries ? entry : whole_entries + ((entry - whole_entries) >> 1);
+                const int half = entry < whole_entries ? -1 : ((entry - whole_entries) & 1);
                 if (g.mode == MODE_SDD) {
                     fill(g, s, tile, 0);
                 } else {
@@ -238,6 +252,14 @@ struct WorkIter {
                     fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, nt);
                 }
                 if (s.nk == 0) continue;          // empty row blocks are zero-filled by the epilogue warps
+                if (half >= 0) {                  // one 128-wide half of a tile of the last wave
+                    if (s.b_row1 < 0) {
+                        if (half == 1) continue;  // the tile is only 128 wide: there is no second half
+                    } else {
+                        if (half == 1) s.b_row0 = s.b_row1;
+                        s.b_row1 = -1;
+                    }
+                }
                 s.i0 = 0;
                 s.i1 = s.nk;
                 s.owner = 0; s.parts = 1; s.part = 0;
