@@ -221,6 +221,27 @@ def test_many_ctas_per_tile(built_lib, M, N, K):
         _close(dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, 2.0).T, dw_ref, "dw again")
 
 
+@pytest.mark.parametrize("panels", [False, True])
+def test_sdd_kept_t_with_many_tiles(built_lib, panels):
+    """Transposed-plan SDD on a grid of hundreds of tiles (several tiles per CTA), flat and panel results."""
+    from flash_dropout.cuda.binding_gemm import BlockPlan, sdd_kept_t, sdd_kept_t_panels
+    M, N, K, p = 16384 + 64, 200, 640, 0.5                       # plan grid 129 x 5; ragged pixel count
+    x, w, dy = _inputs(M, N, K, seed=21)
+    mask_np = pm.block_mask(M, K, 128, p, seed=22)
+    _, dx_ref, _ = md.forward_backward(x, mask_np, 128, p, w, dy)
+    plan = BlockPlan.from_mask(torch.from_numpy(mask_np).to(DEV), M, K, 128)
+    B, dC = w.to(DEV), dy.to(DEV)
+    Mp = (M + 127) // 128 * 128
+    if panels:
+        out = torch.zeros((Mp // 128, K, 128), device=DEV, dtype=torch.float16)
+        sdd_kept_t_panels(B.T, dC, plan, 2.0, out=out)
+        dxT = out.permute(1, 0, 2).reshape(K, Mp)[:, :M]
+    else:
+        dxT = torch.zeros((K, M), device=DEV, dtype=torch.float16)
+        sdd_kept_t(B.T, dC, plan, 2.0, out=dxT)
+    _close(dxT.T, dx_ref, "dx^T")
+
+
 def test_errors_mirror_the_reference(built_lib):
     """gemm_binding.cu:18-22,49-50,87-89 raise RuntimeError for device / rank / stride / dtype problems."""
     from flash_dropout.cuda.binding_gemm import GEMM
