@@ -68,22 +68,29 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
         return grad_input, grad_weight, None, None, None
 
 
-_last_cast = {"key": None, "ref": None}
+_last_cast = {"key": None, "src": None, "ref": None}
 
 
 def _autocast_input(input: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
     """``input.to(dt)``, shared between consecutive layers that are fed the very same tensor (the q / k / v
-    projections of an attention block): one cast forward, and one cast of the summed gradient backward."""
+    projections of an attention block): one cast forward, and one cast of the summed gradient backward.
+
+    The entry is valid only for the very tensor it was made from, unmodified since.  A layer sees a fresh 2-D
+    view object on every call, so the tensor is identified by the object that owns its memory (the view's base)
+    plus the view's geometry; the entry holds only a weak reference to that owner, so once it is freed the entry
+    is dead and a new tensor that the allocator places at the same address can never be taken for it."""
     if input.dtype == dt:
         return input
-    key = (input.data_ptr(), input._version, tuple(input.shape), tuple(input.stride()), input.dtype, dt,
+    owner = input._base if input._base is not None else input
+    key = (input._version, tuple(input.shape), tuple(input.stride()), input.storage_offset(), input.dtype, dt,
            input.requires_grad, torch.is_grad_enabled())
-    if _last_cast["key"] == key:
+    src = _last_cast["src"]
+    if src is not None and src() is owner and _last_cast["key"] == key:
         cached = _last_cast["ref"]()
         if cached is not None:
             return cached
     out = input.to(dt)
-    _last_cast["key"], _last_cast["ref"] = key, weakref.ref(out)
+    _last_cast["key"], _last_cast["src"], _last_cast["ref"] = key, weakref.ref(owner), weakref.ref(out)
     return out
 
 

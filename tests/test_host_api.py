@@ -121,3 +121,30 @@ def test_cuda_op_fails_loudly_without_cuda():
     with pytest.raises(RuntimeError):
         F.cuda_blockwise_dropout_matmul(torch.zeros(128, 128, dtype=torch.float16),
                                         torch.zeros(128, 128, dtype=torch.float16), 128, 0.5)
+
+
+def test_autocast_cast_cache_never_outlives_its_tensor():
+    """The shared q/k/v input cast must hit only for the very same tensor, and must miss for a new tensor that the
+    allocator happens to place at the address of a freed one (same shape, version 0)."""
+    from flash_dropout.functional.blockwise_dropout_matmul_cuda import _autocast_input
+    for _ in range(20):
+        x1 = torch.randn(64, 32)
+        kept = _autocast_input(x1, torch.float16)            # stays alive, as autograd would keep it for backward
+        addr = x1.data_ptr()
+        del x1
+        x2 = torch.randn(64, 32)
+        got = _autocast_input(x2, torch.float16)
+        assert torch.equal(got, x2.half()), f"stale cast returned (same address reused: {x2.data_ptr() == addr})"
+        assert kept is not got
+    # the three projections of an attention block: fresh 2-D views of one 3-D activation share one cast
+    x = torch.randn(2, 8, 32)
+    a = _autocast_input(x.reshape(-1, 32), torch.float16)
+    b = _autocast_input(x.reshape(-1, 32), torch.float16)
+    assert a is b
+    x.add_(1.0)                                              # an in-place update invalidates the entry
+    c = _autocast_input(x.reshape(-1, 32), torch.float16)
+    assert c is not a and torch.equal(c, x.reshape(-1, 32).half())
+    # a different window of the same owner is a different tensor
+    d = _autocast_input(x[0], torch.float16)
+    e = _autocast_input(x[1], torch.float16)
+    assert torch.equal(d, x[0].half()) and torch.equal(e, x[1].half())
