@@ -1,6 +1,8 @@
 // Library-level pieces of the C ABI: version, thread-local error text, cached device facts.
 #include <string.h>
 
+#include <atomic>
+
 #include "sd_common.h"
 
 namespace sd {
@@ -19,16 +21,19 @@ int fail(int code, const char* fmt, ...) {
 }
 
 int sm_count_current_device(int* out) {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64] = {};   // read from several host threads at once
     int dev = 0;
     SD_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && cached[dev] > 0) {
-        *out = cached[dev];
-        return SD_OK;
+    if (dev < 64) {
+        const int have = cached[dev].load(std::memory_order_relaxed);
+        if (have > 0) {
+            *out = have;
+            return SD_OK;
+        }
     }
     int n = 0;
     SD_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-    if (dev < 64) cached[dev] = n;
+    if (dev < 64) cached[dev].store(n, std::memory_order_relaxed);
     *out = n;
     return SD_OK;
 }

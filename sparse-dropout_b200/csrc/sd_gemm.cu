@@ -43,6 +43,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -406,16 +407,6 @@ __device__ __forceinline__ bool flag_wait(const int* flag, volatile int* abort_f
     }
 }
 
-#ifdef SD_TIMING
-// Development aid (not compiled into the product): per-CTA timestamps of one launch.
-__device__ unsigned long long sd_timing[1024][16];
-#define SD_STAMP(slot)                                                                     \
-    do {                                                                                   \
-        sd_timing[blockIdx.x][slot] = global_timer_ns();                                   \
-    } while (0)
-#else
-#define SD_STAMP(slot) do {} while (0)
-#endif
 
 // ------------------------------------------------------------------ shared tiles of the split schedule
 // The CTAs seg.owner .. seg.owner + seg.parts - 1 have each parked the partial accumulator of their part of one
@@ -431,9 +422,6 @@ __device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int eidx, 
     bool ok = true;
     if (eidx == 0) ok = counter_wait(arrive, P, abort_flag, g.status, ST_FIXUP);
     if (!epilogue_all(ok, epi_threads)) return false;
-#ifdef SD_TIMING
-    if (eidx == 0) SD_STAMP(5);
-#endif
     const int n_units = (seg.b_row1 >= 0 ? 8 : 4) * 4;
     unsigned short* C = static_cast<unsigned short*>(g.C);
     const bool quad_ok = g.c_cs == 1 && (g.c_rs & 3) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 7) == 0;
@@ -503,9 +491,6 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     uint8_t* staging = aligned + TILE_SMEM;   // 32 KiB of TMA-store staging, 1024-aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef SD_TIMING
-    if (threadIdx.x == 0) SD_STAMP(8);
-#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -536,9 +521,6 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     grid_dep_wait();
 
     const int n_ctas = gridDim.x, cta = blockIdx.x;
-#ifdef SD_TIMING
-    if (threadIdx.x == 0) { SD_STAMP(0); sd_timing[blockIdx.x][6] = clock64(); }
-#endif
 
     const int b_producer_warp = (blockDim.x >> 5) - 1;
     if (warp == 0 || warp == b_producer_warp) {
@@ -596,7 +578,6 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                     }
                 }
             }
-            if (loads_a) SD_STAMP(1);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -640,7 +621,6 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1;
             }
-            SD_STAMP(2);
         }
         __syncwarp();
     } else {
@@ -780,15 +760,9 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 has_shared = true;
             }
         }
-#ifdef SD_TIMING
-        if (eidx == 0) SD_STAMP(4);
-#endif
         if (g.tma_store && lane == 0) bulk_wait_all();           // staged results are in global memory
         __syncwarp();
         if (alive && has_shared) alive = reduce_shared_tile(g, shared, eidx, epi_threads, abort_flag);
-#ifdef SD_TIMING
-        if (eidx == 0) { SD_STAMP(3); sd_timing[blockIdx.x][7] = clock64(); }
-#endif
         __syncwarp();
     }
 
@@ -797,9 +771,6 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
-#ifdef SD_TIMING
-        if (lane == 0) SD_STAMP(9);
-#endif
     }
 }
 
@@ -883,16 +854,15 @@ static int make_operand_map(CUtensorMap* out, bool* mn_major, const char* name, 
 template <bool A_MN, bool B_MN>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& g, int grid,
                           int epi_warps, cudaStream_t st) {
-    static bool configured[64] = {};
+    // Called from the main thread and from autograd's worker threads at once: the per-device "already configured"
+    // flags are atomics (setting the attribute twice is harmless, so relaxed ordering is enough).
+    static std::atomic<bool> configured[64] = {};
     int dev = 0;
     SD_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
+    if (dev >= 64 || !configured[dev].load(std::memory_order_relaxed)) {
         SD_CUDA_TRY(cudaFuncSetAttribute(sparsedrop_gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GEMM_SMEM));
-        configured[dev] = true;
-    } else if (dev >= 64) {
-        SD_CUDA_TRY(cudaFuncSetAttribute(sparsedrop_gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GEMM_SMEM));
+        if (dev < 64) configured[dev].store(true, std::memory_order_relaxed);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -1210,13 +1180,6 @@ int sd_gemm_dsd_static_scratch(const void* A, int64_t a_rs, int64_t a_cs, const 
                         dtype, scratch, status, stream, sd::kStaticScratchSlots);
 }
 
-#ifdef SD_TIMING
-int sd_debug_timing(unsigned long long* host_out /* [1024][16] */) {
-    SD_CUDA_TRY(cudaDeviceSynchronize());
-    SD_CUDA_TRY(cudaMemcpyFromSymbol(host_out, sd::sd_timing, sizeof(unsigned long long) * 1024 * 16));
-    return SD_OK;
-}
-#endif
 
 int sd_check_status(const int* status, void* stream) {
     if (!status) return sd::fail(SD_ERR_INVALID_ARG, "status is null");

@@ -299,12 +299,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
 // a popcount of that word, so all lists are written in parallel, a warp per row.  Same outputs as plan_kernel.
 constexpr int kBitsMaxRows = 3072;
 
-#ifdef SD_TIMING
-__device__ long long sd_plan_timing[16];
-#define SD_PSTAMP(i) do { if (threadIdx.x == 0) sd_plan_timing[i] = clock64(); } while (0)
-#else
-#define SD_PSTAMP(i) do {} while (0)
-#endif
 
 __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) {
     __shared__ unsigned keepmask[kBitsMaxRows];
@@ -337,7 +331,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
     const unsigned long long offset = a.offset + (a.counter ? *a.counter : 0ull);
     if (threadIdx.x == 0) s_max_row = 0;
     if (threadIdx.x < 40) bins[threadIdx.x] = 0;
-    SD_PSTAMP(0);
 
     // ---- the drop decisions, one tile per thread; kept tiles set their bit in the row word
     for (int r = threadIdx.x; r < R; r += kPlanThreads) keepmask[r] = 0u;
@@ -356,7 +349,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         if (!drop) atomicOr(&keepmask[r], 1u << c);
     }
     __syncthreads();
-    SD_PSTAMP(1);
 
     // ---- row offsets: thread t owns rows [t*rpt, (t+1)*rpt)
     int nnz, n_items;
@@ -384,7 +376,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         if (threadIdx.x == 0) row_ptr[R] = nnz;
     }
     __syncthreads();
-    SD_PSTAMP(2);
 
     // ---- row lists, one tile per thread: positions are popcounts of the row word below this column
     for (int i = threadIdx.x; i < R * C; i += kPlanThreads) {
@@ -410,7 +401,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         }
     }
 
-    SD_PSTAMP(3);
     // ---- columns: warp w owns the row chunk [w*rpw, (w+1)*rpw); lane = column
     const int rpw = (R + 31) / 32;
     const int cr0 = min(R, warp * rpw), cr1 = min(R, cr0 + rpw);
@@ -420,7 +410,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         col_chunk[warp][lane] = cnt;
     }
     __syncthreads();
-    SD_PSTAMP(4);
     {   // warp w turns the chunk counts of column w into an exclusive prefix over the row chunks (lane = row chunk)
         const int cnt = col_chunk[lane][warp];
         int incl = cnt;
@@ -472,14 +461,12 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
         }
     }
     __syncthreads();
-    SD_PSTAMP(5);
     if (lane < C) {
         int off = s_col_ptr[lane] + col_chunk[warp][lane];
         for (int r = cr0; r < cr1; ++r)
             if ((keepmask[r] >> lane) & 1u) row_idx[off++] = r;
     }
 
-    SD_PSTAMP(6);
     // ---- row order, heaviest first (stable rank sort for short lists, counting sort otherwise)
     if (R <= 64) {
         if (int(threadIdx.x) < R) {
@@ -523,7 +510,6 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
             }
         }
     }
-    SD_PSTAMP(7);
 }
 
 // The same plan from a cluster of kPlanClusterSize CTAs, for grids of thousands of tiles, where one SM is bound by
@@ -814,13 +800,6 @@ static int launch_plan(const PlanArgs& a, void* stream) {
 
 extern "C" {
 
-#ifdef SD_TIMING
-int sd_debug_plan_timing(long long* host_out /* [16] */) {
-    SD_CUDA_TRY(cudaDeviceSynchronize());
-    SD_CUDA_TRY(cudaMemcpyFromSymbol(host_out, sd::sd_plan_timing, sizeof(long long) * 16));
-    return SD_OK;
-}
-#endif
 
 size_t sd_plan_bytes(int R, int C) {
     if (R <= 0 || C <= 0) return 0;

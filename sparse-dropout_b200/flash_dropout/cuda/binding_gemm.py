@@ -162,6 +162,60 @@ def workspace(device: torch.device) -> torch.Tensor:
     return ws
 
 
+_status_words: dict = {}
+SD_ERR_TIMEOUT = -4
+
+
+def _dev_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The device's failure-detection words (int32[4], word 0 is the status): every kernel launch of this module is
+    given word 0, and a device-side wait that runs out of time records its code there instead of spinning on."""
+    idx = _dev_index(device)
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = w
+    return w
+
+
+def _status_ptr(device: torch.device) -> int:
+    return status_word(device).data_ptr()
+
+
+def check_status(device: torch.device | int | None = None) -> None:
+    """Raises ``SparseDropError`` if a kernel launched on ``device`` since the last check gave up on a bounded wait.
+
+    Waits for the device's current stream, reads the status word, and on a recorded time-out puts the library back
+    into a usable state before raising: the counters of every cached split-schedule workspace of the device are
+    cleared again (a launch that gave up may have left them non-zero) and the status word is reset.  The results of
+    the step that timed out are not valid; later launches are.  Cheap enough to call where the host synchronises
+    anyway (after a training step's loss has been read, at the end of a timed region)."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    elif isinstance(device, int):
+        device = torch.device("cuda", device)
+    idx = _dev_index(device)
+    w = _status_words.get(idx)
+    if w is None:
+        return                                  # nothing was ever launched on this device
+    L = _lib.lib()
+    with _on_device(device):
+        rc = L.sd_check_status(w.data_ptr(), _lib.stream_ptr(device))
+        if rc == 0:
+            return
+        msg = L.sd_last_error().decode()
+        if rc == SD_ERR_TIMEOUT:
+            for (d, stream), ws in _workspaces.items():
+                if d == idx:
+                    _lib.check(L.sd_workspace_init(ws.data_ptr(), _lib.stream_ptr(device)))
+            w.zero_()
+            torch.cuda.current_stream(device).synchronize()
+    raise _lib.SparseDropError(f"libsparsedrop error {rc}: {msg}")
+
+
 def _ws_ptr(ws, device: torch.device):
     if ws is None:
         return None
@@ -219,7 +273,8 @@ def dense(A: torch.Tensor, B: torch.Tensor, scale: float = 1.0, out: torch.Tenso
     Cm = _out(A, B, out)
     with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm(*_mat(A), *_mat(B), *_mat(Cm), A.size(0), B.size(0), A.size(1),
-                                      float(scale), dt, _ws_ptr(ws, A.device), None, _lib.stream_ptr(A.device)))
+                                      float(scale), dt, _ws_ptr(ws, A.device), _status_ptr(A.device),
+                                      _lib.stream_ptr(A.device)))
     return Cm
 
 
@@ -234,7 +289,7 @@ def dsd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, side: int, scale: flo
     Cm = _out(A, B, out)
     with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm_dsd(*_mat(A), *_mat(B), *_mat(Cm), M, B.size(0), K, plan.buf.data_ptr(),
-                                          side, float(scale), dt, _ws_ptr(ws, A.device), None,
+                                          side, float(scale), dt, _ws_ptr(ws, A.device), _status_ptr(A.device),
                                           _lib.stream_ptr(A.device)))
     return Cm
 
@@ -251,7 +306,7 @@ def sdd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float,
     with _on_device(A.device):
         fn = _lib.lib().sd_gemm_sdd if zero_dropped else _lib.lib().sd_gemm_sdd_kept
         _lib.check(fn(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),
-                                          float(scale), dt, _ws_ptr(ws, A.device), None, _lib.stream_ptr(A.device)))
+                   float(scale), dt, _ws_ptr(ws, A.device), _status_ptr(A.device), _lib.stream_ptr(A.device)))
     return Cm
 
 
@@ -266,7 +321,7 @@ def sdd_kept_t(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float, 
     Cm = _out(A, B, out)
     with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm_sdd_kept_t(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),
-                                                 float(scale), dt, _ws_ptr(ws, A.device), None,
+                                                 float(scale), dt, _ws_ptr(ws, A.device), _status_ptr(A.device),
                                                  _lib.stream_ptr(A.device)))
     return Cm
 
@@ -299,7 +354,7 @@ def dsd_panels(P: torch.Tensor, pixels: int, B: torch.Tensor, plan: BlockPlan, s
         raise RuntimeError(f"out must be {(M, N)}, got {tuple(Cm.shape)}")
     with _on_device(P.device):
         _lib.check(_lib.lib().sd_gemm_dsd_panels(P.data_ptr(), pixels, kg, *_mat(B), *_mat(Cm), N, plan.buf.data_ptr(),
-                                                 side, float(scale), dt, _ws_ptr(ws, P.device), None,
+                                                 side, float(scale), dt, _ws_ptr(ws, P.device), _status_ptr(P.device),
                                                  _lib.stream_ptr(P.device)))
     return Cm
 
@@ -317,7 +372,8 @@ def sdd_kept_t_panels(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: 
     with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm_sdd_kept_t_panels(*_mat(A), *_mat(B), out.data_ptr(), kg, pixels, A.size(1),
                                                         plan.buf.data_ptr(), float(scale), dt,
-                                                        _ws_ptr(ws, A.device), None, _lib.stream_ptr(A.device)))
+                                                        _ws_ptr(ws, A.device), _status_ptr(A.device),
+                                                        _lib.stream_ptr(A.device)))
     return out
 
 

@@ -14,7 +14,7 @@ colP[ceil(M/128)][K64][128], so that every kept 128x128 block is one contiguous 
   backward  DSD          : dW2d[Kout, K] written transposed, reduction over kept row blocks of each K tile
             SDD          : kept blocks of dcolP = W2d^T . dy2d^T / (1-p)         (plan of the transposed result)
             col2im_kept  : dx (NCHW) = adjoint gather over kept blocks           (HBM-bound)
-  By default the kept blocks of colT are saved for backward (151 MB at BASELINE's conv config, half of what an
+  By default the kept blocks of colT are saved for backward (151 MB for a 256x64x32x32 input with a 3x3 filter, half of what an
   unfold-based layer keeps); ``recompute_cols=True`` saves only the input (33 MB) and rebuilds colT in backward.
 """
 from __future__ import annotations

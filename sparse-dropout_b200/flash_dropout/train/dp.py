@@ -112,9 +112,29 @@ class FlatGradDataParallel:
         return all(p.grad is not None and p.grad.data_ptr() == base + self._esize * self._slices[p][0] for p in self.params)
 
 
+_steps_since_check = 0
+
+
+def _maybe_check_status(device: torch.device, check_every: int) -> None:
+    """Every ``check_every`` steps: read the kernels' failure-detection word (one stream synchronisation) and raise
+    if a device-side wait ran out of time during those steps."""
+    global _steps_since_check
+    if device.type != "cuda" or check_every <= 0:
+        return
+    _steps_since_check += 1
+    if _steps_since_check >= check_every:
+        _steps_since_check = 0
+        from flash_dropout.cuda.binding_gemm import check_status
+        check_status(device)
+
+
 def train_step(model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torch.optim.Optimizer, loss_fn,
-               autocast_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """zero grads -> forward/backward (bucket all-reduces overlap backward) -> wait -> optimizer step."""
+               autocast_dtype: torch.dtype | None = None, check_every: int = 64) -> torch.Tensor:
+    """zero grads -> forward/backward (bucket all-reduces overlap backward) -> wait -> optimizer step.
+
+    Every ``check_every`` steps (0 = never) the kernels' status word is read; a step whose kernels gave up on a
+    wait raises ``SparseDropError`` instead of training on with undefined gradients."""
+    _maybe_check_status(dp.flat_grad.device, check_every)
     dp.zero_grad()
     dev_type = dp.flat_grad.device.type
     if autocast_dtype is not None:
@@ -131,7 +151,7 @@ def train_step(model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torc
 class GraphedTrainStep:
     """zero_grad + forward + backward captured once in a CUDA graph and replayed every step.
 
-    The training steps BASELINE names are made of dozens of small launches (a plan kernel and three GEMMs per
+    The MLP and char-GPT training steps are made of dozens of small launches (a plan kernel and three GEMMs per
     DropoutMM, plus the model's other ops); eagerly they are bound by host launch overhead, which is what the
     reference's report identifies as the limit for small layers (report.pdf section 3.4).  Replaying a graph
     removes that.  Masks stay fresh because the plan kernel takes its Philox offset from a counter in device
@@ -182,7 +202,10 @@ class GraphedTrainStep:
             self.dp.flat_grad.div_(self.dp.world)
         self.optimizer.step()
 
+    check_every = 64      # steps between reads of the kernels' failure-detection word (0 = never)
+
     def __call__(self) -> torch.Tensor:
+        _maybe_check_status(self.dp.flat_grad.device, self.check_every)
         self.graph.replay()
         self._finish()
         return self.loss

@@ -20,10 +20,15 @@ def next_multiple(x: int, base: int) -> int:
 
 
 class BasicNet(nn.Module):
-    def __init__(self, input_dim: int, num_layers: int, hidden_dim: int, output_dim: int, dropout: dict):
+    """``input_dim`` may be the flattened input width or, as in the reference (eval/mlp/model.py:10-21), a sample
+    batch whose first element has that many entries."""
+
+    def __init__(self, input_dim: int | torch.Tensor, num_layers: int, hidden_dim: int, output_dim: int, dropout: dict):
         super().__init__()
         assert num_layers >= 0
         self.output_dim = output_dim
+        if isinstance(input_dim, torch.Tensor):
+            input_dim = input_dim[0].numel()
         self.in_proj = DropoutMM(input_dim, hidden_dim, **dropout)
         self.out_proj = DropoutMM(hidden_dim, next_multiple(output_dim, 128), **dropout)
         self.layers = nn.ModuleList(DropoutMM(hidden_dim, hidden_dim, **dropout) for _ in range(num_layers))

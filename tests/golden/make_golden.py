@@ -8,6 +8,8 @@ Imported from the reference (paths relative to its root):
     flash_dropout/functional/utils.py     blockwise_dropout_mask, mask_to_increment_table
     flash_dropout/functional/naive.py     blockwise_dropout_matmul_mask  (+ autograd for dx, dW)
     flash_dropout/functional/im2col_conv2d.py   im2col_conv2d
+    eval/mlp/model.py                     BasicNet   (variant "none", reduced width)
+    eval/llm/model.py                     GPT        (variant "none", reduced width)
 Masks fed to the reference are drawn by oracle/philox_mask.py (the reference's tests also draw one mask
 and hand it to both implementations, test/test_cuda.py:34); inputs are stored in the file so the
 fixture does not depend on any RNG version.
@@ -105,10 +107,44 @@ def main(ref_root: str) -> None:
         out[f"conv{i}_y"] = y.numpy()
     out["conv_count"] = np.int64(len(conv_cases))
 
+    # ---- 5. the two consumer models (eval/mlp/model.py:8-40, eval/llm/model.py:83-155) at reduced width, built by the
+    # reference's own classes with variant "none" (no randomness in forward): parameter names, shapes and values,
+    # logits (and the GPT loss) for a stored input.  eval/utils.py imports wandb, which is not needed for the
+    # models: an empty stand-in module satisfies the import.
+    import types
+    for name in ("wandb", "wandb.apis", "wandb.apis.public"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    sys.modules["wandb.apis.public"].Run = object
+    from eval.llm.model import GPT as RefGPT
+    from eval.mlp.model import BasicNet as RefBasicNet
+    torch.manual_seed(1234)
+    xs = torch.rand(16, 28, 28)
+    mlp = RefBasicNet(xs, 2, 128, 10, dict(p=0.5, variant="none", block_size=(128, 128))).train()
+    out["mlp_cfg"] = np.array([784, 2, 128, 10], dtype=np.int64)
+    out["mlp_x"] = xs.numpy()
+    out["mlp_logits"] = mlp(xs).detach().numpy()
+    out["mlp_param_names"] = np.array(list(mlp.state_dict().keys()))
+    for k, v in mlp.state_dict().items():
+        out["mlp_param/" + k] = v.numpy()
+    gpt = RefGPT(65, 32, 2, 4, 64, dict(p=0.2, variant="none", block_size=(128, 128))).train()
+    idx = torch.randint(0, 65, (4, 32))
+    logits, loss = gpt(idx)
+    out["gpt_cfg"] = np.array([65, 32, 2, 4, 64], dtype=np.int64)
+    out["gpt_idx"] = idx.numpy()
+    out["gpt_logits"] = logits.detach().numpy()
+    out["gpt_loss"] = np.float32(loss.item())
+    out["gpt_param_names"] = np.array(list(gpt.state_dict().keys()))
+    for k, v in gpt.state_dict().items():
+        out["gpt_param/" + k] = v.numpy()
+    # which parameters AdamW decays (eval/llm/model.py:157-173): every tensor with 2 or more dimensions
+    out["gpt_decay_names"] = np.array([n for n, q in gpt.named_parameters() if q.dim() >= 2])
+
     path = os.path.join(REPO, "tests", "golden", "reference_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes;", "torch", torch.__version__)
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/sparse-dropout")
+    main(sys.argv[1])

@@ -88,7 +88,7 @@ def test_conv_op_against_oracle(built_lib, geom, Ko, recompute):
 
 
 def test_conv_baseline_config_shapes(built_lib):
-    """BASELINE configs[2] at a reduced batch (N=16 of 256): 64 -> 128 channels, 32x32, 3x3, pad 1, p=0.5;
+    """The benchmark conv layer at a reduced batch (N=16 of 256): 64 -> 128 channels, 32x32, 3x3, pad 1, p=0.5;
     mask grid (N*1024/128) x 5 with a ragged last K block (576 = 4.5 blocks)."""
     import flash_dropout.functional as F
     from flash_dropout import random as sd_random
@@ -113,7 +113,7 @@ def test_conv_baseline_config_shapes(built_lib):
 
 
 def test_conv_full_size_properties(built_lib):
-    """BASELINE configs[2] at its full size (256 x 64 x 32 x 32, 64 -> 128, 3x3, pad 1): size-independent properties.
+    """The benchmark conv layer at its full size (256 x 64 x 32 x 32, 64 -> 128, 3x3, pad 1): size-independent properties.
 
     * p = 0 (nothing dropped): forward, dW and dx agree with cuDNN's dense convolution;
     * p = 0.5: the op equals the dense convolution machinery applied to an explicitly masked im2col matrix, checked

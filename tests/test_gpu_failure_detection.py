@@ -36,3 +36,39 @@ def test_selftest_rejects_long_limits(built_lib):
     words = torch.zeros(4, dtype=torch.int32, device=DEV)
     assert built_lib.sd_selftest_bounded_wait(words.data_ptr(), 5_000_000_000, None) == -1
     assert built_lib.sd_selftest_bounded_wait(None, 1000, None) == -1
+
+
+def test_operator_api_reports_a_timeout_and_recovers(built_lib):
+    """Every launch of the operator API carries the device's status word.  A time-out recorded in that word (made
+    here by the self-test kernel, whose waits nobody satisfies, run against the very same word) is raised by
+    flash_dropout.check_status(), which also re-arms the split-schedule workspace; the next layer call works."""
+    import flash_dropout
+    import flash_dropout.functional as F
+    from flash_dropout import _lib
+    from flash_dropout.cuda import binding_gemm as bg
+    from oracle import masked_dense as md
+    from oracle import philox_mask as pm
+    M, N, K, p = 256, 256, 4096, 0.5                          # 2 output tiles, 32 K tiles: the split schedule
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(M, K, generator=g) * K ** -0.25).half()
+    w = (torch.randn(N, K, generator=g) * K ** -0.25).half()
+    mask_np = pm.block_mask(M, K, 128, p, seed=1)
+    plan = bg.BlockPlan.from_mask(torch.from_numpy(mask_np).to(DEV), M, K, 128)
+    want = md.forward(x, mask_np, 128, p, w)
+    y = bg.dsd(x.to(DEV), w.to(DEV), plan, _lib.SD_PLAN_ROWS, 2.0)
+    flash_dropout.check_status(DEV)                           # healthy: returns quietly
+    torch.testing.assert_close(y.float().cpu(), want, rtol=1e-2, atol=1e-2)
+    words = bg.status_word(DEV)
+    stream = torch.cuda.current_stream(DEV).cuda_stream
+    assert built_lib.sd_selftest_bounded_wait(words.data_ptr(), 5_000_000, stream) == 0
+    ws = bg.workspace(DEV)
+    ws[:8].fill_(1)                                           # what a launch that gave up may leave: dirty counters
+    with pytest.raises(_lib.SparseDropError, match="bounded wait expired"):
+        flash_dropout.check_status(DEV)
+    assert words[0].item() == 0 and int(ws[:8].sum().item()) == 0     # word reset, workspace counters cleared
+    flash_dropout.check_status(DEV)                           # and quiet again
+    y2 = bg.dsd(x.to(DEV), w.to(DEV), plan, _lib.SD_PLAN_ROWS, 2.0)
+    torch.testing.assert_close(y2.float().cpu(), want, rtol=1e-2, atol=1e-2)
+    xa, wa = x.to(DEV).requires_grad_(), w.to(DEV).requires_grad_()
+    F.cuda_blockwise_dropout_matmul(xa, wa, 128, p).sum().backward()  # the autograd op still runs
+    flash_dropout.check_status(DEV)

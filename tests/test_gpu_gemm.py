@@ -138,7 +138,7 @@ def test_block_size_larger_than_tile(built_lib):
 
 
 def test_full_size_properties_4096(built_lib):
-    """BASELINE config 2 (4096^3, p = 0.5): size-independent properties instead of a CPU oracle pass.
+    """The headline GEMM size (4096^3, p = 0.5): size-independent properties instead of a CPU oracle pass.
 
     With whole-tile shares (no workspace) every output element is one sequential fp32 accumulation over its
     kept K tiles, so:
@@ -171,9 +171,57 @@ def test_full_size_properties_4096(built_lib):
     full = BlockPlan.from_seed(M, K, 128, 0.0, 0, 0, DEV)
     assert torch.equal(dsd(x, w, full, _lib.SD_PLAN_ROWS, 1.0), dense(x, w))
     assert torch.equal(sdd(dy, w.T, full, 1.0), dense(dy, w.T))
-    # against cuBLAS on the masked input (fp32 accumulate both sides)
+    # all three products against fp32 matmuls of the masked operands (fp32 accumulate both sides)
     torch.testing.assert_close(y.float(), s * (xz.float() @ w.float().T), rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(dx.float(), s * (dy.float() @ w.float()) * keep, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(dw.float(), s * (dy.float().T @ xz.float()), rtol=RTOL, atol=ATOL)
     torch.testing.assert_close(dsd(x, w, plan, _lib.SD_PLAN_ROWS, 2 * s).float(), 2 * y.float(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("la,lb", list(product(("row", "col"), repeat=2)))
+def test_dense_variants_4096_against_fp32(built_lib, la, lb):
+    """Every operand-major variant of the kernel at the full 4096^3 size against an fp32 matmul: descriptors, K
+    walks and stores beyond 2048 rows and columns, for K-major and MN-major operands alike."""
+    from flash_dropout.cuda import binding_gemm as bg
+    M = N = K = 4096
+    x, w, _ = (t.to(DEV) for t in _inputs(M, N, K, seed=13))
+    A = x.T.contiguous().T if la == "col" else x
+    B = w.T.contiguous().T if lb == "col" else w
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(bg.dense(A, B, ws=None).float(), want, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(bg.dense(A, B).float(), want, rtol=RTOL, atol=ATOL)
+
+
+# GEMM shapes (M, N, K, p) of the two training-step workloads, in the dtype those steps run in: the hidden layers
+# of the 784-1024-1024-1024-10 MLP at batch 512, and the attention projections, c_fc and c_proj of the 6-layer
+# d=384 char-GPT at 64 x 256 tokens.
+TRAIN_SHAPES = [(512, 1024, 1024, 0.5), (512, 128, 1024, 0.5), (16384, 384, 384, 0.2), (16384, 1536, 384, 0.2),
+                (16384, 384, 1536, 0.2)]
+
+
+@pytest.mark.parametrize("M,N,K,p", TRAIN_SHAPES)
+@pytest.mark.parametrize("use_ws", [True, False])
+def test_training_step_shapes_bf16(built_lib, M, N, K, p, use_ws):
+    """bf16 forward, dX and dW at the exact layer shapes of the MLP and GPT steps, with the workspace (dW of the
+    16384-row layers takes the split schedule) and without it (whole tiles), against the oracle."""
+    from flash_dropout import _lib
+    from flash_dropout.cuda import binding_gemm as bg
+    from flash_dropout.cuda.binding_gemm import BlockPlan
+    ws = "auto" if use_ws else None
+    x, w, dy = _inputs(M, N, K, seed=31, dtype=torch.bfloat16)
+    mask_np = pm.block_mask(M, K, 128, p, seed=32, offset=M + K)
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, 128, p, w, dy)
+    plan = BlockPlan.from_mask(torch.from_numpy(mask_np).to(DEV), M, K, 128)
+    A, B, dC = x.to(DEV), w.to(DEV), dy.to(DEV)
+    s = 1 / (1 - p)
+    tol = dict(rtol=2e-2, atol=4e-2)                              # bf16: 8-bit mantissa
+    torch.testing.assert_close(bg.dsd(A, B, plan, _lib.SD_PLAN_ROWS, s, ws=ws).float().cpu(), y_ref, **tol)
+    dX = bg.sdd(dC, B.T, plan, s, ws=ws)
+    torch.testing.assert_close(dX.float().cpu(), dx_ref, **tol)
+    assert (dX.float().cpu()[md._keep_matrix(mask_np, M, K, 128) == 0] == 0).all()
+    dW = torch.full((N, K), float("nan"), device=DEV, dtype=torch.bfloat16)
+    bg.dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, s, out=dW.T, ws=ws)
+    torch.testing.assert_close(dW.float().cpu(), dw_ref, **tol)
 
 
 def test_equal_share_schedule_4096(built_lib):

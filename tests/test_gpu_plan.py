@@ -8,7 +8,7 @@ from oracle import philox_mask as pm
 pytestmark = pytest.mark.gpu
 
 CASES = [  # (M, K, block_size, p, seed, offset)
-    (1024, 1024, 128, 0.5, 0, 0),            # BASELINE config 1 grid (8 x 8)
+    (1024, 1024, 128, 0.5, 0, 0),            # 8 x 8 grid (the 1024^3 CPU case)
     (4096, 4096, 128, 0.5, 0, 5),            # config 2 grid (32 x 32)
     (4096, 4096, 128, 0.0, 1, 0),
     (4096, 4096, 128, 0.999, 1, 0),          # whole rows dropped

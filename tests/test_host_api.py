@@ -148,3 +148,35 @@ def test_autocast_cast_cache_never_outlives_its_tensor():
     d = _autocast_input(x[0], torch.float16)
     e = _autocast_input(x[1], torch.float16)
     assert torch.equal(d, x[0].half()) and torch.equal(e, x[1].half())
+
+
+def _load_reference_params(model, golden, prefix):
+    names = [str(n) for n in golden[f"{prefix}_param_names"]]
+    assert list(model.state_dict().keys()) == names          # same names in the same order as the reference's
+    sd = {n: torch.from_numpy(golden[f"{prefix}_param/{n}"]) for n in names}
+    for n, v in model.state_dict().items():
+        assert tuple(v.shape) == tuple(sd[n].shape), n
+    model.load_state_dict(sd, strict=True)
+
+
+def test_models_load_reference_checkpoints(golden):
+    """The restated MLP and char-GPT take the reference models' state_dict unchanged and reproduce their logits
+    (eval/mlp/model.py:8-40, eval/llm/model.py:83-155; fixtures from the reference's own classes)."""
+    from flash_dropout.train import GPT, BasicNet
+    din, layers, hidden, dout = (int(v) for v in golden["mlp_cfg"])
+    x = torch.from_numpy(golden["mlp_x"])
+    for first_arg in (din, x):                               # width, or a sample batch as the reference passes
+        mlp = BasicNet(first_arg, layers, hidden, dout, dict(p=0.5, variant="none", block_size=(128, 128))).train()
+        _load_reference_params(mlp, golden, "mlp")
+        torch.testing.assert_close(mlp(x), torch.from_numpy(golden["mlp_logits"]), rtol=1e-5, atol=1e-5)
+    vocab, ctx, n_layer, n_head, n_embed = (int(v) for v in golden["gpt_cfg"])
+    gpt = GPT(vocab, ctx, n_layer, n_head, n_embed, dict(p=0.2, variant="none", block_size=(128, 128))).train()
+    _load_reference_params(gpt, golden, "gpt")
+    logits, loss = gpt(torch.from_numpy(golden["gpt_idx"]))
+    torch.testing.assert_close(logits, torch.from_numpy(golden["gpt_logits"]), rtol=1e-4, atol=1e-5)
+    assert abs(loss.item() - float(golden["gpt_loss"])) < 1e-4
+    opt = gpt.configure_optimizers(weight_decay=0.1, lr=1e-3, fused=False)
+    decayed = {id(q) for q in opt.param_groups[0]["params"]}
+    want = {str(n) for n in golden["gpt_decay_names"]}
+    assert {n for n, q in gpt.named_parameters() if id(q) in decayed} == want
+    assert opt.param_groups[0]["weight_decay"] == 0.1 and opt.param_groups[1]["weight_decay"] == 0.0
