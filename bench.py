@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE.json configs[1]): one SparseDrop linear at M = N = K = 4096, fp16 inputs, fp32
+Headline workload: one SparseDrop linear at M = N = K = 4096, fp16 inputs, fp32
 accumulation, 128 x 128 blocks, p = 0.5, inputs N(0, K^-1/2).  One "step" is the whole hot path for one
 batch: the Philox block-plan kernel (mask + kept-block lists), the DSD forward, the SDD dX and the DSD dW.
 The metric is useful TFLOP/s: 3 * 2 * 128^2 * N * (kept blocks of that step's mask) / time.
@@ -17,6 +17,10 @@ The metric is useful TFLOP/s: 3 * 2 * 128^2 * N * (kept blocks of that step's ma
 * cpu_baseline / --impl reference — the reference's CPU path (oracle/cpu_path.py) on the host cores.
 * N > 1    — one process per GPU (torchrun), data parallel: every rank runs the step on its own batch
              shard and the weight gradient is all-reduced over NCCL; weak scaling.
+* sub-records, appended last on the same JSON line and measured in the same process: `sustained` (>= 0.5 s of
+  back-to-back steps with the clocks seen), `p_sweep` (p = 0 .. 0.9), `conv` (the 256x64x32x32 3x3 conv layer,
+  forward + backward), `mlp` / `gpt` (training-step samples/s at this run's N, SparseDrop and vanilla dropout),
+  `c1_cpu` (the reference's 1024^3 fp32 forward on the host).
 """
 from __future__ import annotations
 
@@ -39,10 +43,11 @@ P_DROP = 0.5
 SEED = 0
 N_SETS = 4
 METRIC = "DSD/SDD useful TFLOP/s (DSD fwd + SDD dX + DSD dW on kept 128x128 blocks) at 4096^3 fp16, p=0.5"
-WORKLOAD = ("BASELINE configs[1]: SparseDrop linear fwd+bwd, M=N=K=4096, fp16 in / fp32 acc, 128x128 blocks, "
+WORKLOAD = ("SparseDrop linear fwd+bwd, M=N=K=4096, fp16 in / fp32 acc, 128x128 blocks, "
             "p=0.5, x,W,dy~N(0,K^-1/2), per-step Philox mask (seed 0, offset=step)")
-# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch at this workload (mean of the step's three launches:
-# 60.3 / 92.2 / 63.1 MB), from the ncu capture summarised in profiles/gemm_kernel_4096_p05.md.
+# DRAM bytes (read + written) per GEMM launch of this workload as an ncu capture counts them: the mean of the
+# step's three launches, 60.3 / 92.2 / 63.1 MB.  A profiler figure cannot be taken inside a timed run, so it is
+# carried here as a constant and reported as `roofline.traffic`.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 71.9e6
 
 
@@ -53,6 +58,14 @@ def measured_peaks() -> tuple[float, str]:
             return float(json.load(f)["bf16_tflops"]), "measured burst bf16 (MEASURED_PEAKS.json)"
     except (OSError, KeyError, ValueError):
         return 1590.0, "fallback 1.59 PFLOP/s (MEASURED_PEAKS.json absent)"
+
+
+def measured_peak(key: str, fallback: float) -> tuple[float, str]:
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)[key]), "measured"
+    except (OSError, KeyError, ValueError):
+        return fallback, "fallback"
 
 
 class ClockSampler:
@@ -112,6 +125,8 @@ def useful_flops(kept_tiles: int) -> float:
 
 # ------------------------------------------------------------------------------------------ reference arm
 def run_reference(args) -> None:
+    """The reference's own CPU implementation of the path (oracle/_ref when present, else the oracle port) on all
+    host threads; rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -123,16 +138,21 @@ def run_reference(args) -> None:
     tflops = useful_flops(r["kept_tiles"]) / r["seconds_per_pass"] / 1e12
     sample = (f"{r['passes']} full passes of the 4096^3 fwd+dX+dW masked-dense path in fp32 "
               f"(dense work: dropped blocks are not skipped on the CPU), median; {info['cpu_model']}")
+    c1 = cpu_path.time_forward_1024(seed=SEED, p=P_DROP)
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": r["passes"], "warmup": 1, "ms_per_step": r["seconds_per_pass"] * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "host": info["cpu_model"]},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": r["threads"], "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": r["threads"], "kind": r["kind"], "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "c1_cpu": {"workload": "fp32 forward y=(mask o x).W^T/(1-p), 1024^3, 128x128 blocks, p=0.5, seed 0",
+                   "ms": c1["ms"], "cores": c1["threads"], "kind": c1["kind"],
+                   "dense_equivalent_gflops": c1["dense_equivalent_gflops"]},
     }
     print(json.dumps(line))
+
 
 
 # ------------------------------------------------------------------------------------------ our arm
@@ -179,7 +199,7 @@ def run_ours(args) -> None:
                 h.wait()
                 pending[j] = None
 
-    def step(i: int, events=None):
+    def step(i: int, events=None, exchange: bool = True):
         x, w, dy, y, dx, dw = sets[i % N_SETS]
         plan = plans[i % N_SETS]
         if pending[i % N_SETS] is not None:
@@ -199,7 +219,7 @@ def run_ours(args) -> None:
         dsd(x.T, dy.T, plan, _lib.SD_PLAN_COLS, scale, out=dw.T)
         if events is not None:
             events[3].record()
-        if world > 1:
+        if world > 1 and exchange:
             # the gradient exchange runs on NCCL's stream while the next steps compute; it is waited for
             # before this operand set is used again (and at the end of the timed region)
             pending[i % N_SETS] = dist.all_reduce(dw, async_op=True)
@@ -296,7 +316,34 @@ def run_ours(args) -> None:
     e2e_kept = sum(int(pl.header[0].item()) for pl in e2e_plans)
     live = [None, None]
 
-    # ---- speed-up over the same kernels at p = 0 (the other half of the headline metric), rank 0 only
+    # ---- aggregate over ranks: max time, summed work
+    stats = torch.tensor([ms_total, e2e_ms, gemm_ms], device=dev, dtype=torch.float64)
+    work = torch.tensor([float(kept), float(e2e_kept)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, e2e_ms, gemm_ms_max = stats.tolist()
+    kept_all, e2e_kept_all = work.tolist()
+    # the end of a timed region is where the host synchronises anyway: did any kernel give up on a wait?
+    import flash_dropout
+    flash_dropout.check_status(dev)
+
+    # ---- training-step workloads at this run's N (every rank takes part), SparseDrop and vanilla dropout
+    train = {}
+    if not args.no_extras:
+        tsteps = max(10, min(steps, 50))
+        for wl in ("mlp", "gpt"):
+            rec = {}
+            for variant in ("blockwise[cuda]", "vanilla"):
+                r = measure_train(wl, variant, dev, world, rank, tsteps, 5, graph=True, e2e=False)
+                rec[variant] = {"samples_per_s": r["samples_per_s"], "ms_per_step": r["ms_per_step"]}
+                step_desc, wl_name = r["step"], r["workload"]
+            rec["speedup_vs_vanilla"] = rec["blockwise[cuda]"]["samples_per_s"] / rec["vanilla"]["samples_per_s"]
+            rec.update({"n_gpus": world, "steps": tsteps, "workload": wl_name, "step": step_desc})
+            train[wl] = rec
+        flash_dropout.check_status(dev)
+
+    # ---- rank 0 only: the same kernels over p (speed-up vs p = 0), a sustained run, the conv layer, CPU legs
     extra = {}
     if rank == 0 and not args.no_extras:
         def time_three(plan, sc, reps=10):
@@ -315,6 +362,7 @@ def run_ours(args) -> None:
                 ts.sort()
                 out.append(ts[len(ts) // 2])
             return out
+
         def time_stream(plan, sc, n=40, warm=5):
             """The three launches back to back over the rotating operand sets, as in the timed region above."""
             evs3 = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n)]
@@ -330,32 +378,68 @@ def run_ours(args) -> None:
                 if ev: ev[3].record()
             torch.cuda.synchronize()
             return [sum(ev[j].elapsed_time(ev[j + 1]) for ev in evs3) / n for j in range(3)]
-        sweep, stream_ms = {}, {}
-        for p in (0.0, 0.5):
-            plan = BlockPlan.from_seed(M, K, BLOCK, p, SEED, 0, dev)
-            t = time_three(plan, 1.0 / (1.0 - p))
-            stream_ms[p] = time_stream(plan, 1.0 / (1.0 - p))
-            nk = int(plan.header[0].item())
-            sweep[p] = (t, nk)
+
+        # p = 0, 0.1, ..., 0.9: one mask per p from (seed, offset = index of p); fwd + dX + dW
+        ps = [round(0.1 * i, 1) for i in range(10)]
+        stream_ms, cold_ms, kept_p = {}, {}, {}
+        for idx, p in enumerate(ps):
+            plan = BlockPlan.from_seed(M, K, BLOCK, p, SEED, 0 if p in (0.0, 0.5) else idx, dev)
+            stream_ms[p] = time_stream(plan, 1.0 / (1.0 - p), n=40 if p in (0.0, 0.5) else 20)
+            cold_ms[p] = time_three(plan, 1.0 / (1.0 - p), reps=10 if p in (0.0, 0.5) else 5)
+            kept_p[p] = int(plan.header[0].item())
         t0s, t5s = stream_ms[0.0], stream_ms[0.5]
-        c0s, c5s = sweep[0.0][0], sweep[0.5][0]
+        c0s, c5s = cold_ms[0.0], cold_ms[0.5]
         extra["speedup_vs_p0"] = {"fwd_dsd": t0s[0] / t5s[0], "dx_sdd": t0s[1] / t5s[1], "dw_dsd": t0s[2] / t5s[2],
                                   "fwd_bwd": sum(t0s) / sum(t5s), "ms_p0": t0s, "ms_p0.5": t5s,
-                                  "kept_p0.5": sweep[0.5][1],
+                                  "kept_p0.5": kept_p[0.5],
                                   "method": "mean of 40 back-to-back fwd/dX/dW triples over the rotating operand sets "
                                             "(the timed region's loop), same fixed mask for every triple",
                                   "cold_single_launch": {"fwd_bwd": sum(c0s) / sum(c5s), "ms_p0": c0s, "ms_p0.5": c5s,
                                                          "method": "median of 10 single launches, L2 flushed and the "
                                                                    "stream drained between launches"}}
+        r3 = lambda v: round(v, 4)
+        extra["p_sweep"] = {
+            "p": ps, "kept_blocks": [kept_p[p] for p in ps],
+            "fwd_bwd_ms": [r3(sum(stream_ms[p])) for p in ps],
+            "speedup_vs_p0": [r3(sum(t0s) / sum(stream_ms[p])) for p in ps],
+            "useful_tflops": [r3(useful_flops(kept_p[p]) / (sum(stream_ms[p]) * 1e-3) / 1e12) for p in ps],
+            "cold_fwd_bwd_ms": [r3(sum(cold_ms[p])) for p in ps],
+            "cold_speedup_vs_p0": [r3(sum(c0s) / sum(cold_ms[p])) for p in ps],
+            "method": "fwd+dX+dW at 4096^3 fp16, one Philox mask per p; back-to-back triples over rotating operand "
+                      "sets (mean), and single launches with L2 flushed and the stream drained (median)"}
 
-    # ---- aggregate over ranks: max time, summed work
-    stats = torch.tensor([ms_total, e2e_ms, gemm_ms], device=dev, dtype=torch.float64)
-    work = torch.tensor([float(kept), float(e2e_kept)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(work, op=dist.ReduceOp.SUM)
-    ms_total, e2e_ms, gemm_ms_max = stats.tolist()
-    kept_all, e2e_kept_all = work.tolist()
+        # sustained: the whole step back to back for at least half a second, with the clocks seen meanwhile
+        n_sus = max(3000, int(0.6 / max(1e-6, ms_total / steps * 1e-3)))
+        torch.cuda.synchronize()
+        sampler2 = ClockSampler(local, period_s=0.01)
+        sampler2.start()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.perf_counter()
+        s0.record()
+        for i in range(n_sus):
+            step(10_000 + i, exchange=False)
+        s1.record()
+        torch.cuda.synchronize()
+        w1 = time.perf_counter()
+        clocks2 = sampler2.stop(w0, w1)
+        sus_ms = s0.elapsed_time(s1)
+        kept_dev.zero_()
+        for i in range(n_sus):
+            _lib.check(L.sd_plan_from_seed(plans[0].buf.data_ptr(), plans[0].R, plans[0].C, 1, SEED,
+                                           (rank << 40) + 10_000 + i, P_DROP, None, stream.cuda_stream))
+            kept_dev += plans[0].header[0]
+        sus_tflops = useful_flops(kept_dev.item()) / (sus_ms * 1e-3) / 1e12
+        sus_peak, sus_src = measured_peak("bf16_tflops_sustained", 1400.0)
+        extra["sustained"] = {"seconds": sus_ms * 1e-3, "steps": n_sus, "ms_per_step": sus_ms / n_sus,
+                              "useful_tflops": sus_tflops, "peak": sus_peak,
+                              "peak_source": f"{sus_src} sustained bf16", "frac": sus_tflops / sus_peak,
+                              "clocks": clocks2, "power_capped": "sw_power_cap" in (clocks2.get("reasons") or [])}
+        flash_dropout.check_status(dev)
+        sets.clear()
+        plans.clear()
+        torch.cuda.empty_cache()
+        extra["conv"] = measure_conv(dev, max(10, min(steps, 30)), 3, extras=False)
+        flash_dropout.check_status(dev)
 
     if rank == 0:
         value = useful_flops(kept_all) / (ms_total * 1e-3) / 1e12
@@ -381,39 +465,61 @@ def run_ours(args) -> None:
                            "H2D / compute / D2H of consecutive steps overlap on three streams"},
             "gpu_launches": 4 * steps, "clocks": clocks,
         }
-        line.update(extra)
         if world == 1 and not args.no_extras:
             from oracle import cpu_path
             info = cpu_path.host_info()
             r = cpu_path.time_linear_fwd_bwd(M, N, K, BLOCK, P_DROP, seed=SEED, budget_s=12.0, max_passes=4)
             line["cpu_baseline"] = {
                 "value": useful_flops(r["kept_tiles"]) / r["seconds_per_pass"] / 1e12, "unit": "TFLOP/s",
-                "cores": r["threads"], "kind": "port",
+                "cores": r["threads"], "kind": r["kind"],
                 "sample": f"{r['passes']} full 4096^3 fwd+dX+dW passes, fp32 masked-dense (no block skipping), "
                           f"median {r['seconds_per_pass']:.3f} s; {info['cpu_model']}"}
+        # sub-records last: a reader that keeps only the end of the line still sees them
+        for key in ("speedup_vs_p0", "sustained", "p_sweep", "conv"):
+            if key in extra:
+                line[key] = extra[key]
+        line.update(train)
+        if not args.no_extras:
+            from oracle import cpu_path
+            c1 = cpu_path.time_forward_1024(seed=SEED, p=P_DROP)
+            line["c1_cpu"] = {"workload": "fp32 forward y=(mask o x).W^T/(1-p), 1024^3, 128x128 blocks, p=0.5, seed 0",
+                              "ms": c1["ms"], "cores": c1["threads"], "kind": c1["kind"],
+                              "dense_equivalent_gflops": c1["dense_equivalent_gflops"]}
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
-# ------------------------------------------------------------------------------------------ conv
-def run_conv(args) -> None:
-    """BASELINE configs[2]: Conv2d 64->128, 3x3, pad 1 on 256x64x32x32 fp16, blockwise dropout p=0.5, fwd+bwd."""
+# ------------------------------------------------------------------------------------------ conv layer
+CONV_SHAPE = dict(Nb=256, C=64, H=32, W=32, Ko=128)
+
+
+def conv_algorithmic_bytes() -> float:
+    """Bytes a fused forward + backward of the conv layer has to move: forward reads x and writes y; backward reads
+    dy twice (dW and dX), reads x once more (dW) and writes dx; the weights are negligible."""
+    c = CONV_SHAPE
+    x = c["Nb"] * c["C"] * c["H"] * c["W"] * 2
+    y = c["Nb"] * c["Ko"] * c["H"] * c["W"] * 2
+    return float(x + y + 2 * y + x + x)
+
+
+def measure_conv(dev, steps: int, warmup: int, extras: bool) -> dict:
+    """Conv2d 64->128, 3x3, pad 1 on 256x64x32x32 fp16 with blockwise dropout p=0.5 on the im2col matrix
+    (262144 x 576, 128x128 blocks): forward + backward, replayed from a CUDA graph, L2 flushed between steps."""
     import torch
 
     import flash_dropout.functional as F
     from flash_dropout import random as sd_random
     from flash_dropout.cuda.binding_gemm import BlockPlan
 
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    Nb, C, H, W, Ko, p = 256, 64, 32, 32, 128, P_DROP
+    c = CONV_SHAPE
+    Nb, C, H, W, Ko, p = c["Nb"], c["C"], c["H"], c["W"], c["Ko"], P_DROP
     g = torch.Generator().manual_seed(SEED)
     x = torch.randn(Nb, C, H, W, generator=g).half().to(dev).requires_grad_()
     k = (torch.randn(Ko, C, 3, 3, generator=g) / 24).half().to(dev).requires_grad_()
     dy = torch.randn(Nb, Ko, H, W, generator=g).half().to(dev).contiguous(memory_format=torch.channels_last)
     M, K = Nb * H * W, C * 9
-    steps, warmup = args.steps, max(args.warmup, 3)
     sd_random.manual_seed(SEED, subsequence=0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
@@ -433,12 +539,12 @@ def run_conv(args) -> None:
         y = F.cuda_blockwise_dropout_matmul(a, k.reshape(Ko, K), BLOCK, p)
         y.backward(dy.permute(0, 2, 3, 1).reshape(M, Ko))
 
-    def timeit(fn):
+    def timeit(fn, n):
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
         ts = []
-        for _ in range(steps):
+        for _ in range(n):
             flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); fn(); b.record(); torch.cuda.synchronize()
@@ -460,59 +566,74 @@ def run_conv(args) -> None:
             fn()
         return graph.replay
 
-    # The step is ~10 launches behind ~0.3 ms of Python: timed eagerly it is bound by the host, so the headline is
-    # the replay of a captured step (both arms), with the eager times beside it.
-    eager_sparse, eager_dense = timeit(sparse_step), timeit(dense_step)
-    t_unfold = timeit(unfold_step) if not args.no_extras else None
-    if sd_random.device_counter(dev) is None:
+    # The step is a handful of launches behind ~0.3 ms of Python: timed eagerly it is bound by the host, so the
+    # headline is the replay of a captured step (both arms), with the eager times beside it when extras are on.
+    out_ms = {}
+    if extras:
+        out_ms["sparsedrop_eager"] = timeit(sparse_step, steps)
+        out_ms["cudnn_dense_eager"] = timeit(dense_step, steps)
+        out_ms["torch_unfold+sparsedrop_linear_eager"] = timeit(unfold_step, max(3, steps // 4))
+    had_counter = sd_random.device_counter(dev) is not None
+    if not had_counter:
         sd_random.enable_device_counter(dev)
-    t_sparse, t_dense = timeit(graphed(sparse_step)), timeit(graphed(dense_step))
-    plan = BlockPlan.from_seed(M, K, BLOCK, p, SEED, 0, dev)
+    t_sparse, t_dense = timeit(graphed(sparse_step), steps), timeit(graphed(dense_step), steps)
+    if not had_counter:
+        sd_random.disable_device_counter()
+    plan = BlockPlan.from_seed(M, 640, BLOCK, p, SEED, 0, dev)
     mask = plan.tile_mask.cpu()
     widths = torch.tensor([128, 128, 128, 128, 64])            # last K block is 64 wide (576 = 4.5 blocks)
     kept_cols = ((mask == 0).float() * widths).sum().item()    # kept (row block, k) columns
     flops = 3 * 2.0 * 128 * Ko * kept_cols                     # fwd + dW + dX on kept blocks
+    hbm, hbm_src = measured_peak("hbm_gbs", 6650.0)
+    tens, _ = measured_peak("bf16_tflops", 1590.0)
+    bytes_alg = conv_algorithmic_bytes()
+    t_roof_ms = max(bytes_alg / (hbm * 1e9), flops / (tens * 1e12)) * 1e3
+    out_ms["sparsedrop_graph"] = t_sparse
+    out_ms["cudnn_dense_graph"] = t_dense
+    return {"workload": "Conv2d 64->128 3x3 pad 1, input 256x64x32x32 fp16, 128x128 blocks on the im2col matrix "
+                        "(262144 x 576), p=0.5, fwd+bwd; CUDA graph replay, 256 MB L2 flush between steps",
+            "ms_per_step": t_sparse, "useful_tflops": flops / (t_sparse * 1e-3) / 1e12,
+            "speedup_vs_cudnn_dense": t_dense / t_sparse, "compare_ms": out_ms,
+            "roofline": {"bound": "hbm", "algorithmic_bytes": bytes_alg, "useful_flops": flops,
+                         "floor_ms": t_roof_ms, "frac": t_roof_ms / t_sparse,
+                         "peak": f"{hbm_src} {hbm:.0f} GB/s copy, {tens:.0f} TFLOP/s"}}
+
+
+def run_conv(args) -> None:
+    import torch
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    r = measure_conv(dev, steps, warmup, extras=not args.no_extras)
     print(json.dumps({
-        "metric": "SparseDrop conv fwd+bwd useful TFLOP/s", "value": flops / (t_sparse * 1e-3) / 1e12, "unit": "TFLOP/s",
-        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": t_sparse, "higher_is_better": True,
+        "metric": "SparseDrop conv fwd+bwd useful TFLOP/s", "value": r["useful_tflops"], "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": "BASELINE configs[2]: Conv2d 64->128 3x3 pad 1, input 256x64x32x32 fp16, 128x128 blocks "
-                               "on the im2col matrix (262144 x 576), p=0.5, fwd+bwd", "l2": "256 MB flush between steps",
-                   "step": "CUDA graph replay of forward + backward"},
-        "compare_ms": {"sparsedrop_im2col_kept+dsd/sdd": t_sparse, "cudnn_dense_conv_fwd_bwd": t_dense,
-                       "sparsedrop_eager": eager_sparse, "cudnn_dense_eager": eager_dense,
-                       "torch_unfold+sparsedrop_linear_eager": t_unfold},
-        "gpu_launches": 6 * steps}))
+        "config": {"workload": r["workload"]}, "compare_ms": r["compare_ms"], "roofline": r["roofline"],
+        "gpu_launches": 4 * steps}))
 
 
 # ------------------------------------------------------------------------------------------ training steps
-def run_train(args) -> None:
-    """BASELINE configs[3] (MLP) / configs[4] (char-GPT): one optimizer step per "step", batch sharded over ranks."""
+def measure_train(workload: str, variant: str, dev, world: int, rank: int, steps: int, warmup: int,
+                  graph: bool = True, e2e: bool = True) -> dict:
+    """One optimizer step per "step" of the MLP (784-1024-1024-1024-10, batch 512/GPU, p=0.5, AdamW lr 1e-3) or the
+    char-GPT (6 layers, d=384, 6 heads, ctx 256, vocab 65, batch 64/GPU, p=0.2, AdamW), bf16 autocast, batch sharded
+    over the ranks.  The process group, if any, is already initialised."""
     import torch
     import torch.distributed as dist
 
     from flash_dropout import random as sd_random
     from flash_dropout.train import GPT, BasicNet, FlatGradDataParallel, train_step
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the SparseDrop kernels have no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(SEED)
-    variant = args.variant
-    if args.workload == "mlp":
+    if workload == "mlp":
         per_gpu, p = 512, 0.5
         model = BasicNet(784, 2, 1024, 10, dict(p=p, variant=variant, block_size=(128, 128))).to(dev)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True)
         g = torch.Generator().manual_seed(SEED + 1 + rank)
         host_x = torch.rand(per_gpu, 28, 28, generator=g).pin_memory()
         host_y = torch.randint(0, 10, (per_gpu,), generator=g).pin_memory()
-        name = "BASELINE configs[3]: MLP 784-1024-1024-1024-10, bf16 autocast, batch 512/GPU, p=0.5, AdamW lr 1e-3"
+        name = "MLP 784-1024-1024-1024-10, bf16 autocast, batch 512/GPU, p=0.5, AdamW lr 1e-3"
         loss_of = lambda m, x, y: torch.nn.functional.cross_entropy(m(x).float(), y)
     else:
         per_gpu, p = 64, 0.2
@@ -521,12 +642,11 @@ def run_train(args) -> None:
         g = torch.Generator().manual_seed(SEED + 1 + rank)
         host_x = torch.randint(0, 65, (per_gpu, 256), generator=g).pin_memory()
         host_y = host_x
-        name = "BASELINE configs[4]: char-GPT 6 layers d=384 6 heads ctx 256 vocab 65, bf16 autocast, batch 64/GPU, p=0.2, AdamW"
+        name = "char-GPT 6 layers d=384 6 heads ctx 256 vocab 65, bf16 autocast, batch 64/GPU, p=0.2, AdamW"
         loss_of = lambda m, x, y: m(x)[1]
     dp = FlatGradDataParallel(model)
     sd_random.manual_seed(SEED, subsequence=rank)
     x_dev, y_dev = host_x.to(dev), host_y.to(dev)
-    steps, warmup = args.steps, max(args.warmup, 3)
 
     def barrier():
         if world > 1:
@@ -534,7 +654,7 @@ def run_train(args) -> None:
         torch.cuda.synchronize()
 
     graphed = None
-    if not args.no_graph:
+    if graph:
         from flash_dropout.train import GraphedTrainStep
         graphed = GraphedTrainStep(model, dp, opt, loss_of, (x_dev, y_dev), autocast_dtype=torch.bfloat16)
 
@@ -553,12 +673,14 @@ def run_train(args) -> None:
         loss = train_step(model, dp, opt, lambda m: loss_of(m, x, y), autocast_dtype=torch.bfloat16)
         return loss if resident else loss.item()
 
-    results = {}
+    results, clocks, last = {}, None, 0.0
     for label, resident in (("value", True), ("e2e", False)):
+        if label == "e2e" and not e2e:
+            continue
         for _ in range(warmup):
             one(resident)
         barrier()
-        sampler = ClockSampler(local) if label == "value" else None
+        sampler = ClockSampler(dev.index) if label == "value" else None
         if sampler:
             sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -575,24 +697,49 @@ def run_train(args) -> None:
         results[label] = ms.item()
         if sampler:
             clocks = sampler.stop(t0, t1)
+    n_mm = sum(1 for m in model.modules() if m.__class__.__name__ == "DropoutMM")
+    out = {"workload": name, "variant": variant, "per_gpu": per_gpu, "n_gpus": world,
+           "samples_per_s": per_gpu * world * steps / (results["value"] * 1e-3),
+           "ms_per_step": results["value"] / steps, "clocks": clocks, "final_loss": float(last),
+           "step": graphed.describe() if graphed is not None and hasattr(graphed, "describe") else
+                   ("CUDA graph replay" if graphed is not None else
+                    "zero_grad + fwd + bwd (bucketed NCCL all-reduce overlapped) + optimizer"),
+           "gpu_launches": (4 * n_mm * steps) if "blockwise[cuda]" in variant else 0,
+           "h2d_bytes_per_step": host_x.numel() * host_x.element_size()
+                                 + (0 if host_y is host_x else host_y.numel() * 8)}
+    if "e2e" in results:
+        out["e2e_samples_per_s"] = per_gpu * world * steps / (results["e2e"] * 1e-3)
+        out["e2e_ms_per_step"] = results["e2e"] / steps
+    # free the step's graph and model before the next measurement
+    del graphed, dp, opt, model
+    torch.cuda.synchronize()
+    return out
+
+
+def run_train(args) -> None:
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the SparseDrop kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    r = measure_train(args.workload, args.variant, dev, world, rank, steps, warmup, graph=not args.no_graph)
     if rank == 0:
-        n_mm = sum(1 for m in model.modules() if m.__class__.__name__ == "DropoutMM")
-        line = {
-            "metric": "train-step samples/s", "value": per_gpu * world * steps / (results["value"] * 1e-3),
-            "unit": "samples/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": results["value"] / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 autocast (fp32 accumulate, fp32 master weights)", "data": "synthetic",
-            "config": {"workload": name, "variant": variant, "parallelism": f"dp{world}",
-                       "step": ("CUDA graph replay of zero_grad + fwd + bwd, then flat NCCL all-reduce + optimizer"
-                                if graphed is not None else
-                                "zero_grad + fwd + bwd (bucketed NCCL all-reduce overlapped) + optimizer")},
-            "e2e": {"value": per_gpu * world * steps / (results["e2e"] * 1e-3), "unit": "samples/s",
-                    "h2d_bytes_per_step": host_x.numel() * host_x.element_size() + (0 if host_y is host_x else host_y.numel() * 8),
-                    "d2h_bytes_per_step": 4, "ms_per_step": results["e2e"] / steps},
-            "gpu_launches": (4 * n_mm * steps) if "blockwise[cuda]" in variant else 0, "clocks": clocks,
-            "final_loss": float(last),
-        }
-        print(json.dumps(line))
+        print(json.dumps({
+            "metric": "train-step samples/s", "value": r["samples_per_s"], "unit": "samples/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast (fp32 accumulate, fp32 master weights)",
+            "data": "synthetic",
+            "config": {"workload": r["workload"], "variant": r["variant"], "parallelism": f"dp{world}", "step": r["step"]},
+            "e2e": {"value": r.get("e2e_samples_per_s"), "unit": "samples/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                    "d2h_bytes_per_step": 4, "ms_per_step": r.get("e2e_ms_per_step")},
+            "gpu_launches": r["gpu_launches"], "clocks": r["clocks"], "final_loss": r["final_loss"]}))
     if world > 1:
         dist.destroy_process_group()
 
@@ -609,7 +756,7 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true",
                     help="training workloads: launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-extras", action="store_true",
-                    help="skip the p=0 comparison and the CPU baseline (short runs under a profiler)")
+                    help="skip the sub-records, the p=0 comparison and the CPU baseline (short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
