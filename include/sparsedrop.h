@@ -268,6 +268,38 @@ int sd_gemm_sdd_kept_t_panels(const void* A, int64_t a_rs, int64_t a_cs,
                               void* P, int kg, int pixels, int K, const void* plan,
                               float scale, int dtype, void* workspace, int* status, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Fused convolution: im2col + DSD in one kernel.  The A operand of the product is the im2col matrix of
+ * flash_dropout/functional/im2col_conv2d.py:17-20 (rows = output pixels m = (n, p, q), columns k = c*R*S + r*S + s),
+ * but it is never written to memory: extra warps of the GEMM kernel gather each 64-wide stage of it straight from
+ * the contiguous NCHW input x into shared memory, and only the kept blocks of the plan are ever gathered.  The plan
+ * is the one of the N*P*Q x C*R*S matrix, ceil(N*P*Q/128) x ceil(C*R*S/128).  Served geometries (ask
+ * sd_conv_fused_supported; other geometries use the sd_im2col_kept path): S = 3, unit horizontal stride and
+ * dilation, pad_w = 1, W in {8, 16, 32, 64}; any R, vertical stride, dilation and padding.  No counterpart in the
+ * reference, whose conv layer materialises the matrix with F.unfold (im2col_conv2d.py:17) and has no blockwise
+ * dropout (flash_dropout/layers/dropout_conv.py:86-99 is commented out).
+ * ------------------------------------------------------------------------------------------ */
+
+/* 1 if the geometry is served by sd_conv_dsd_fwd / sd_conv_dsd_dw, else 0. */
+int sd_conv_fused_supported(int N, int C, int H, int W, int R, int S,
+                            int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w);
+
+/* Forward: Y2d[N*P*Q, Ko] = scale * (keep o im2col(x)) . W2d^T with W2d[Ko, >= C*R*S] (the filter viewed 2-D;
+ * columns past C*R*S are never read).  Y2d viewed (N, P, Q, Ko) is the channels-last result. */
+int sd_conv_dsd_fwd(const void* x, int N, int C, int H, int W, int R, int S,
+                    int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                    const void* W2d, int64_t w_rs, int64_t w_cs,
+                    void* Y2d, int64_t y_rs, int64_t y_cs, int Ko,
+                    const void* plan, float scale, int dtype, void* workspace, int* status, void* stream);
+
+/* Weight gradient: dW2d[Ko, C*R*S] = scale * dY2d^T . (keep o im2col(x)) with dY2d[N*P*Q, Ko]; columns of dW2d
+ * past C*R*S (if its row stride leaves room for any) are not written.  Reduces over all pixels: pass a workspace. */
+int sd_conv_dsd_dw(const void* x, int N, int C, int H, int W, int R, int S,
+                   int pad_h, int pad_w, int stride_h, int stride_w, int dil_h, int dil_w,
+                   const void* dY2d, int64_t dy_rs, int64_t dy_cs,
+                   void* dW2d, int64_t dw_rs, int64_t dw_cs, int Ko,
+                   const void* plan, float scale, int dtype, void* workspace, int* status, void* stream);
+
 /*
  * Exercises the bounded device-side waits the kernels are built on, without a fault or a hang: a one-warp kernel
  * waits on a barrier nobody arrives on and on a counter nobody increments, each for at most limit_ns (<= 1 s),

@@ -81,6 +81,19 @@ constexpr size_t WS_SLOT_BYTES = WS_SLOT_FLOATS * sizeof(float);   // 128 KiB; o
 enum GemmMode { MODE_DENSE = 0, MODE_DSD = 1, MODE_SDD = 2 };
 enum StatusCode { ST_PRODUCER = 1, ST_MMA_FULL = 2, ST_MMA_ACC = 3, ST_EPILOGUE = 4, ST_FIXUP = 5 };
 
+// Geometry of a convolution whose im2col matrix (rows = output pixels m = (n, p, q), columns k = c*R*3 + r*3 + s,
+// the unfold order of flash_dropout/functional/im2col_conv2d.py:17-20) is the A operand, built on the fly by the
+// gather warps instead of being read through a tensor map.  Only filters 3 wide with unit horizontal stride and
+// dilation and one column of padding (so Q == W) on rows of 8, 16, 32 or 64 pixels take this path.
+struct ConvGather {
+    const unsigned short* x;     // NCHW input, contiguous, 16-byte aligned
+    int C, H, W, R, P;
+    int stride_h, dil_h, pad_h;
+    int PQ, HW;
+    int k_real;                  // C * R * 3: columns of the im2col matrix that exist
+    int pixels;                  // N * P * Q: rows that exist
+};
+
 struct GemmArgs {
     int mode;
     int MM, NN, KK;
@@ -108,6 +121,7 @@ struct GemmArgs {
     int tma_store;                   // result written by TMA from a swizzled staging buffer: 1 row-major, 2 column-major
     float* ws_slots;
     int* ws_flags;
+    ConvGather conv;                 // used by the GATHER variants of the kernel only
 };
 
 // The part [i0, i1) of one output tile's kept K-tile list that this CTA computes.
@@ -474,7 +488,17 @@ __device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int eidx, 
 }
 
 // ------------------------------------------------------------------ the kernel
-template <bool A_MN, bool B_MN>
+// GATHER selects how the A operand reaches shared memory:
+//   0  TMA loads through tmapA (every product of a linear layer, and the conv's materialised im2col matrix);
+//   1  conv forward: A = the im2col matrix, rows = output pixels (MN-major in shared memory), gathered from the
+//      NCHW input by four extra warps; the matrix never exists in global memory;
+//   2  conv dW: A = the transposed im2col matrix, rows = k, reduction over pixels (K-major), gathered likewise.
+// The gather warps come after the B producer warp; warp 0 then has nothing to do.  They work as two groups of two
+// warps that take alternate stages, so two stages are being filled at any time and each thread keeps six 16-byte
+// loads in flight; a stage's `full` barrier counts the B producer plus the two warps of the group that fills it.
+constexpr int GATHER_WARPS = 4;
+
+template <bool A_MN, bool B_MN, int GATHER = 0>
 __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1)
 sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                        const __grid_constant__ CUtensorMap tmapC, const GemmArgs g) {
@@ -491,19 +515,22 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     uint8_t* staging = aligned + TILE_SMEM;   // 32 KiB of TMA-store staging, 1024-aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_warps = blockDim.x >> 5;
+    const int b_producer_warp = n_warps - 1 - (GATHER ? GATHER_WARPS : 0);
+    const int epi_warps = n_warps - 3 - (GATHER ? GATHER_WARPS : 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 2);                         // the A producer and the B producer
+            mbar_init(bar_full + 8 * s, GATHER ? 3 : 2);            // the A producer (or two gather warps) and the B producer
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, (blockDim.x >> 5) - 3);   // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8 * a, epi_warps);               // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_mbar_init();
-        tma_prefetch_desc(&tmapA);
+        if (!GATHER) tma_prefetch_desc(&tmapA);
         tma_prefetch_desc(&tmapB);
         if (g.tma_store) tma_prefetch_desc(&tmapC);
     }
@@ -522,14 +549,13 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
 
     const int n_ctas = gridDim.x, cta = blockIdx.x;
 
-    const int b_producer_warp = (blockDim.x >> 5) - 1;
     if (warp == 0 || warp == b_producer_warp) {
         // ============================== producers: warp 0 loads the A tiles, the last warp the B tiles.  Two threads
         // because one thread issues a tensor load only every ~110 cycles: the six loads of a stage with both operands
         // MN-major, or the index walk between the short tiles of a conv, would otherwise sit on the critical path.
         // Each arrives on the stage's `full` barrier with its own byte count.
         const bool loads_a = warp == 0;
-        if (lane == 0) {
+        if (lane == 0 && !(GATHER && loads_a)) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -623,11 +649,102 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             }
         }
         __syncwarp();
+    } else if (GATHER && warp > b_producer_warp) {
+        // ============================== gather warps: build the A tile of a stage from the NCHW input.
+        // One work item = one aligned 8-pixel chunk of one input row for one (channel, filter row): the three taps
+        // s = 0, 1, 2 are that chunk shifted by -1, 0, +1 pixel, the pixel that comes in at either end is traded
+        // with the neighbouring lane (which owns the neighbouring chunk of the same image row), and the item writes
+        // up to three k-rows of the 128B-swizzled stage.  Rows and pixels that do not exist are written as zeros.
+        const int gw = warp - b_producer_warp - 1, group = gw >> 1;
+        const int t = ((gw & 1) << 5) | lane;                       // 0..63 inside the group
+        const ConvGather& cv = g.conv;
+        // GATHER 1: 16 pixel chunks x 4 (c, r) pairs per pass;  GATHER 2: 8 pixel chunks x 8 pairs per pass
+        const int chunk = GATHER == 1 ? (t & 15) : (t & 7), tsub = GATHER == 1 ? (t >> 4) : (t >> 3);
+        constexpr int PAIRS_PER_PASS = GATHER == 1 ? 4 : 8, PASSES = 6;
+        int stage = 0;
+        uint32_t phase = 0, sc = 0;
+        bool ok = true;
+        WorkIter it;
+        it.init(g, cta, n_ctas);
+        Seg w;
+        while (ok && it.next(g, w)) {
+            for (int i = w.i0; ok && i < w.i1; ++i) {
+                const int kb = w.klist ? __ldg(w.klist + i) : i;
+                for (int h = 0; h < 2; ++h) {
+                    const int k = kb * 128 + h * BK;
+                    if (k >= g.KK) break;
+                    const bool mine = (sc & 1) == uint32_t(group);
+                    ++sc;
+                    if (mine) {
+                        ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status, ST_PRODUCER);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        const uint32_t sA = tiles + stage * STAGE_BYTES;
+                        // rows of the stage = k-rows [k_lo, k_hi) of the im2col matrix; this thread's 8 pixels start at m0
+                        const int k_lo = GATHER == 1 ? k : w.a_row;
+                        const int k_hi = min(k_lo + (GATHER == 1 ? BK : 128), cv.k_real);
+                        const int m0 = (GATHER == 1 ? w.a_row : k) + chunk * 8;
+                        const bool live = m0 < cv.pixels;
+                        const int n = live ? m0 / cv.PQ : 0, pq = m0 - n * cv.PQ, p = pq / cv.W, q0 = pq - p * cv.W;
+                        const unsigned short* xn = cv.x + (long long)n * cv.C * cv.HW + q0;
+                        const int hbase = p * cv.stride_h - cv.pad_h;
+                        const bool has_left = q0 > 0, has_right = q0 + 8 < cv.W;
+                        const int rows = k_hi - k_lo;
+                        const int cr_begin = k_lo / 3, cr_end = (k_hi + 2) / 3;
+                        uint4 v[PASSES];
+#pragma unroll
+                        for (int u = 0; u < PASSES; ++u) {
+                            const int cr = cr_begin + tsub + PAIRS_PER_PASS * u;
+                            v[u] = make_uint4(0, 0, 0, 0);
+                            if (cr < cr_end && live) {
+                                const int c = cr / cv.R, r = cr - c * cv.R;
+                                const int hh = hbase + r * cv.dil_h;
+                                if ((unsigned)hh < (unsigned)cv.H)
+                                    v[u] = __ldg(reinterpret_cast<const uint4*>(xn + (long long)c * cv.HW + hh * cv.W));
+                            }
+                        }
+                        // address of (k-row kk, this thread's chunk): MN-major stage = two 64-pixel atoms of 64 k-rows
+                        // of 128 bytes; K-major stage = 128 k-rows of 128 bytes; 16-byte pieces XOR-swizzled by the row
+                        const uint32_t base = GATHER == 1 ? sA + uint32_t(chunk >> 3) * MN_ATOM_BYTES : sA;
+                        const uint32_t piece = GATHER == 1 ? (chunk & 7) : chunk;
+                        auto put = [&](int kk, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+                            const uint32_t addr = base + uint32_t(kk) * 128u + ((piece ^ (uint32_t(kk) & 7u)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                                         : "memory");
+                        };
+#pragma unroll
+                        for (int u = 0; u < PASSES; ++u) {
+                            const int cr = cr_begin + tsub + PAIRS_PER_PASS * u;
+                            uint32_t left = __shfl_up_sync(0xffffffffu, v[u].w, 1);
+                            uint32_t right = __shfl_down_sync(0xffffffffu, v[u].x, 1);
+                            if (!has_left) left = 0;
+                            if (!has_right) right = 0;
+                            if (cr < cr_end) {
+                                const int kk = 3 * cr - k_lo;        // stage row of tap s = 0; -2 .. rows - 1
+                                const uint32_t a0 = __funnelshift_r(v[u].x, v[u].y, 16), a1 = __funnelshift_r(v[u].y, v[u].z, 16),
+                                               a2 = __funnelshift_r(v[u].z, v[u].w, 16);
+                                if (kk >= 0) put(kk, __funnelshift_r(left, v[u].x, 16), a0, a1, a2);
+                                if (kk + 1 >= 0 && kk + 1 < rows) put(kk + 1, v[u].x, v[u].y, v[u].z, v[u].w);
+                                if (kk + 2 < rows) put(kk + 2, a0, a1, a2, __funnelshift_r(v[u].w, right, 16));
+                            }
+                        }
+                        // k-rows past the end of the im2col matrix multiply zero-filled B rows: they must be zeros, not
+                        // whatever the stage held before
+                        for (int kk = rows + tsub; kk < (GATHER == 1 ? BK : 128); kk += PAIRS_PER_PASS) put(kk, 0, 0, 0, 0);
+                        fence_proxy_async();                         // generic-proxy writes -> visible to the tensor core
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_full + 8 * stage);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
     } else {
         // ============================== epilogue
         // Warps 2..5 and 6..9 own TMEM lane quadrants 2,3,0,1 (a warp reaches only the 32 lanes of quadrant warp % 4);
         // the first four take the lower half of a tile's column chunks, the other four the upper half.
-        const int epi_warps = (blockDim.x >> 5) - 3, epi_halves = epi_warps >> 2, epi_threads = epi_warps << 5;
+        const int epi_halves = epi_warps >> 2, epi_threads = epi_warps << 5;
         const bool two_bufs = epi_warps == 4;
         const int quad = warp & 3, half = (warp - 2) >> 2;       // half is 0 throughout with four epilogue warps
         const int etid = quad * 32 + lane;   // 0..127, also the row inside the tile this thread owns
@@ -851,7 +968,7 @@ static int make_operand_map(CUtensorMap* out, bool* mn_major, const char* name, 
     return SD_OK;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int GATHER = 0>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmArgs& g, int grid,
                           int epi_warps, cudaStream_t st) {
     // Called from the main thread and from autograd's worker threads at once: the per-device "already configured"
@@ -860,13 +977,13 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     int dev = 0;
     SD_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev].load(std::memory_order_relaxed)) {
-        SD_CUDA_TRY(cudaFuncSetAttribute(sparsedrop_gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GEMM_SMEM));
+        SD_CUDA_TRY(cudaFuncSetAttribute(sparsedrop_gemm_kernel<A_MN, B_MN, GATHER>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
         if (dev < 64) configured[dev].store(true, std::memory_order_relaxed);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(96 + 32 * epi_warps);
+    cfg.blockDim = dim3(96 + 32 * epi_warps + (GATHER ? 32 * GATHER_WARPS : 0));
     cfg.dynamicSmemBytes = GEMM_SMEM;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -874,7 +991,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, sparsedrop_gemm_kernel<A_MN, B_MN>, ta, tb, tc, g));
+    SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, sparsedrop_gemm_kernel<A_MN, B_MN, GATHER>, ta, tb, tc, g));
     return SD_OK;
 }
 
@@ -901,7 +1018,10 @@ static PlanView view_plan(const void* plan, int R, int C) {
 static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs,
                     void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
                     float scale, int dtype, void* workspace, int* status, void* stream, int max_ctas = 0,
-                    bool zero_dropped = true, bool sdd_t = false, int panels = 0) {
+                    bool zero_dropped = true, bool sdd_t = false, int panels = 0, const ConvGather* conv = nullptr,
+                    int gather = 0) {
+    // gather: 1 / 2 = A is the im2col matrix of `conv` (rows = pixels) / its transpose (rows = k), built inside the
+    // kernel from the NCHW input; A, a_rs, a_cs are then ignored.
     // panels: 1 = A is the conv's im2col matrix in panels of 128 pixels ([pixels/128][kg][128]); DSD with the plan's
     // rows = pixel blocks: side ROWS means A[M = pixels, K = kg], side COLS means A[M = kg, K = pixels].
     // 2 = C[M = kg, N = pixels] is stored that way (SDD for the transposed plan).  kg must be a multiple of 64.
@@ -919,7 +1039,10 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     bool a_mn = false, b_mn = false;
     int rc;
     int a_panel_kg = 0, c_panel_kg = 0;
-    if (panels == 1) {
+    if (gather) {
+        a_mn = gather == 1;
+        rc = SD_OK;
+    } else if (panels == 1) {
         const bool rows_are_pixels = plan_side == SD_PLAN_ROWS;
         const int pixels = rows_are_pixels ? M : K, kg = rows_are_pixels ? K : M;
         if (kg & 63) return fail(SD_ERR_LAYOUT, "panel layout needs a k extent that is a multiple of 64 (got %d)", kg);
@@ -941,8 +1064,10 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     }
     rc = make_operand_map(&tb, &b_mn, "B", B, b_rs, b_cs, N, K, dtype);
     if (rc) return rc;
+    if (gather) ta = tb;                       // the kernel never touches tmapA
 
     GemmArgs g{};
+    if (conv) g.conv = *conv;
     g.mode = mode;
     g.MM = M; g.NN = N; g.KK = K;
     g.C = C; g.c_rs = c_rs; g.c_cs = c_cs;
@@ -1064,6 +1189,13 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         const int v = e ? atoi(e) : 0;
         return (v == 4 || v == 8) ? v : 0;
     }();
+    if (gather) {
+        // four gather warps join the CTA, so the epilogue keeps four (the register budget of 352 threads)
+        if (gather == 1 && !b_mn) return launch_variant<true, false, 1>(ta, tb, tc, g, grid, 4, st);
+        if (gather == 1) return launch_variant<true, true, 1>(ta, tb, tc, g, grid, 4, st);
+        if (b_mn) return launch_variant<false, true, 2>(ta, tb, tc, g, grid, 4, st);
+        return launch_variant<false, false, 2>(ta, tb, tc, g, grid, 4, st);
+    }
     const int epi_warps = epi_warps_env ? epi_warps_env : ((!g.split && k_tiles >= 24) ? 4 : MAX_EPI_WARPS);
     if (!a_mn && !b_mn) return launch_variant<false, false>(ta, tb, tc, g, grid, epi_warps, st);
     if (!a_mn && b_mn) return launch_variant<false, true>(ta, tb, tc, g, grid, epi_warps, st);
@@ -1152,6 +1284,60 @@ int sd_gemm_sdd_kept_t_panels(const void* A, int64_t a_rs, int64_t a_cs, const v
                               void* workspace, int* status, void* stream) {
     return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, P, 128, 1, kg, pixels, K, plan, 0, scale, dtype,
                         workspace, status, stream, 0, /*zero_dropped=*/false, /*sdd_t=*/true, /*panels=*/2);
+}
+
+// ---- fused convolution: the im2col matrix is gathered inside the GEMM kernel and never written to memory
+static int make_conv_gather(sd::ConvGather* cv, const void* x, int N, int C, int H, int W, int R, int S, int pad_h,
+                            int pad_w, int stride_h, int stride_w, int dil_h, int dil_w) {
+    if (!x) return sd::fail(SD_ERR_INVALID_ARG, "x is null");
+    if (!sd_conv_fused_supported(N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w))
+        return sd::fail(SD_ERR_INVALID_ARG,
+                        "the fused convolution serves filters 3 wide with unit horizontal stride and dilation and one "
+                        "column of padding on rows of 8, 16, 32 or 64 pixels; use the sd_im2col_kept path otherwise");
+    if (reinterpret_cast<uintptr_t>(x) & 15) return sd::fail(SD_ERR_LAYOUT, "x must be 16-byte aligned");
+    const int P = (H + 2 * pad_h - dil_h * (R - 1) - 1) / stride_h + 1;
+    cv->x = static_cast<const unsigned short*>(x);
+    cv->C = C; cv->H = H; cv->W = W; cv->R = R; cv->P = P;
+    cv->stride_h = stride_h; cv->dil_h = dil_h; cv->pad_h = pad_h;
+    cv->PQ = P * W; cv->HW = H * W;
+    cv->k_real = C * R * 3;
+    cv->pixels = N * P * W;
+    return SD_OK;
+}
+
+int sd_conv_fused_supported(int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h, int stride_w,
+                            int dil_h, int dil_w) {
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || R <= 0 || S != 3) return 0;
+    if (stride_w != 1 || dil_w != 1 || pad_w != 1 || stride_h <= 0 || dil_h <= 0 || pad_h < 0) return 0;
+    if (W != 8 && W != 16 && W != 32 && W != 64) return 0;
+    const long long P = ((long long)H + 2 * pad_h - (long long)dil_h * (R - 1) - 1) / stride_h + 1;
+    if (P <= 0) return 0;
+    if ((long long)N * P * W > (1ll << 30) || (long long)C * R * 3 > (1ll << 30)) return 0;
+    if ((long long)N * C * H * W > (1ll << 31) - 1) return 0;
+    return 1;
+}
+
+int sd_conv_dsd_fwd(const void* x, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
+                    int stride_w, int dil_h, int dil_w, const void* W2d, int64_t w_rs, int64_t w_cs, void* Y2d,
+                    int64_t y_rs, int64_t y_cs, int Ko, const void* plan, float scale, int dtype, void* workspace,
+                    int* status, void* stream) {
+    sd::ConvGather cv;
+    int rc = make_conv_gather(&cv, x, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w);
+    if (rc) return rc;
+    return sd::run_gemm(sd::MODE_DSD, nullptr, 0, 0, W2d, w_rs, w_cs, Y2d, y_rs, y_cs, cv.pixels, Ko, cv.k_real, plan,
+                        SD_PLAN_ROWS, scale, dtype, workspace, status, stream, 0, true, false, 0, &cv, 1);
+}
+
+int sd_conv_dsd_dw(const void* x, int N, int C, int H, int W, int R, int S, int pad_h, int pad_w, int stride_h,
+                   int stride_w, int dil_h, int dil_w, const void* dY2d, int64_t dy_rs, int64_t dy_cs, void* dW2d,
+                   int64_t dw_rs, int64_t dw_cs, int Ko, const void* plan, float scale, int dtype, void* workspace,
+                   int* status, void* stream) {
+    sd::ConvGather cv;
+    int rc = make_conv_gather(&cv, x, N, C, H, W, R, S, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w);
+    if (rc) return rc;
+    // dW2d^T [k, Ko] = (keep o col)^T [k, pixels] . dY2d^T [Ko, pixels]^T: B = dY2d^T, C = dW2d^T (strides swapped)
+    return sd::run_gemm(sd::MODE_DSD, nullptr, 0, 0, dY2d, dy_cs, dy_rs, dW2d, dw_cs, dw_rs, cv.k_real, Ko, cv.pixels,
+                        plan, SD_PLAN_COLS, scale, dtype, workspace, status, stream, 0, true, false, 0, &cv, 2);
 }
 
 size_t sd_workspace_bytes(void) {

@@ -24,6 +24,7 @@ EXPORTS = (
     "sd_plan_from_mask", "sd_workspace_bytes", "sd_workspace_init", "sd_gemm", "sd_gemm_dsd", "sd_gemm_sdd", "sd_gemm_sdd_kept", "sd_gemm_sdd_kept_t",
     "sd_gemm_dsd_static_scratch", "sd_im2col_kept", "sd_col2im_kept", "sd_im2col_kept_panels", "sd_col2im_kept_panels",
     "sd_gemm_dsd_panels", "sd_gemm_sdd_kept_t_panels", "sd_selftest_bounded_wait", "sd_check_status",
+    "sd_conv_fused_supported", "sd_conv_dsd_fwd", "sd_conv_dsd_dw",
 )
 
 
@@ -82,6 +83,12 @@ def lib() -> C.CDLL:
     L.sd_gemm_dsd_panels.argtypes = [vp, i32, i32] + mat * 2 + [i32, vp, i32, f32, i32, vp, vp, vp]
     L.sd_gemm_sdd_kept_t_panels.restype = i32
     L.sd_gemm_sdd_kept_t_panels.argtypes = mat * 2 + [vp, i32, i32, i32, vp, f32, i32, vp, vp, vp]
+    L.sd_conv_fused_supported.restype = i32
+    L.sd_conv_fused_supported.argtypes = [i32] * 12
+    L.sd_conv_dsd_fwd.restype = i32
+    L.sd_conv_dsd_fwd.argtypes = [vp] + [i32] * 12 + mat * 2 + [i32, vp, f32, i32, vp, vp, vp]
+    L.sd_conv_dsd_dw.restype = i32
+    L.sd_conv_dsd_dw.argtypes = [vp] + [i32] * 12 + mat * 2 + [i32, vp, f32, i32, vp, vp, vp]
     L.sd_selftest_bounded_wait.restype = i32
     L.sd_selftest_bounded_wait.argtypes = [vp, u64, vp]
     L.sd_workspace_bytes.restype = C.c_size_t

@@ -377,6 +377,65 @@ def sdd_kept_t_panels(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: 
     return out
 
 
+def conv_fused_supported(x_shape, kernel_size, padding, stride, dilation) -> bool:
+    """True if the geometry is served by the fused im2col + DSD kernels (``conv_dsd_fwd`` / ``conv_dsd_dw``)."""
+    N, C, H, W = x_shape
+    R, S = kernel_size
+    return bool(_lib.lib().sd_conv_fused_supported(N, C, H, W, R, S, padding[0], padding[1], stride[0], stride[1],
+                                                   dilation[0], dilation[1]))
+
+
+def _conv_geom(x: torch.Tensor, kernel_size, padding, stride, dilation):
+    if x.dim() != 4 or not x.is_contiguous():
+        raise RuntimeError("x must be a contiguous NCHW tensor")
+    N, C, H, W = x.shape
+    R, S = kernel_size
+    return (N, C, H, W, R, S, padding[0], padding[1], stride[0], stride[1], dilation[0], dilation[1])
+
+
+def conv_dsd_fwd(x: torch.Tensor, w2d: torch.Tensor, plan: BlockPlan, kernel_size, padding, stride, dilation,
+                 scale: float, ws="auto") -> torch.Tensor:
+    """``y2d[N*P*Q, Ko] = scale * (keep o im2col(x)) @ w2d.T`` with the im2col matrix gathered inside the kernel."""
+    dt = _lib.dtype_code(x.dtype)
+    _check_operand(w2d, "w2d")
+    geom = _conv_geom(x, kernel_size, padding, stride, dilation)
+    N, C, H, W, R, S = geom[:6]
+    P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) // stride[0] + 1
+    M, K, Ko = N * P * W, C * R * S, w2d.size(0)
+    if (plan.R, plan.C) != (ceil(M / TILE), ceil(K / TILE)):
+        raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the {M} x {K} im2col matrix")
+    if w2d.size(1) < K or w2d.dtype != x.dtype or w2d.device != x.device:
+        raise RuntimeError("w2d must be [Ko, >= C*R*S] of x's dtype and device")
+    y2d = torch.empty((M, Ko), dtype=x.dtype, device=x.device)
+    with _on_device(x.device):
+        _lib.check(_lib.lib().sd_conv_dsd_fwd(x.data_ptr(), *geom, *_mat(w2d), *_mat(y2d), Ko, plan.buf.data_ptr(),
+                                              float(scale), dt, _ws_ptr(ws, x.device), _status_ptr(x.device),
+                                              _lib.stream_ptr(x.device)))
+    return y2d
+
+
+def conv_dsd_dw(x: torch.Tensor, dy2d: torch.Tensor, plan: BlockPlan, kernel_size, padding, stride, dilation,
+                scale: float, out: torch.Tensor, ws="auto") -> torch.Tensor:
+    """``out[Ko, :C*R*S] = scale * dy2d.T @ (keep o im2col(x))``; ``out`` is [Ko, >= C*R*S] row-major."""
+    dt = _lib.dtype_code(x.dtype)
+    _check_operand(dy2d, "dy2d")
+    geom = _conv_geom(x, kernel_size, padding, stride, dilation)
+    N, C, H, W, R, S = geom[:6]
+    P = (H + 2 * padding[0] - dilation[0] * (R - 1) - 1) // stride[0] + 1
+    M, K, Ko = N * P * W, C * R * S, dy2d.size(1)
+    if (plan.R, plan.C) != (ceil(M / TILE), ceil(K / TILE)):
+        raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the {M} x {K} im2col matrix")
+    if dy2d.size(0) != M or dy2d.dtype != x.dtype or dy2d.device != x.device:
+        raise RuntimeError(f"dy2d must be [{M}, Ko] of x's dtype and device")
+    if out.dim() != 2 or out.size(0) != Ko or out.size(1) < K or out.stride(1) != 1 or out.dtype != x.dtype:
+        raise RuntimeError("out must be a row-major [Ko, >= C*R*S] matrix of x's dtype")
+    with _on_device(x.device):
+        _lib.check(_lib.lib().sd_conv_dsd_dw(x.data_ptr(), *geom, *_mat(dy2d), *_mat(out), Ko, plan.buf.data_ptr(),
+                                             float(scale), dt, _ws_ptr(ws, x.device), _status_ptr(x.device),
+                                             _lib.stream_ptr(x.device)))
+    return out
+
+
 @cache
 class GEMM:
     """Drop-in for the reference's ``GEMM`` wrapper (flash_dropout/cuda/binding_gemm.py:7-47)."""

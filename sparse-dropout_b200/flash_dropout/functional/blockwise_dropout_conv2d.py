@@ -25,7 +25,8 @@ import torch
 
 from flash_dropout import _lib
 from flash_dropout import random as sd_random
-from flash_dropout.cuda.binding_gemm import BlockPlan, _on_device, dsd_panels, sdd_kept_t_panels
+from flash_dropout.cuda.binding_gemm import (BlockPlan, _on_device, conv_dsd_dw, conv_dsd_fwd, conv_fused_supported,
+                                             dsd_panels, sdd_kept_t_panels)
 
 from .im2col_conv2d import conv_output_size
 
@@ -97,7 +98,7 @@ def col2im_kept(dcolT: torch.Tensor, x_shape, kernel_size, padding, stride, dila
 
 class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, kernel, block_size, p, padding, stride, dilation, plan, recompute_cols):
+    def forward(ctx, input, kernel, block_size, p, padding, stride, dilation, plan, recompute_cols, fused):
         assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
         if not (input.is_cuda and kernel.is_cuda):
             raise RuntimeError("input and kernel must be CUDA")
@@ -117,12 +118,19 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
         if Kg != K or Kog != Ko:                         # 16-byte rows for TMA; zero padding changes nothing
             w2d = torch.nn.functional.pad(w2d, (0, Kg - K, 0, Kog - Ko))
         w2d = w2d.contiguous()
-        colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg, panels=True)
-        y2d = dsd_panels(colT, M, w2d, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))   # (M, Kog)
-        if recompute_cols:
+        input = input.contiguous()
+        ctx.fused = fused and conv_fused_supported(input.shape, (R, S), padding, stride, dilation)
+        if ctx.fused:
+            # im2col + DSD in one kernel: the matrix is gathered stage by stage from the input, never stored
+            y2d = conv_dsd_fwd(input, w2d, plan, (R, S), padding, stride, dilation, 1.0 / (1.0 - p))   # (M, Kog)
             ctx.save_for_backward(input, w2d)
         else:
-            ctx.save_for_backward(input, w2d, colT)
+            colT = im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg, panels=True)
+            y2d = dsd_panels(colT, M, w2d, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))   # (M, Kog)
+            if recompute_cols:
+                ctx.save_for_backward(input, w2d)
+            else:
+                ctx.save_for_backward(input, w2d, colT)
         ctx.plan, ctx.p = plan, p
         ctx.geom = (padding, stride, dilation, (R, S), Ko, K)
         return y2d.view(N, P, Q, Kog)[..., :Ko].permute(0, 3, 1, 2)
@@ -140,7 +148,11 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
             dy2d = torch.nn.functional.pad(dy2d, (0, Kog - Ko))
         dy2d = dy2d.contiguous()
         grad_input = grad_kernel = None
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and ctx.fused:
+            dw2d = torch.empty((Kog, Kg), dtype=input.dtype, device=input.device)
+            conv_dsd_dw(input, dy2d, plan, (R, S), padding, stride, dilation, scale, out=dw2d)
+            grad_kernel = dw2d[:Ko, :K].reshape(Ko, C, R, S)
+        elif ctx.needs_input_grad[1]:
             colT = saved_cols[0] if saved_cols else im2col_kept(input, (R, S), padding, stride, dilation, plan, Kg,
                                                                  panels=True)
             dw2d = torch.empty((Kog, Kg), dtype=input.dtype, device=input.device)
@@ -152,16 +164,20 @@ class BlockwiseDropoutConv2dCUDA(torch.autograd.Function):
             # dcolT = w2d.T @ dy2d.T on the kept blocks, written into panels; col2im reads kept blocks only
             sdd_kept_t_panels(w2d.T, dy2d, plan, scale, out=dcolT)
             grad_input = col2im_kept(dcolT, input.shape, (R, S), padding, stride, dilation, plan)
-        return grad_input, grad_kernel, None, None, None, None, None, None, None
+        return grad_input, grad_kernel, None, None, None, None, None, None, None, None
 
 
 def blockwise_dropout_conv2d(input: torch.Tensor, kernel: torch.Tensor, block_size: int, p: float,
                              padding=(0, 0), stride=(1, 1), dilation=(1, 1), plan=None,
-                             recompute_cols: bool = False) -> torch.Tensor:
-    """Conv2d (no bias) whose im2col matrix is block-dropped with probability ``p``; NCHW in, NCHW-shaped out."""
+                             recompute_cols: bool = False, fused: bool = True) -> torch.Tensor:
+    """Conv2d (no bias) whose im2col matrix is block-dropped with probability ``p``; NCHW in, NCHW-shaped out.
+
+    ``fused`` (default): geometries the fused kernels serve (3-wide filters, unit horizontal stride / dilation, one
+    column of padding, rows of 8..64 pixels) never materialise the im2col matrix; others, and ``fused=False``, go
+    through the kept-block im2col stage."""
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
         input, kernel = input.to(dt), kernel.to(dt)
     with torch.autocast("cuda", enabled=False):
         return BlockwiseDropoutConv2dCUDA.apply(input, kernel, block_size, p, tuple(padding), tuple(stride),
-                                                tuple(dilation), plan, recompute_cols)
+                                                tuple(dilation), plan, recompute_cols, fused)

@@ -60,9 +60,58 @@ def test_im2col_and_col2im_against_unfold_fold(built_lib, geom, dtype, panels):
     assert torch.equal(dense[:K, :M].float().cpu(), want)
 
 
-@pytest.mark.parametrize("recompute", [False, True])
-@pytest.mark.parametrize("geom,Ko", [(GEOMS[0], 128), (GEOMS[1], 24), (GEOMS[2], 40), (GEOMS[4], 10)])
-def test_conv_op_against_oracle(built_lib, geom, Ko, recompute):
+FUSED_GEOMS = [  # geometries the fused im2col + DSD kernels serve (3-wide filter, unit horizontal stride, pad_w 1)
+    (2, 16, 16, 16, 3, 3, (1, 1), (1, 1), (1, 1)),       # K = 144: a ragged second K block
+    (1, 64, 32, 32, 3, 3, (1, 1), (1, 1), (1, 1)),       # the benchmark layer's shape for one image
+    (3, 6, 12, 8, 2, 3, (0, 1), (1, 1), (2, 1)),         # 8-pixel rows, M = 240 (ragged last pixel block), R = 2, dilated rows
+    (1, 20, 6, 64, 3, 3, (1, 1), (2, 1), (1, 1)),        # 64-pixel rows, vertical stride 2, K = 180
+    (5, 24, 8, 8, 3, 3, (1, 1), (1, 1), (1, 1)),         # 8x8 images: a pixel block spans two images; K = 216
+    (2, 43, 16, 32, 1, 3, (0, 1), (1, 1), (1, 1)),       # R = 1, K = 129: one k-row in the second block
+]
+
+
+@pytest.mark.parametrize("geom", FUSED_GEOMS)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Ko", [128, 40, 264])
+def test_fused_conv_products_against_oracle(built_lib, geom, dtype, Ko):
+    """sd_conv_dsd_fwd / sd_conv_dsd_dw (im2col gathered inside the GEMM kernel) against the masked-dense oracle on the
+    unfold matrix, for p = 0 and p = 0.5, with and without the workspace."""
+    from flash_dropout.cuda import binding_gemm as bg
+    N, C, H, W, R, S, pad, stride, dil = geom
+    assert bg.conv_fused_supported((N, C, H, W), (R, S), pad, stride, dil)
+    g = torch.Generator().manual_seed(N * 100 + C + Ko)
+    x = torch.randn(N, C, H, W, generator=g).to(dtype)
+    cols = md.im2col_matrix(x, R, S, pad, stride, dil)                               # (M, K) fp32, unfold order
+    M, K = cols.shape
+    Kp, Kop = (K + 7) & ~7, (Ko + 7) & ~7
+    w = (torch.randn(Ko, K, generator=g) * K ** -0.5).to(dtype)
+    dy = (torch.randn(M, Ko, generator=g) * 0.5).to(dtype)
+    w2d = torch.zeros(Kop, Kp, dtype=dtype)
+    w2d[:Ko, :K] = w
+    dy2d = torch.zeros(M, Kop, dtype=dtype)
+    dy2d[:, :Ko] = dy
+    tol = dict(rtol=1e-2, atol=1e-2) if dtype == torch.float16 else dict(rtol=2e-2, atol=4e-2)
+    xd, w2dd, dy2dd = x.to(DEV), w2d.to(DEV), dy2d.to(DEV)
+    for p, ws in ((0.5, "auto"), (0.0, "auto"), (0.5, None)):
+        mask = pm.block_mask(M, K, 128, p, seed=17, offset=Ko)
+        plan = bg.BlockPlan.from_mask(torch.from_numpy(mask).to(DEV), M, K, 128)
+        s = 1 / (1 - p)
+        y_ref, _, dw_ref = md.forward_backward(cols, mask, 128, p, w, dy)
+        y2d = bg.conv_dsd_fwd(xd, w2dd, plan, (R, S), pad, stride, dil, s, ws=ws)
+        torch.testing.assert_close(y2d[:, :Ko].float().cpu(), y_ref, **tol)
+        assert (y2d[:, Ko:] == 0).all()
+        dw2d = torch.full((Kop, Kp), float("nan"), dtype=dtype, device=DEV)
+        bg.conv_dsd_dw(xd, dy2dd, plan, (R, S), pad, stride, dil, s, out=dw2d, ws=ws)
+        scale = max(1.0, float(M) ** 0.5 / 8)                                        # |dW| grows with sqrt(M)
+        torch.testing.assert_close(dw2d[:Ko, :K].float().cpu() / scale, dw_ref / scale, **tol)
+    assert not bg.conv_fused_supported((N, C, H, W), (R, 2), pad, stride, dil)
+    assert not bg.conv_fused_supported((N, C, H, W), (R, S), pad, (1, 2), dil)
+
+
+@pytest.mark.parametrize("recompute,fused", [(False, True), (False, False), (True, False)])
+@pytest.mark.parametrize("geom,Ko", [(GEOMS[0], 128), (GEOMS[1], 24), (GEOMS[2], 40), (GEOMS[4], 10), (GEOMS[5], 24),
+                                     (GEOMS[6], 136)])
+def test_conv_op_against_oracle(built_lib, geom, Ko, recompute, fused):
     import flash_dropout.functional as F
     from flash_dropout import random as sd_random
     N, C, H, W, R, S, pad, stride, dil = geom
@@ -73,7 +122,7 @@ def test_conv_op_against_oracle(built_lib, geom, Ko, recompute):
     xa, ka = x.to(DEV).requires_grad_(), k.to(DEV).requires_grad_()
     sd_random.manual_seed(31, subsequence=0)
     y = F.cuda_blockwise_dropout_conv2d(xa, ka, 128, p, padding=pad, stride=stride, dilation=dil,
-                                        recompute_cols=recompute)
+                                        recompute_cols=recompute, fused=fused)
     P, Q = y.shape[2:]
     dy = (torch.randn(N, Ko, P, Q, generator=g) * 0.25).half()
     y.backward(dy.to(DEV))
