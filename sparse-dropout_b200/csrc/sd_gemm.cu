@@ -67,9 +67,15 @@ constexpr int TILE_SMEM = STAGES * STAGE_BYTES;          // 192 KiB
 // warps only take issue slots from the producer and MMA warps.
 constexpr int MAX_EPI_WARPS = 8;
 constexpr int STAGING_BYTES = 8 * 4096;                  // TMA-store staging
-constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/ + STAGING_BYTES;
+// Tile table: a CTA that runs several whole-tile passes resolves all of them once, in its prologue, into shared
+// memory (row block, column tile, keep bits of the row block's K tiles), so that no role pays the chain of
+// dependent index loads (order -> list bounds -> list entries) again for every tile.
+constexpr int TAB_MAX = 96;
+constexpr int TAB_BYTES = TAB_MAX * 16;
+constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/ + STAGING_BYTES + TAB_BYTES;
 static_assert(GEMM_SMEM <= 227 * 1024, "over the shared memory of one CTA");
 constexpr int GEMM_MAX_THREADS = 96 + MAX_EPI_WARPS * 32;   // producer A, MMA, epilogue warps, producer B
+constexpr int GATHER_THREADS = 96 + 4 * 32 + 8 * 32;         // with gather warps: four epilogue warps, eight gather warps
 constexpr int TMEM_COLS = 512;
 
 // Workspace of the split schedule: flags first, then one fp32 partial tile per CTA.
@@ -92,7 +98,31 @@ struct ConvGather {
     int PQ, HW;
     int k_real;                  // C * R * 3: columns of the im2col matrix that exist
     int pixels;                  // N * P * Q: rows that exist
+    int log2_w;                  // W is a power of two
+    uint32_t mul_pq, shr_pq;     // fast_div constants for P * Q and R
+    uint32_t mul_r, shr_r;
+    int pass_dc[3], pass_dr[3];  // (channel, filter row) step between a gather thread's passes, per GATHER mode:
+                                 // the pair index advances by 4 (mode 1) or 8 (mode 2) = pass_dc * R + pass_dr
 };
+
+// n / d for 0 <= n < 2^31 by one multiply-high and a shift; (mul, shr) come from fast_div_constants(d).
+__host__ __device__ __forceinline__ int fast_div(int n, uint32_t mul, uint32_t shr) {
+#if defined(__CUDA_ARCH__)
+    return mul ? int(__umulhi(uint32_t(n), mul) >> shr) : n;
+#else
+    return mul ? int((uint64_t(uint32_t(n)) * mul >> 32) >> shr) : n;
+#endif
+}
+// Round-up multiplier: with L = ceil(log2 d), mul = ceil(2^(31+L) / d) fits 32 bits and
+// floor(n * mul / 2^(31+L)) == floor(n / d) for every n below 2^31.  d == 1 is flagged by mul == 0.
+inline void fast_div_constants(uint32_t d, uint32_t* mul, uint32_t* shr) {
+    if (d <= 1) { *mul = 0; *shr = 0; return; }
+    uint32_t L = 0;
+    while ((1ull << L) < d) ++L;
+    const uint32_t pw = 31 + L;
+    *mul = uint32_t(((1ull << pw) + d - 1) / d);
+    *shr = pw - 32;
+}
 
 struct GemmArgs {
     int mode;
@@ -121,6 +151,7 @@ struct GemmArgs {
     int tma_store;                   // result written by TMA from a swizzled staging buffer: 1 row-major, 2 column-major
     float* ws_slots;
     int* ws_flags;
+    int use_table;                   // whole-tile schedule whose tiles can be described by the shared-memory table
     ConvGather conv;                 // used by the GATHER variants of the kernel only
 };
 
@@ -130,6 +161,42 @@ struct Seg {
     const int* klist;            // kept K-tile indices of the whole tile, or null for 0..nk-1
     int nk, i0, i1;
     int owner, parts, part;      // split schedule: first CTA of the tile's group, CTAs in the group, this CTA's place
+    uint32_t bits;               // use_bits: bit kb set = K tile kb is kept (replaces klist; at most 32 K tiles)
+    bool use_bits;
+};
+
+// The K tiles of one segment, in order.  List entries are fetched one step ahead of their use, so the load of the
+// next entry is in flight while the current K tile is being processed.
+struct KIter {
+    const int* klist;
+    int i, i1, pre;
+    uint32_t bits;
+    bool use_bits;
+    __device__ __forceinline__ void init(const Seg& w) {
+        use_bits = w.use_bits;
+        bits = w.bits;
+        klist = w.klist;
+        i = w.i0;
+        i1 = w.i1;
+        pre = (!use_bits && klist && i < i1) ? __ldg(klist + i) : 0;
+    }
+    __device__ __forceinline__ bool next(int& kb) {
+        if (use_bits) {
+            if (!bits) return false;
+            kb = __ffs(bits) - 1;
+            bits &= bits - 1;
+            return true;
+        }
+        if (i >= i1) return false;
+        if (klist) {
+            kb = pre;
+            if (i + 1 < i1) pre = __ldg(klist + i + 1);
+        } else {
+            kb = i;
+        }
+        ++i;
+        return true;
+    }
 };
 
 // Walks this CTA's share of the launch.  Every role of the CTA runs its own copy and sees the same
@@ -146,6 +213,8 @@ struct WorkIter {
     int whole_entries, n_entries;   // whole tiles: list entries that are whole tiles, and all entries (see init)
     int sp_rb, sp_nt, sp_owner, sp_parts, sp_part;   // split: this CTA's one segment; sp_parts == 0: none
     bool split, snake;
+    const int4* tab;             // shared-memory tile table (see TAB_MAX), or null: resolve every tile from the plan
+    int passes;                  // whole tiles: passes over the entry list this grid makes
 
     __device__ __forceinline__ int count(const GemmArgs& g, int r) const {
         return __ldg(g.list_ptr + r + 1) - __ldg(g.list_ptr + r);
@@ -168,8 +237,9 @@ struct WorkIter {
                                       : unsigned((unsigned long long)spare * w / total);
         return tile + int(extra);
     }
-    __device__ void init(const GemmArgs& g, int cta, int n_ctas) {
+    __device__ void init(const GemmArgs& g, int cta, int n_ctas, const int4* table) {
         split = g.split != 0;
+        tab = nullptr;
         nk_uniform = (g.KK + 127) >> 7;
         n_tiles = g.mode == MODE_SDD ? __ldg(g.n_items) : g.n_row_blocks * g.n_col_tiles;
         t = cta;
@@ -194,6 +264,8 @@ struct WorkIter {
                 whole_entries = waves * n_ctas;
         }
         n_entries = whole_entries + 2 * (n_tiles - whole_entries);
+        passes = (n_entries + n_ctas - 1) / n_ctas;
+        if (g.use_table && !split && passes >= 2 && passes <= TAB_MAX) tab = table;
         if (!split || n_tiles == 0 || n_tiles > n_ctas) return;
         const int row_weight = 2 * g.n_col_tiles - (ragged ? 1 : 0);
         const unsigned total = work_before(g, n_tiles, row_weight);
@@ -217,6 +289,8 @@ struct WorkIter {
         sp_parts = sp_part < parts ? parts : 0;
     }
     __device__ __forceinline__ void fill(const GemmArgs& g, Seg& s, int row_block, int n_tile) const {
+        s.bits = 0;
+        s.use_bits = false;
         if (g.mode == MODE_SDD && g.sdd_single) {
             const int pr = __ldg(g.items + 2 * row_block), pc = __ldg(g.items + 2 * row_block + 1);
             s.a_row = (g.sdd_single == 2 ? pc : pr) * 128;
@@ -246,38 +320,74 @@ struct WorkIter {
             }
         }
     }
+    // Whole-tile schedule: the segment of pass `ps` for this CTA, resolved from the plan; false if the pass holds nothing
+    // for this CTA.  Pass j hands out entries [j*stride, (j+1)*stride) of the heaviest-first list; with unequal row
+    // blocks, forwards on even passes and backwards on odd ones, so the CTA that got the heaviest tile of one pass gets
+    // the lightest of the next.
+    __device__ bool resolve(const GemmArgs& g, int ps, Seg& s) const {
+        const int entry = ps * stride + ((snake && (ps & 1)) ? stride - 1 - t : t);
+        if (entry >= n_entries) return false;
+        const int tile = entry < whole_entries ? entry : whole_entries + ((entry - whole_entries) >> 1);
+        const int half = entry < whole_entries ? -1 : ((entry - whole_entries) & 1);
+        if (g.mode == MODE_SDD) {
+            fill(g, s, tile, 0);
+        } else {
+            // list order: row blocks heaviest first, and when the last column tile is only 128 wide (half the
+            // work), all full-width tiles before all narrow ones, so that no CTA collects only full-width tiles
+            int rbi, nt;
+            if (tile < n_full) { rbi = tile / full_per_row; nt = tile - rbi * full_per_row; }
+            else { rbi = tile - n_full; nt = g.n_col_tiles - 1; }
+            fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, nt);
+        }
+        if (s.nk == 0) return false;          // empty row blocks are zero-filled by the epilogue warps
+        if (half >= 0) {                      // one 128-wide half of a tile of the last wave
+            if (s.b_row1 < 0) {
+                if (half == 1) return false;  // the tile is only 128 wide: there is no second half
+            } else {
+                if (half == 1) s.b_row0 = s.b_row1;
+                s.b_row1 = -1;
+            }
+        }
+        s.i0 = 0;
+        s.i1 = s.nk;
+        s.owner = 0; s.parts = 1; s.part = 0;
+        return true;
+    }
+    // Prologue of a CTA that uses the tile table: every thread resolves some of the passes.
+    __device__ void fill_table(const GemmArgs& g, int4* table, int tid, int n_threads) const {
+        for (int ps = tid; ps < passes; ps += n_threads) {
+            Seg s;
+            int4 e = make_int4(-1, 0, 0, 0);
+            if (resolve(g, ps, s)) {
+                uint32_t bits = 0;
+                if (g.mode == MODE_DSD)
+                    for (int j = 0; j < s.nk; ++j) bits |= 1u << __ldg(s.klist + j);
+                e = make_int4(s.a_row, s.b_row0, s.b_row1, int(bits));
+            }
+            table[ps] = e;
+        }
+    }
     __device__ bool next(const GemmArgs& g, Seg& s) {
         if (!split) {
-            // pass j hands out tiles [j*stride, (j+1)*stride) of the heaviest-first list; with unequal row blocks,
-            // forwards on even passes and backwards on odd ones, so the CTA that got the heaviest tile of one pass
-            // gets the lightest of the next
-            for (; pass * stride < n_entries; ++pass) {
-                const int entry = pass * stride + ((snake && (pass & 1)) ? stride - 1 - t : t);
-                if (entry >= n_entries) continue;
-                const int tile = entry < whole_entries ? entry : whole_entries + ((entry - whole_entries) >> 1);
-                const int half = entry < whole_entries ? -1 : ((entry - whole_entries) & 1);
-                if (g.mode == MODE_SDD) {
-                    fill(g, s, tile, 0);
-                } else {
-                    // list order: row blocks heaviest first, and when the last column tile is only 128 wide (half the
-                    // work), all full-width tiles before all narrow ones, so that no CTA collects only full-width tiles
-                    int rbi, nt;
-                    if (tile < n_full) { rbi = tile / full_per_row; nt = tile - rbi * full_per_row; }
-                    else { rbi = tile - n_full; nt = g.n_col_tiles - 1; }
-                    fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, nt);
+            if (tab) {
+                for (; pass < passes; ++pass) {
+                    const int4 e = tab[pass];
+                    if (e.x < 0) continue;
+                    s.a_row = e.x; s.b_row0 = e.y; s.b_row1 = e.z;
+                    s.klist = nullptr;
+                    s.use_bits = g.mode == MODE_DSD;
+                    s.bits = uint32_t(e.w);
+                    s.nk = s.use_bits ? __popc(s.bits) : nk_uniform;
+                    s.i0 = 0;
+                    s.i1 = s.nk;
+                    s.owner = 0; s.parts = 1; s.part = 0;
+                    ++pass;
+                    return true;
                 }
-                if (s.nk == 0) continue;          // empty row blocks are zero-filled by the epilogue warps
-                if (half >= 0) {                  // one 128-wide half of a tile of the last wave
-                    if (s.b_row1 < 0) {
-                        if (half == 1) continue;  // the tile is only 128 wide: there is no second half
-                    } else {
-                        if (half == 1) s.b_row0 = s.b_row1;
-                        s.b_row1 = -1;
-                    }
-                }
-                s.i0 = 0;
-                s.i1 = s.nk;
-                s.owner = 0; s.parts = 1; s.part = 0;
+                return false;
+            }
+            for (; pass < passes; ++pass) {
+                if (!resolve(g, pass, s)) continue;
                 ++pass;
                 return true;
             }
@@ -496,10 +606,11 @@ __device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int eidx, 
 // The gather warps come after the B producer warp; warp 0 then has nothing to do.  They work as two groups of two
 // warps that take alternate stages, so two stages are being filled at any time and each thread keeps six 16-byte
 // loads in flight; a stage's `full` barrier counts the B producer plus the two warps of the group that fills it.
-constexpr int GATHER_WARPS = 4;
+constexpr int GATHER_WARPS = 8, GATHER_GROUPS = 4;
+static_assert(GATHER_GROUPS == STAGES, "each gather group owns one ring slot");
 
 template <bool A_MN, bool B_MN, int GATHER = 0>
-__global__ void __launch_bounds__(GEMM_MAX_THREADS, 1)
+__global__ void __launch_bounds__(GATHER ? GATHER_THREADS : GEMM_MAX_THREADS, 1)
 sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
                        const __grid_constant__ CUtensorMap tmapC, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -513,6 +624,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 14);
     uint8_t* staging = aligned + TILE_SMEM;   // 32 KiB of TMA-store staging, 1024-aligned
+    int4* tab = reinterpret_cast<int4*>(aligned + TILE_SMEM + STAGING_BYTES + 256);   // tile table, TAB_BYTES
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_warps = blockDim.x >> 5;
@@ -548,6 +660,14 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
     grid_dep_wait();
 
     const int n_ctas = gridDim.x, cta = blockIdx.x;
+    if (g.use_table) {
+        WorkIter it;
+        it.init(g, cta, n_ctas, tab);
+        if (it.tab) {                            // same decision in every thread and, below, in every role
+            it.fill_table(g, tab, threadIdx.x, blockDim.x);
+            __syncthreads();
+        }
+    }
 
     if (warp == 0 || warp == b_producer_warp) {
         // ============================== producers: warp 0 loads the A tiles, the last warp the B tiles.  Two threads
@@ -560,12 +680,14 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             uint32_t phase = 0;
             bool ok = true;
             WorkIter it;
-            it.init(g, cta, n_ctas);
+            it.init(g, cta, n_ctas, tab);
             Seg w;
             while (ok && it.next(g, w)) {
                 const uint32_t tx = loads_a ? A_BYTES : (w.b_row1 >= 0 ? B_BYTES : B_HALF_BYTES);
-                for (int i = w.i0; ok && i < w.i1; ++i) {
-                    const int kb = w.klist ? __ldg(w.klist + i) : i;
+                KIter kit;
+                kit.init(w);
+                int kb;
+                while (ok && kit.next(kb)) {
                     for (int h = 0; h < 2; ++h) {
                         const int k = kb * 128 + h * BK;
                         if (k >= g.KK) break;
@@ -617,7 +739,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
             WorkIter it;
-            it.init(g, cta, n_ctas);
+            it.init(g, cta, n_ctas, tab);
             Seg w;
             for (int seg = 0; ok && it.next(g, w); ++seg) {
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, g.status, ST_MMA_ACC)) break;
@@ -625,8 +747,10 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 tc_fence_after();
                 const uint32_t d = tmem_base + acc * BN;
                 const uint32_t idesc = w.b_row1 >= 0 ? g.idesc256 : g.idesc128;
-                for (int i = w.i0; ok && i < w.i1; ++i) {
-                    const int kb = w.klist ? __ldg(w.klist + i) : i;
+                KIter kit;
+                kit.init(w);
+                int kb;
+                while (ok && kit.next(kb)) {
                     for (int h = 0; h < 2; ++h) {
                         if (kb * 128 + h * BK >= g.KK) break;
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
@@ -655,89 +779,134 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         // s = 0, 1, 2 are that chunk shifted by -1, 0, +1 pixel, the pixel that comes in at either end is traded
         // with the neighbouring lane (which owns the neighbouring chunk of the same image row), and the item writes
         // up to three k-rows of the 128B-swizzled stage.  Rows and pixels that do not exist are written as zeros.
-        const int gw = warp - b_producer_warp - 1, group = gw >> 1;
-        const int t = ((gw & 1) << 5) | lane;                       // 0..63 inside the group
+        // Group j (two warps) fills ring slot j.  The loads of a group's next stage are issued before its current
+        // stage is stored, so their latency hides behind the stores and the wait for the slot; loads and stores are
+        // predicated, not branched around, and each helper below is expanded exactly once.
+        const int gw = warp - b_producer_warp - 1, group = gw >> 1;   // group == ring slot (GATHER_GROUPS == STAGES)
+        const int t = ((gw & 1) << 5) | lane;                         // 0..63 inside the group
         const ConvGather& cv = g.conv;
         // GATHER 1: 16 pixel chunks x 4 (c, r) pairs per pass;  GATHER 2: 8 pixel chunks x 8 pairs per pass
         const int chunk = GATHER == 1 ? (t & 15) : (t & 7), tsub = GATHER == 1 ? (t >> 4) : (t >> 3);
-        constexpr int PAIRS_PER_PASS = GATHER == 1 ? 4 : 8, PASSES = 6;
-        int stage = 0;
-        uint32_t phase = 0, sc = 0;
-        bool ok = true;
+        constexpr int PAIRS_PER_PASS = GATHER == 1 ? 4 : 8, PASSES = 6, STAGE_ROWS = GATHER == 1 ? BK : 128;
+        const uint32_t piece = GATHER == 1 ? (chunk & 7) : chunk;
+        const uint32_t slot_base = tiles + group * STAGE_BYTES + (GATHER == 1 ? uint32_t(chunk >> 3) * MN_ATOM_BYTES : 0u);
+        const uint32_t slot_full = bar_full + 8 * group, slot_empty = bar_empty + 8 * group;
+
+        struct StageJob {
+            uint32_t parity;       // parity to wait for on the slot's `empty` barrier
+            int k_lo, rows;        // first k-row of the im2col matrix in the stage, and how many exist
+            int cr0, cr_end;       // this thread's first (channel, filter row) pair, and the end of the stage's pairs
+            bool has_left, has_right;
+        };
+        // Walks the CTA's stages in the order every role sees them and stops at those of this group's slot.
         WorkIter it;
-        it.init(g, cta, n_ctas);
+        it.init(g, cta, n_ctas, tab);
         Seg w;
-        while (ok && it.next(g, w)) {
-            for (int i = w.i0; ok && i < w.i1; ++i) {
-                const int kb = w.klist ? __ldg(w.klist + i) : i;
-                for (int h = 0; h < 2; ++h) {
-                    const int k = kb * 128 + h * BK;
-                    if (k >= g.KK) break;
-                    const bool mine = (sc & 1) == uint32_t(group);
-                    ++sc;
-                    if (mine) {
-                        ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, g.status, ST_PRODUCER);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) break;
-                        const uint32_t sA = tiles + stage * STAGE_BYTES;
-                        // rows of the stage = k-rows [k_lo, k_hi) of the im2col matrix; this thread's 8 pixels start at m0
-                        const int k_lo = GATHER == 1 ? k : w.a_row;
-                        const int k_hi = min(k_lo + (GATHER == 1 ? BK : 128), cv.k_real);
-                        const int m0 = (GATHER == 1 ? w.a_row : k) + chunk * 8;
-                        const bool live = m0 < cv.pixels;
-                        const int n = live ? m0 / cv.PQ : 0, pq = m0 - n * cv.PQ, p = pq / cv.W, q0 = pq - p * cv.W;
-                        const unsigned short* xn = cv.x + (long long)n * cv.C * cv.HW + q0;
-                        const int hbase = p * cv.stride_h - cv.pad_h;
-                        const bool has_left = q0 > 0, has_right = q0 + 8 < cv.W;
-                        const int rows = k_hi - k_lo;
-                        const int cr_begin = k_lo / 3, cr_end = (k_hi + 2) / 3;
-                        uint4 v[PASSES];
-#pragma unroll
-                        for (int u = 0; u < PASSES; ++u) {
-                            const int cr = cr_begin + tsub + PAIRS_PER_PASS * u;
-                            v[u] = make_uint4(0, 0, 0, 0);
-                            if (cr < cr_end && live) {
-                                const int c = cr / cv.R, r = cr - c * cv.R;
-                                const int hh = hbase + r * cv.dil_h;
-                                if ((unsigned)hh < (unsigned)cv.H)
-                                    v[u] = __ldg(reinterpret_cast<const uint4*>(xn + (long long)c * cv.HW + hh * cv.W));
-                            }
-                        }
-                        // address of (k-row kk, this thread's chunk): MN-major stage = two 64-pixel atoms of 64 k-rows
-                        // of 128 bytes; K-major stage = 128 k-rows of 128 bytes; 16-byte pieces XOR-swizzled by the row
-                        const uint32_t base = GATHER == 1 ? sA + uint32_t(chunk >> 3) * MN_ATOM_BYTES : sA;
-                        const uint32_t piece = GATHER == 1 ? (chunk & 7) : chunk;
-                        auto put = [&](int kk, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-                            const uint32_t addr = base + uint32_t(kk) * 128u + ((piece ^ (uint32_t(kk) & 7u)) << 4);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
-                                         : "memory");
-                        };
-#pragma unroll
-                        for (int u = 0; u < PASSES; ++u) {
-                            const int cr = cr_begin + tsub + PAIRS_PER_PASS * u;
-                            uint32_t left = __shfl_up_sync(0xffffffffu, v[u].w, 1);
-                            uint32_t right = __shfl_down_sync(0xffffffffu, v[u].x, 1);
-                            if (!has_left) left = 0;
-                            if (!has_right) right = 0;
-                            if (cr < cr_end) {
-                                const int kk = 3 * cr - k_lo;        // stage row of tap s = 0; -2 .. rows - 1
-                                const uint32_t a0 = __funnelshift_r(v[u].x, v[u].y, 16), a1 = __funnelshift_r(v[u].y, v[u].z, 16),
-                                               a2 = __funnelshift_r(v[u].z, v[u].w, 16);
-                                if (kk >= 0) put(kk, __funnelshift_r(left, v[u].x, 16), a0, a1, a2);
-                                if (kk + 1 >= 0 && kk + 1 < rows) put(kk + 1, v[u].x, v[u].y, v[u].z, v[u].w);
-                                if (kk + 2 < rows) put(kk + 2, a0, a1, a2, __funnelshift_r(v[u].w, right, 16));
-                            }
-                        }
-                        // k-rows past the end of the im2col matrix multiply zero-filled B rows: they must be zeros, not
-                        // whatever the stage held before
-                        for (int kk = rows + tsub; kk < (GATHER == 1 ? BK : 128); kk += PAIRS_PER_PASS) put(kk, 0, 0, 0, 0);
-                        fence_proxy_async();                         // generic-proxy writes -> visible to the tensor core
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_full + 8 * stage);
-                    }
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        KIter kit;
+        int kb = 0, h = 2, ring = 0;
+        uint32_t phase = 0;
+        bool in_tile = false;
+        const unsigned short* xrow = cv.x;      // this thread's 8 pixels in channel 0, input row 0 (may lie outside the image)
+        int hbase = 0;
+        bool live = false, has_left = false, has_right = false;
+        auto decode_pixels = [&](int m0) {      // m0: first of this thread's 8 consecutive output pixels
+            live = m0 < cv.pixels;
+            const int mm = live ? m0 : 0;
+            const int n = fast_div(mm, cv.mul_pq, cv.shr_pq), pq = mm - n * cv.PQ;
+            const int pp = pq >> cv.log2_w, q0 = pq & (cv.W - 1);
+            xrow = cv.x + (long long)n * cv.C * cv.HW + q0;
+            hbase = pp * cv.stride_h - cv.pad_h;
+            has_left = q0 > 0;
+            has_right = q0 + 8 < cv.W;
+        };
+        auto next_job = [&](StageJob& job) -> bool {
+            for (;;) {
+                if (!in_tile) {
+                    if (!it.next(g, w)) return false;
+                    in_tile = true;
+                    kit.init(w);
+                    h = 2;
+                    if (GATHER == 1) decode_pixels(w.a_row + chunk * 8);         // pixels are the tile's rows
                 }
+                if (h == 2) {                                                    // next K tile of the segment
+                    if (!kit.next(kb)) { in_tile = false; continue; }
+                    h = 0;
+                }
+                const int k = kb * 128 + h * BK;
+                if (k >= g.KK) { h = 2; continue; }
+                ++h;
+                const bool mine = ring == group;
+                job.parity = phase ^ 1;
+                if (++ring == STAGES) { ring = 0; phase ^= 1; }
+                if (!mine) continue;
+                job.k_lo = GATHER == 1 ? k : w.a_row;
+                const int k_hi = min(job.k_lo + STAGE_ROWS, cv.k_real);
+                job.rows = k_hi - job.k_lo;
+                job.cr0 = job.k_lo / 3 + tsub;
+                job.cr_end = (k_hi + 2) / 3;
+                if (GATHER == 2) decode_pixels(k + chunk * 8);                   // pixels are the reduction index
+                job.has_left = has_left;
+                job.has_right = has_right;
+                return true;
             }
+        };
+        auto issue_loads = [&](const StageJob& job, uint4 (&v)[PASSES]) {
+            int c = fast_div(job.cr0, cv.mul_r, cv.shr_r), r = job.cr0 - c * cv.R;
+#pragma unroll
+            for (int u = 0; u < PASSES; ++u) {
+                const int hh = hbase + r * cv.dil_h;
+                const bool pred = live && job.cr0 + PAIRS_PER_PASS * u < job.cr_end && (unsigned)hh < (unsigned)cv.H;
+                v[u] = ldg_nc_v4_pred(xrow + (long long)c * cv.HW + hh * cv.W, pred);
+                c += cv.pass_dc[GATHER];                                               // (c, r) of the pair PAIRS_PER_PASS further on
+                r += cv.pass_dr[GATHER];
+                if (r >= cv.R) { r -= cv.R; ++c; }
+            }
+        };
+        // Stores the stage.  Returns false if the wait for the slot was abandoned.
+        auto store_stage = [&](const StageJob& job, const uint4 (&v)[PASSES]) -> bool {
+            bool ok = mbar_wait(slot_empty, job.parity, abort_flag, g.status, ST_PRODUCER);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return false;
+            // address of (k-row kk, this thread's chunk): MN-major stage = two 64-pixel atoms of 64 k-rows of 128
+            // bytes; K-major stage = 128 k-rows of 128 bytes; 16-byte pieces XOR-swizzled by the row
+            auto put = [&](int kk, bool pred, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+                st_shared_v4_pred(slot_base + uint32_t(kk) * 128u + ((piece ^ (uint32_t(kk) & 7u)) << 4), pred, a, b, c, d);
+            };
+#pragma unroll
+            for (int u = 0; u < PASSES; ++u) {
+                const int cr = job.cr0 + PAIRS_PER_PASS * u;
+                uint32_t left = __shfl_up_sync(0xffffffffu, v[u].w, 1);
+                uint32_t right = __shfl_down_sync(0xffffffffu, v[u].x, 1);
+                if (!job.has_left) left = 0;
+                if (!job.has_right) right = 0;
+                const bool on = cr < job.cr_end;
+                const int kk = 3 * cr - job.k_lo;                // stage row of tap s = 0; -2 .. rows - 1
+                const uint32_t a0 = __funnelshift_r(v[u].x, v[u].y, 16), a1 = __funnelshift_r(v[u].y, v[u].z, 16),
+                               a2 = __funnelshift_r(v[u].z, v[u].w, 16);
+                put(kk, on && kk >= 0, __funnelshift_r(left, v[u].x, 16), a0, a1, a2);
+                put(kk + 1, on && kk + 1 >= 0 && kk + 1 < job.rows, v[u].x, v[u].y, v[u].z, v[u].w);
+                put(kk + 2, on && kk + 2 < job.rows, a0, a1, a2, __funnelshift_r(v[u].w, right, 16));
+            }
+            // k-rows past the end of the im2col matrix multiply zero-filled B rows: they must be zeros, not
+            // whatever the stage held before
+            for (int kk = job.rows + tsub; kk < STAGE_ROWS; kk += PAIRS_PER_PASS) put(kk, true, 0, 0, 0, 0);
+            fence_proxy_async();                                 // generic-proxy writes -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(slot_full);
+            return true;
+        };
+        StageJob cur, nxt;
+        uint4 vc[PASSES], vn[PASSES];
+        bool have_cur = false;
+        for (;;) {
+            const bool have_nxt = next_job(nxt);
+            if (have_nxt) issue_loads(nxt, vn);
+            if (have_cur && !store_stage(cur, vc)) break;
+            if (!have_nxt) break;
+            cur = nxt;
+#pragma unroll
+            for (int u = 0; u < PASSES; ++u) vc[u] = vn[u];
+            have_cur = true;
         }
         __syncwarp();
     } else {
@@ -767,7 +936,7 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             }
         }
         WorkIter it;
-        it.init(g, cta, n_ctas);
+        it.init(g, cta, n_ctas, tab);
         int acc = 0;
         uint32_t acc_phase = 0;
         Seg w;
@@ -1143,6 +1312,8 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     } else if (tiles_upper < grid) {
         grid = int(tiles_upper);
     }
+    // Whole-tile launches describe their tiles once per CTA in shared memory when a tile's kept K tiles fit a 32-bit mask
+    g.use_table = !g.split && (mode != MODE_DSD || k_tiles <= 32);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Row-major result with 16-byte rows: written by TMA (clipped at the ragged edge); otherwise by the warps.
     CUtensorMap tc = ta;
@@ -1302,6 +1473,12 @@ static int make_conv_gather(sd::ConvGather* cv, const void* x, int N, int C, int
     cv->PQ = P * W; cv->HW = H * W;
     cv->k_real = C * R * 3;
     cv->pixels = N * P * W;
+    cv->log2_w = W == 8 ? 3 : W == 16 ? 4 : W == 32 ? 5 : 6;
+    sd::fast_div_constants(uint32_t(P * W), &cv->mul_pq, &cv->shr_pq);
+    sd::fast_div_constants(uint32_t(R), &cv->mul_r, &cv->shr_r);
+    cv->pass_dc[0] = cv->pass_dr[0] = 0;
+    cv->pass_dc[1] = 4 / R; cv->pass_dr[1] = 4 % R;
+    cv->pass_dc[2] = 8 / R; cv->pass_dr[2] = 8 % R;
     return SD_OK;
 }
 

@@ -111,6 +111,30 @@ __device__ __forceinline__ bool counter_wait(const int* counter, int target, vol
     }
 }
 
+// ---------------------------------------------------------------- predicated memory access
+// 16-byte read-only global load that is skipped (result zero) when `pred` is false: no branch around it.
+__device__ __forceinline__ uint4 ldg_nc_v4_pred(const void* ptr, bool pred) {
+    uint4 v;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+        "@p ld.global.nc.v4.b32 {%0, %1, %2, %3}, [%4];\n\t}\n"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "l"(ptr), "r"(int(pred)));
+    return v;
+}
+// 16-byte shared-memory store that is skipped when `pred` is false.
+__device__ __forceinline__ void st_shared_v4_pred(uint32_t addr, bool pred, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "@p st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n\t}\n"
+        :
+        : "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(int(pred))
+        : "memory");
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -34,8 +34,12 @@ class FlatGradDataParallel:
         dtype = self.params[0].dtype
         if any(p.dtype != dtype for p in self.params):
             raise ValueError("all trainable parameters must share one dtype (the master-weight dtype)")
-        self.flat_grad = torch.zeros(total, dtype=dtype, device=dev)
+        self.flat_grad = self._alloc_flat(total, dtype, dev)
         self._esize = self.flat_grad.element_size()
+        # NCCL averages inside the collective; other backends (gloo in the CPU tests) sum and the mean is taken after
+        self._avg_in_collective = (self.world > 1 and dev.type == "cuda" and
+                                   dist.get_backend(process_group) == "nccl")
+        self._reduce_op = dist.ReduceOp.AVG if self._avg_in_collective else dist.ReduceOp.SUM
         # parameters are laid out in REVERSE registration order: backward produces gradients roughly last
         # layer first, so bucket 0 (the front of the buffer) completes first
         off = 0
@@ -74,7 +78,27 @@ class FlatGradDataParallel:
         sd_random.set_subsequence(self.rank)     # every rank draws its own masks from the shared seed
 
     # ------------------------------------------------------------------
-    defer_allreduce = False     # set by GraphedTrainStep: no per-bucket collectives from the hooks
+    def _alloc_flat(self, total: int, dtype: torch.dtype, dev: torch.device) -> torch.Tensor:
+        """The flat gradient buffer.  With NCCL on several GPUs it comes from a memory pool that is registered with
+        the communicator as a user buffer, so that NCCL can reduce it in place (through NVLink SHARP where the fabric
+        offers it) instead of staging it through its own buffers, which also takes fewer of its thread blocks away
+        from the compute kernels.  Where this torch build or backend has no such pool, a plain tensor is used."""
+        self.registered_buffer = False
+        if self.world > 1 and dev.type == "cuda" and dist.get_backend(self.group) == "nccl":
+            try:
+                backend = (self.group or dist.group.WORLD)._get_backend(dev)
+                pool = torch.cuda.MemPool(backend.mem_allocator)
+                with torch.cuda.use_mem_pool(pool):
+                    flat = torch.zeros(total, dtype=dtype, device=dev)
+                backend.register_mem_pool(pool)
+                self._pool = pool                       # keeps the registration alive
+                self.registered_buffer = True
+                return flat
+            except Exception:                           # noqa: BLE001 - any failure means: not available here
+                pass
+        return torch.zeros(total, dtype=dtype, device=dev)
+
+    defer_allreduce = False     # hooks stay quiet: the caller reduces the whole flat buffer itself
 
     def _on_grad_ready(self, p: torch.Tensor) -> None:
         if self.defer_allreduce:
@@ -83,7 +107,7 @@ class FlatGradDataParallel:
         self._pending[b] -= 1
         if self._pending[b] == 0:
             lo, hi = self.buckets[b]
-            self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+            self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], op=self._reduce_op, group=self.group,
                                                  async_op=True))
 
     def zero_grad(self) -> None:
@@ -98,13 +122,14 @@ class FlatGradDataParallel:
         for b, left in enumerate(self._pending):       # parameters that received no gradient this step
             if left > 0:
                 lo, hi = self.buckets[b]
-                self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                self._handles.append(dist.all_reduce(self.flat_grad[lo:hi], op=self._reduce_op, group=self.group,
                                                      async_op=True))
                 self._pending[b] = 0
         for h in self._handles:
             h.wait()
         self._handles = []
-        self.flat_grad.div_(self.world)
+        if not self._avg_in_collective:
+            self.flat_grad.div_(self.world)
 
     def grads_are_views(self) -> bool:
         """True while autograd kept accumulating in place into the flat buffer."""
@@ -149,7 +174,8 @@ def train_step(model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torc
 
 
 class GraphedTrainStep:
-    """zero_grad + forward + backward captured once in a CUDA graph and replayed every step.
+    """A whole training step captured once in a CUDA graph and replayed every step: zero the gradients, forward,
+    backward with the bucketed gradient all-reduces overlapping it, and the optimizer update.
 
     The MLP and char-GPT training steps are made of dozens of small launches (a plan kernel and three GEMMs per
     DropoutMM, plus the model's other ops); eagerly they are bound by host launch overhead, which is what the
@@ -157,13 +183,16 @@ class GraphedTrainStep:
     removes that.  Masks stay fresh because the plan kernel takes its Philox offset from a counter in device
     memory that each launch increments (``flash_dropout.random.enable_device_counter``).
 
-    The gradient all-reduce (one flat buffer) and the optimizer step run eagerly after the replay: two or three
-    launches, and NCCL stays outside the capture.  ``inputs`` are static device tensors: copy each batch into
-    them before calling the step.
+    Inside the captured step each gradient bucket is all-reduced the moment backward has finished it, on the
+    collective's own stream, so the exchange overlaps the rest of backward; the optimizer joins after the last
+    bucket.  This needs an optimizer whose step can be captured (``capturable``: its step count lives on the device);
+    an optimizer without that option, or ``whole_step=False``, leaves the collectives and the update outside the
+    graph (one flat all-reduce and the update launched after every replay).  ``inputs`` are static device tensors:
+    copy each batch into them before calling the step.
     """
 
     def __init__(self, model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torch.optim.Optimizer, loss_fn,
-                 inputs: tuple, autocast_dtype: torch.dtype | None = None, warmup: int = 3):
+                 inputs: tuple, autocast_dtype: torch.dtype | None = None, warmup: int = 3, whole_step: bool = True):
         self.model, self.dp, self.optimizer = model, dp, optimizer
         self.inputs = inputs
         dev = dp.flat_grad.device
@@ -171,35 +200,57 @@ class GraphedTrainStep:
             raise RuntimeError("GraphedTrainStep needs CUDA")
         if sd_random.device_counter(dev) is None:
             sd_random.enable_device_counter(dev)
-        self._hooks_enabled = False
+        self.whole_step = whole_step and self._make_capturable(optimizer)
+        dp.defer_allreduce = not self.whole_step        # outside the graph: one flat all-reduce after the replay
 
         def fwd_bwd():
-            dp.flat_grad.zero_()
+            dp.zero_grad()
             if autocast_dtype is not None:
                 with torch.autocast("cuda", dtype=autocast_dtype):
                     loss = loss_fn(model, *inputs)
             else:
                 loss = loss_fn(model, *inputs)
             loss.backward()
+            if self.whole_step:
+                dp.finish()
+                optimizer.step()
             return loss.detach()
 
-        dp.defer_allreduce = True                      # bucket hooks stay quiet: one flat all-reduce after replay
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for _ in range(warmup):                    # allocations, autotuning and lazy init happen here
                 fwd_bwd()
-                self._finish()
+                if not self.whole_step:
+                    self._finish()
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
             self.loss = fwd_bwd()
 
+    @staticmethod
+    def _make_capturable(optimizer: torch.optim.Optimizer) -> bool:
+        """Switches the optimizer to device-side step counts if it has that option and has not stepped yet."""
+        if not all("capturable" in g for g in optimizer.param_groups):
+            return False
+        if len(optimizer.state) != 0 and not all(g["capturable"] for g in optimizer.param_groups):
+            return False                                # step counts already live on the host
+        for g in optimizer.param_groups:
+            g["capturable"] = True
+        return True
+
+    def describe(self) -> str:
+        if self.whole_step:
+            return ("CUDA graph replay of zero_grad + fwd + bwd + bucketed NCCL all-reduce (overlapping backward) + "
+                    "optimizer" if self.dp.world > 1 else "CUDA graph replay of zero_grad + fwd + bwd + optimizer")
+        return "CUDA graph replay of zero_grad + fwd + bwd, then flat all-reduce + optimizer"
+
     def _finish(self) -> None:
         if self.dp.world > 1:
-            dist.all_reduce(self.dp.flat_grad, op=dist.ReduceOp.SUM, group=self.dp.group)
-            self.dp.flat_grad.div_(self.dp.world)
+            dist.all_reduce(self.dp.flat_grad, op=self.dp._reduce_op, group=self.dp.group)
+            if not self.dp._avg_in_collective:
+                self.dp.flat_grad.div_(self.dp.world)
         self.optimizer.step()
 
     check_every = 64      # steps between reads of the kernels' failure-detection word (0 = never)
@@ -207,5 +258,6 @@ class GraphedTrainStep:
     def __call__(self) -> torch.Tensor:
         _maybe_check_status(self.dp.flat_grad.device, self.check_every)
         self.graph.replay()
-        self._finish()
+        if not self.whole_step:
+            self._finish()
         return self.loss
