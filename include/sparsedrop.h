@@ -269,6 +269,37 @@ int sd_gemm_sdd_kept_t_panels(const void* A, int64_t a_rs, int64_t a_cs,
                               float scale, int dtype, void* workspace, int* status, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Products with an elementwise neighbour of the layer fused into the epilogue.  The reference applies these as
+ * separate PyTorch ops around DropoutMM: ReLU after every layer of its MLP (eval/mlp/model.py:33-38), and autograd's
+ * cast + accumulate of the 16-bit weight gradient into the fp32 parameter gradient
+ * (flash_dropout/functional/blockwise_dropout_matmul_cuda.py:35-53 under autocast).
+ * ------------------------------------------------------------------------------------------ */
+
+/* sd_gemm_dsd whose result goes through ReLU before it is stored: C = max(scale * (keep o A) . B^T, 0). */
+int sd_gemm_dsd_relu(const void* A, int64_t a_rs, int64_t a_cs,
+                     const void* B, int64_t b_rs, int64_t b_cs,
+                     void* C, int64_t c_rs, int64_t c_cs,
+                     int M, int N, int K, const void* plan, int plan_side,
+                     float scale, int dtype, void* workspace, int* status, void* stream);
+
+/* sd_gemm_dsd with an fp32 result: C (float, element strides c_rs / c_cs, 4-byte aligned) is overwritten, or with
+ * accumulate != 0 added to.  For the weight gradient: written straight into the fp32 gradient of the parameter. */
+int sd_gemm_dsd_f32(const void* A, int64_t a_rs, int64_t a_cs,
+                    const void* B, int64_t b_rs, int64_t b_cs,
+                    float* C, int64_t c_rs, int64_t c_cs,
+                    int M, int N, int K, const void* plan, int plan_side,
+                    float scale, int dtype, int accumulate, void* workspace, int* status, void* stream);
+
+/* sd_gemm_sdd followed by the derivative of a ReLU that produced the layer's input X[M, N] (row-major, row stride
+ * x_rs, 16-byte aligned rows, N a multiple of 8): C = (X > 0) o scale * keep o (A . B^T). */
+int sd_gemm_sdd_relu_mask(const void* A, int64_t a_rs, int64_t a_cs,
+                          const void* B, int64_t b_rs, int64_t b_cs,
+                          void* C, int64_t c_rs, int64_t c_cs,
+                          int M, int N, int K, const void* plan,
+                          const void* X, int64_t x_rs,
+                          float scale, int dtype, void* workspace, int* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Fused convolution: im2col + DSD in one kernel.  The A operand of the product is the im2col matrix of
  * flash_dropout/functional/im2col_conv2d.py:17-20 (rows = output pixels m = (n, p, q), columns k = c*R*S + r*S + s),
  * but it is never written to memory: extra warps of the GEMM kernel gather each 64-wide stage of it straight from

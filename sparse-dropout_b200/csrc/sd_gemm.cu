@@ -152,6 +152,12 @@ struct GemmArgs {
     float* ws_slots;
     int* ws_flags;
     int use_table;                   // whole-tile schedule whose tiles can be described by the shared-memory table
+    int all_halves;                  // whole-tile schedule of a launch that would leave most SMs idle: every tile is
+                                     // handed out as two 128-wide halves, so twice as many SMs stream the operands
+    int act;                         // epilogue: 1 = ReLU on the result (eval/mlp/model.py:33-38 applies it as a separate op)
+    const unsigned short* mask_src;  // epilogue: result elements whose mask_src element is <= 0 are written as zeros: the
+    long long mask_rs;               // derivative of a ReLU that produced the layer's input (row-major, same shape as C)
+    int out_f32, out_acc;            // result stored as fp32 (optionally added to what C holds) instead of 16-bit
     ConvGather conv;                 // used by the GATHER variants of the kernel only
 };
 
@@ -262,6 +268,7 @@ struct WorkIter {
             const int waves = n_tiles / n_ctas, rest = n_tiles - waves * n_ctas;
             if (waves >= 1 && rest > 0 && 2 * rest <= n_ctas && !(g.mode == MODE_SDD && g.sdd_single))
                 whole_entries = waves * n_ctas;
+            if (g.all_halves) whole_entries = 0;
         }
         n_entries = whole_entries + 2 * (n_tiles - whole_entries);
         passes = (n_entries + n_ctas - 1) / n_ctas;
@@ -458,8 +465,45 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& g, bool vec_ok, int 
     }
 }
 
+// The same for an fp32 result (a gradient written, or added, straight into an fp32 buffer).
+__device__ __forceinline__ void store_chunk_f32(const GemmArgs& g, int row, int col, const uint32_t (&r)[32]) {
+    if (row >= g.MM || col >= g.NN) return;
+    float* C = static_cast<float*>(g.C);
+    if (g.c_cs == 1 && (g.c_rs & 3) == 0 && (reinterpret_cast<uintptr_t>(g.C) & 15) == 0 && col + 32 <= g.NN) {
+        float4* dst = reinterpret_cast<float4*>(C + (long long)row * g.c_rs + col);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+            float4 o = make_float4(__uint_as_float(r[4 * v]) * g.scale, __uint_as_float(r[4 * v + 1]) * g.scale,
+                                   __uint_as_float(r[4 * v + 2]) * g.scale, __uint_as_float(r[4 * v + 3]) * g.scale);
+            if (g.out_acc) { const float4 old = dst[v]; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+            dst[v] = o;
+        }
+    } else {
+        // column-major result: consecutive lanes = consecutive rows, one 128-byte segment per warp store
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < g.NN) {
+                float* dst = C + (long long)row * g.c_rs + (long long)(col + j) * g.c_cs;
+                const float v = __uint_as_float(r[j]) * g.scale;
+                *dst = g.out_acc ? *dst + v : v;
+            }
+    }
+}
+
 // Zero a 128 x 128 output tile with 128 threads (tid in [0,128)): one half of the epilogue group.
 __device__ __forceinline__ void zero_tile(const GemmArgs& g, bool vec_ok, bool vec_t_ok, int tid, int row0, int col0) {
+    if (g.out_f32) {
+        if (g.out_acc) return;                                   // adding nothing
+        float* C32 = static_cast<float*>(g.C);
+        if (g.c_rs == 1) {
+            for (int j = 0; j < 128; ++j)
+                if (row0 + tid < g.MM && col0 + j < g.NN) C32[(long long)(col0 + j) * g.c_cs + row0 + tid] = 0.f;
+        } else {
+            for (int i = 0; i < 128; ++i)
+                if (row0 + i < g.MM && col0 + tid < g.NN) C32[(long long)(row0 + i) * g.c_rs + (long long)(col0 + tid) * g.c_cs] = 0.f;
+        }
+        return;
+    }
     unsigned short* C = static_cast<unsigned short*>(g.C);
     if (vec_ok && row0 + 128 <= g.MM && col0 + 128 <= g.NN) {
         const int cchunk = tid & 15, rsub = tid >> 4;
@@ -573,8 +617,20 @@ __device__ bool reduce_shared_tile(const GemmArgs& g, const Seg& seg, int eidx, 
         const int row = seg.a_row + q * 32 + (e & 31);
         const int col = (c < 4 ? seg.b_row0 + c * 32 : seg.b_row1 + (c - 4) * 32) + (e >> 5) * 4;
         if (row >= g.MM || col >= g.NN) continue;
-        const float f[4] = {acc.x * g.scale, acc.y * g.scale, acc.z * g.scale, acc.w * g.scale};
-        if (quad_ok && col + 4 <= g.NN) {
+        float f[4] = {acc.x * g.scale, acc.y * g.scale, acc.z * g.scale, acc.w * g.scale};
+        if (g.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] = fmaxf(f[j], 0.f);
+        }
+        if (g.out_f32) {
+            float* C32 = static_cast<float*>(g.C);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (col + j < g.NN) {
+                    float* dst = C32 + (long long)row * g.c_rs + (long long)(col + j) * g.c_cs;
+                    *dst = g.out_acc ? *dst + f[j] : f[j];
+                }
+        } else if (quad_ok && col + 4 <= g.NN) {
             uint2 o;
             o.x = pack2(f[0], f[1], g.is_bf16);
             o.y = pack2(f[2], f[3], g.is_bf16);
@@ -958,6 +1014,31 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             float* slot = nullptr;
             if (partial) slot = g.ws_slots + size_t(cta) * WS_SLOT_FLOATS;
             // One chunk: 32 rows x 32 fp32 columns in r, thread = row.  `odd` chunks close a pair.
+            // Elementwise work on a chunk before it is converted: the fused ReLU, or the mask of a ReLU's derivative.
+            auto fix = [&](const int c, uint32_t (&r)[32]) {
+                if (partial) return;                             // shared tiles are finished by reduce_shared_tile
+                if (g.act == 1) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = int(r[j]) < 0 ? 0u : r[j];   // sign bit set -> 0
+                }
+                if (g.mask_src) {
+                    const int col = c < 4 ? w.b_row0 + c * 32 : w.b_row1 + (c - 4) * 32;
+                    if (row < g.MM) {
+                        const uint4* src = reinterpret_cast<const uint4*>(g.mask_src + (long long)row * g.mask_rs + col);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            if (col + 8 * v >= g.NN) break;      // N is a multiple of 8 here: whole groups in or out
+                            const uint4 q = __ldg(src + v);
+                            const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (short(wv[j] & 0xffffu) <= 0) r[8 * v + 2 * j] = 0u;
+                                if (short(wv[j] >> 16) <= 0) r[8 * v + 2 * j + 1] = 0u;
+                            }
+                        }
+                    }
+                }
+            };
             auto process = [&](const int c, const uint32_t (&r)[32]) {
                 const int col = c < 4 ? w.b_row0 + c * 32 : w.b_row1 + (c - 4) * 32;
                 if (partial) {
@@ -1016,6 +1097,8 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                         }
                         ++n_stores;
                     }
+                } else if (g.out_f32) {
+                    store_chunk_f32(g, row, col, r);
                 } else {
                     store_chunk(g, vec_ok, row, col, r);
                 }
@@ -1027,8 +1110,10 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             tmem_ld_wait();
             for (int c = c0; c < c0 + nchunks; c += 2) {
                 tmem_ld_32x32(taddr + (c + 1) * 32, rbuf[1]);
+                if (g.act | (g.mask_src != nullptr)) fix(c, rbuf[0]);
                 process(c, rbuf[0]);
                 tmem_ld_wait();
+                if (g.act | (g.mask_src != nullptr)) fix(c + 1, rbuf[1]);
                 if (c + 2 < c0 + nchunks) tmem_ld_32x32(taddr + (c + 2) * 32, rbuf[0]);
                 process(c + 1, rbuf[1]);
                 tmem_ld_wait();
@@ -1164,6 +1249,14 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     return SD_OK;
 }
 
+// Optional epilogue work of one launch (see the fields of the same names in GemmArgs).
+struct GemmExtras {
+    int act = 0;
+    const void* mask_src = nullptr;
+    int64_t mask_rs = 0;
+    int out_f32 = 0, out_acc = 0;
+};
+
 struct PlanView {
     const int *header, *row_ptr, *col_idx, *col_ptr, *row_idx, *row_order, *col_order, *sdd_items, *drop_pairs, *kept_pairs;
 };
@@ -1188,7 +1281,7 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
                     void* C, int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side,
                     float scale, int dtype, void* workspace, int* status, void* stream, int max_ctas = 0,
                     bool zero_dropped = true, bool sdd_t = false, int panels = 0, const ConvGather* conv = nullptr,
-                    int gather = 0) {
+                    int gather = 0, const GemmExtras* extras = nullptr) {
     // gather: 1 / 2 = A is the im2col matrix of `conv` (rows = pixels) / its transpose (rows = k), built inside the
     // kernel from the NCHW input; A, a_rs, a_cs are then ignored.
     // panels: 1 = A is the conv's im2col matrix in panels of 128 pixels ([pixels/128][kg][128]); DSD with the plan's
@@ -1237,6 +1330,20 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
 
     GemmArgs g{};
     if (conv) g.conv = *conv;
+    if (extras) {
+        if (extras->mask_src) {
+            if ((reinterpret_cast<uintptr_t>(extras->mask_src) & 15) || (extras->mask_rs & 7) || extras->mask_rs < N || (N & 7))
+                return fail(SD_ERR_LAYOUT, "the mask source must be row-major with 16-byte aligned rows (N and its row "
+                                           "stride multiples of 8, got N=%d, stride %lld)", N, (long long)extras->mask_rs);
+            if (panels || sdd_t) return fail(SD_ERR_INVALID_ARG, "the mask source is not supported for panel or transposed results");
+        }
+        g.act = extras->act;
+        g.mask_src = static_cast<const unsigned short*>(extras->mask_src);
+        g.mask_rs = extras->mask_rs;
+        g.out_f32 = extras->out_f32;
+        g.out_acc = extras->out_acc;
+        if (g.out_f32 && (reinterpret_cast<uintptr_t>(C) & 3)) return fail(SD_ERR_LAYOUT, "an fp32 result must be 4-byte aligned");
+    }
     g.mode = mode;
     g.MM = M; g.NN = N; g.KK = K;
     g.C = C; g.c_rs = c_rs; g.c_cs = c_cs;
@@ -1303,12 +1410,22 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         const char* e = getenv("SD_SPLIT_MIN_KTILES");   // tuning knob: minimum reduction length (in 128-wide K tiles)
         return e ? atoi(e) : 16;
     }();
-    if (workspace && tiles_upper * 2 <= grid && k_tiles >= split_min_k_tiles && !c_panel_kg) {
+    const bool elementwise = g.mask_src != nullptr;   // the mask is applied by whole-tile epilogues only
+    static const int small_halves = [] {
+        const char* e = getenv("SD_SMALL_HALVES");         // tuning knob: 0 keeps whole 128x256 tiles on small launches
+        return e ? atoi(e) : 1;
+    }();
+    if (workspace && tiles_upper * 2 <= grid && k_tiles >= split_min_k_tiles && !c_panel_kg && !elementwise) {
         if (reinterpret_cast<uintptr_t>(workspace) & 15) return fail(SD_ERR_LAYOUT, "workspace must be 16-byte aligned");
         if (grid > WS_MAX_CTAS) grid = WS_MAX_CTAS;
         g.split = 1;
         g.ws_flags = static_cast<int*>(workspace);
         g.ws_slots = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + WS_FLAG_BYTES);
+    } else if (small_halves && mode != MODE_SDD && !gather && N > 128 && tiles_upper * 2 <= grid) {
+        // a launch this small is bound by how fast one SM can stream a tile's operands: hand every 128x256 tile out as
+        // two 128-wide halves, so that twice as many SMs share the stream
+        g.all_halves = 1;
+        grid = int(tiles_upper * 2);
     } else if (tiles_upper < grid) {
         grid = int(tiles_upper);
     }
@@ -1317,7 +1434,9 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Row-major result with 16-byte rows: written by TMA (clipped at the ragged edge); otherwise by the warps.
     CUtensorMap tc = ta;
-    if (c_panel_kg) {
+    if (g.out_f32) {
+        // fp32 results are written by the epilogue warps directly
+    } else if (c_panel_kg) {
         EncodeTiledFn enc = encode_tiled_fn();
         const long long all_rows = (long long)((N + 127) / 128) * c_panel_kg;
         if (all_rows > (1ll << 31) - 1) return fail(SD_ERR_TOO_LARGE, "panel matrix too large");
@@ -1515,6 +1634,36 @@ int sd_conv_dsd_dw(const void* x, int N, int C, int H, int W, int R, int S, int 
     // dW2d^T [k, Ko] = (keep o col)^T [k, pixels] . dY2d^T [Ko, pixels]^T: B = dY2d^T, C = dW2d^T (strides swapped)
     return sd::run_gemm(sd::MODE_DSD, nullptr, 0, 0, dY2d, dy_cs, dy_rs, dW2d, dw_cs, dw_rs, cv.k_real, Ko, cv.pixels,
                         plan, SD_PLAN_COLS, scale, dtype, workspace, status, stream, 0, true, false, 0, &cv, 2);
+}
+
+int sd_gemm_dsd_relu(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
+                     int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side, float scale,
+                     int dtype, void* workspace, int* status, void* stream) {
+    sd::GemmExtras ex;
+    ex.act = 1;
+    return sd::run_gemm(sd::MODE_DSD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, plan_side, scale,
+                        dtype, workspace, status, stream, 0, true, false, 0, nullptr, 0, &ex);
+}
+
+int sd_gemm_dsd_f32(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, float* C,
+                    int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, int plan_side, float scale,
+                    int dtype, int accumulate, void* workspace, int* status, void* stream) {
+    sd::GemmExtras ex;
+    ex.out_f32 = 1;
+    ex.out_acc = accumulate ? 1 : 0;
+    return sd::run_gemm(sd::MODE_DSD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, plan_side, scale,
+                        dtype, workspace, status, stream, 0, true, false, 0, nullptr, 0, &ex);
+}
+
+int sd_gemm_sdd_relu_mask(const void* A, int64_t a_rs, int64_t a_cs, const void* B, int64_t b_rs, int64_t b_cs, void* C,
+                          int64_t c_rs, int64_t c_cs, int M, int N, int K, const void* plan, const void* X, int64_t x_rs,
+                          float scale, int dtype, void* workspace, int* status, void* stream) {
+    if (!X) return sd::fail(SD_ERR_INVALID_ARG, "X is null");
+    sd::GemmExtras ex;
+    ex.mask_src = X;
+    ex.mask_rs = x_rs;
+    return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
+                        workspace, status, stream, 0, true, false, 0, nullptr, 0, &ex);
 }
 
 size_t sd_workspace_bytes(void) {

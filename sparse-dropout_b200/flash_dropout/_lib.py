@@ -25,6 +25,7 @@ EXPORTS = (
     "sd_gemm_dsd_static_scratch", "sd_im2col_kept", "sd_col2im_kept", "sd_im2col_kept_panels", "sd_col2im_kept_panels",
     "sd_gemm_dsd_panels", "sd_gemm_sdd_kept_t_panels", "sd_selftest_bounded_wait", "sd_check_status",
     "sd_conv_fused_supported", "sd_conv_dsd_fwd", "sd_conv_dsd_dw",
+    "sd_gemm_dsd_relu", "sd_gemm_dsd_f32", "sd_gemm_sdd_relu_mask",
 )
 
 
@@ -83,6 +84,12 @@ def lib() -> C.CDLL:
     L.sd_gemm_dsd_panels.argtypes = [vp, i32, i32] + mat * 2 + [i32, vp, i32, f32, i32, vp, vp, vp]
     L.sd_gemm_sdd_kept_t_panels.restype = i32
     L.sd_gemm_sdd_kept_t_panels.argtypes = mat * 2 + [vp, i32, i32, i32, vp, f32, i32, vp, vp, vp]
+    L.sd_gemm_dsd_relu.restype = i32
+    L.sd_gemm_dsd_relu.argtypes = L.sd_gemm_dsd.argtypes
+    L.sd_gemm_dsd_f32.restype = i32
+    L.sd_gemm_dsd_f32.argtypes = mat * 3 + [i32, i32, i32, vp, i32, f32, i32, i32, vp, vp, vp]
+    L.sd_gemm_sdd_relu_mask.restype = i32
+    L.sd_gemm_sdd_relu_mask.argtypes = mat * 3 + [i32, i32, i32, vp, vp, i64, f32, i32, vp, vp, vp]
     L.sd_conv_fused_supported.restype = i32
     L.sd_conv_fused_supported.argtypes = [i32] * 12
     L.sd_conv_dsd_fwd.restype = i32

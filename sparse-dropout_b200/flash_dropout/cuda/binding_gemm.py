@@ -279,14 +279,35 @@ def dense(A: torch.Tensor, B: torch.Tensor, scale: float = 1.0, out: torch.Tenso
 
 
 def dsd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, side: int, scale: float,
-        out: torch.Tensor | None = None, ws="auto") -> torch.Tensor:
-    """``scale * (keep o A) @ B.T``; ``side`` says whether A's row blocks are the plan's rows or columns."""
+        out: torch.Tensor | None = None, ws="auto", relu: bool = False, accumulate: bool = False) -> torch.Tensor:
+    """``scale * (keep o A) @ B.T``; ``side`` says whether A's row blocks are the plan's rows or columns.
+
+    ``relu`` applies ReLU to the result in the kernel's epilogue.  An fp32 ``out`` receives the result in fp32
+    (overwritten, or added to with ``accumulate``): the way a weight gradient goes straight into an fp32 buffer."""
     dt = _check_pair(A, B)
     M, K = A.shape
     want = (ceil(M / TILE), ceil(K / TILE)) if side == _lib.SD_PLAN_ROWS else (ceil(K / TILE), ceil(M / TILE))
     if (plan.R, plan.C) != want:
         raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match operand A {tuple(A.shape)} (need {want})")
+    if out is not None and out.dtype == torch.float32:
+        if relu:
+            raise RuntimeError("relu and an fp32 result are not combined")
+        if tuple(out.shape) != (M, B.size(0)) or out.device != A.device or not (out.stride(0) == 1 or out.stride(1) == 1):
+            raise RuntimeError("out has the wrong shape, device or strides")
+        with _on_device(A.device):
+            _lib.check(_lib.lib().sd_gemm_dsd_f32(*_mat(A), *_mat(B), *_mat(out), M, B.size(0), K, plan.buf.data_ptr(),
+                                                  side, float(scale), dt, int(accumulate), _ws_ptr(ws, A.device),
+                                                  _status_ptr(A.device), _lib.stream_ptr(A.device)))
+        return out
+    if accumulate:
+        raise RuntimeError("accumulate needs an fp32 out")
     Cm = _out(A, B, out)
+    if relu:
+        with _on_device(A.device):
+            _lib.check(_lib.lib().sd_gemm_dsd_relu(*_mat(A), *_mat(B), *_mat(Cm), M, B.size(0), K, plan.buf.data_ptr(),
+                                                   side, float(scale), dt, _ws_ptr(ws, A.device), _status_ptr(A.device),
+                                                   _lib.stream_ptr(A.device)))
+        return Cm
     with _on_device(A.device):
         _lib.check(_lib.lib().sd_gemm_dsd(*_mat(A), *_mat(B), *_mat(Cm), M, B.size(0), K, plan.buf.data_ptr(),
                                           side, float(scale), dt, _ws_ptr(ws, A.device), _status_ptr(A.device),
@@ -295,14 +316,27 @@ def dsd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, side: int, scale: flo
 
 
 def sdd(A: torch.Tensor, B: torch.Tensor, plan: BlockPlan, scale: float,
-        out: torch.Tensor | None = None, ws="auto", zero_dropped: bool = True) -> torch.Tensor:
+        out: torch.Tensor | None = None, ws="auto", zero_dropped: bool = True,
+        relu_mask: torch.Tensor | None = None) -> torch.Tensor:
     """``scale * keep o (A @ B.T)``: kept output tiles computed, dropped tiles written as zeros
-    (or left untouched with ``zero_dropped=False``, for consumers that only read kept tiles)."""
+    (or left untouched with ``zero_dropped=False``, for consumers that only read kept tiles).
+
+    ``relu_mask``: a row-major tensor of the result's shape; result elements where it is <= 0 are written as zeros
+    (the derivative of the ReLU that produced it), in the kernel's epilogue."""
     dt = _check_pair(A, B)
     M, N = A.size(0), B.size(0)
     if (plan.R, plan.C) != (ceil(M / TILE), ceil(N / TILE)):
         raise RuntimeError(f"plan grid {(plan.R, plan.C)} does not match the output {(M, N)}")
     Cm = _out(A, B, out)
+    if relu_mask is not None:
+        if tuple(relu_mask.shape) != (M, N) or relu_mask.dtype != A.dtype or relu_mask.stride(1) != 1 or not zero_dropped:
+            raise RuntimeError("relu_mask must be a row-major tensor of the result's shape and dtype")
+        with _on_device(A.device):
+            _lib.check(_lib.lib().sd_gemm_sdd_relu_mask(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1),
+                                                        plan.buf.data_ptr(), relu_mask.data_ptr(), relu_mask.stride(0),
+                                                        float(scale), dt, _ws_ptr(ws, A.device), _status_ptr(A.device),
+                                                        _lib.stream_ptr(A.device)))
+        return Cm
     with _on_device(A.device):
         fn = _lib.lib().sd_gemm_sdd if zero_dropped else _lib.lib().sd_gemm_sdd_kept
         _lib.check(fn(*_mat(A), *_mat(B), *_mat(Cm), M, N, A.size(1), plan.buf.data_ptr(),

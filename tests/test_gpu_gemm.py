@@ -311,3 +311,36 @@ def test_errors_mirror_the_reference(built_lib):
     with pytest.raises(ValueError, match="multiple of 128"):
         ext.gemm_dsd(a, a, mask, 64, 1.0)
     assert ext.gemm(a, a).abs().sum().item() == 0     # the context is still healthy
+
+
+@pytest.mark.parametrize("M,N,K,p", [(512, 1024, 1024, 0.5), (384, 264, 640, 0.3), (2048, 2048, 2048, 0.5), (16384, 384, 1536, 0.2)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_epilogues_against_oracle(built_lib, M, N, K, p, dtype):
+    """The elementwise neighbours fused into the epilogues, each against fp32 PyTorch of the same composition on the
+    oracle's products: ReLU after the forward, the ReLU-derivative mask on dX, and dW written / accumulated in fp32."""
+    from flash_dropout import _lib
+    from flash_dropout.cuda import binding_gemm as bg
+    x, w, dy = _inputs(M, N, K, seed=41, dtype=dtype)
+    x = torch.relu(x)                                             # the layer's input is the output of a ReLU
+    mask_np = pm.block_mask(M, K, 128, p, seed=42, offset=N)
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, 128, p, w, dy)
+    plan = bg.BlockPlan.from_mask(torch.from_numpy(mask_np).to(DEV), M, K, 128)
+    A, B, dC = x.to(DEV), w.to(DEV), dy.to(DEV)
+    s = 1 / (1 - p)
+    tol = dict(rtol=RTOL, atol=ATOL) if dtype == torch.float16 else dict(rtol=2e-2, atol=4e-2)
+    y = bg.dsd(A, B, plan, _lib.SD_PLAN_ROWS, s, relu=True)
+    torch.testing.assert_close(y.float().cpu(), torch.relu(y_ref), **tol)
+    assert (y >= 0).all()
+    dX = bg.sdd(dC, B.T, plan, s, relu_mask=A)
+    torch.testing.assert_close(dX.float().cpu(), dx_ref * (x.float() > 0), **tol)
+    assert (dX.float().cpu()[x.float() <= 0] == 0).all()
+    # fp32 weight gradient: written, then accumulated on top
+    dW = torch.full((N, K), float("nan"), device=DEV, dtype=torch.float32)
+    bg.dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, s, out=dW.T)
+    tol32 = dict(rtol=5e-3, atol=5e-3 * max(1.0, M ** 0.5 / 16))  # fp32 store: only the 16-bit inputs round
+    torch.testing.assert_close(dW.cpu(), dw_ref, **tol32)
+    bg.dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, s, out=dW.T, accumulate=True)
+    torch.testing.assert_close(dW.cpu(), 2 * dw_ref, **tol32)
+    dW2 = torch.zeros((N, K), device=DEV, dtype=torch.float32)
+    bg.dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, s, out=dW2.T, ws=None)      # whole tiles, no workspace
+    torch.testing.assert_close(dW2.cpu(), dw_ref, **tol32)
