@@ -206,7 +206,7 @@ def run_ours(args) -> None:
             pending[i % N_SETS].wait()
             pending[i % N_SETS] = None
         # mask + kept-block lists for this step: one launch, offset = step index, rank = Philox subsequence
-        _lib.check(L.sd_plan_from_seed(plan.buf.data_ptr(), plan.R, plan.C, 1, SEED, (rank << 40) + i,
+        _lib.check(L.sd_plan_from_seed(plan.buf.data_ptr(), plan.R, plan.C, 1, 1, SEED, (rank << 40) + i,
                                        P_DROP, None, stream.cuda_stream))
         if events is not None:
             events[0].record()
@@ -251,7 +251,7 @@ def run_ours(args) -> None:
     # kept blocks of every timed step's mask, recomputed after the timed region (same seed / offsets)
     kept_dev = torch.zeros(1, dtype=torch.int64, device=dev)
     for i in range(steps):
-        _lib.check(L.sd_plan_from_seed(plans[0].buf.data_ptr(), plans[0].R, plans[0].C, 1, SEED,
+        _lib.check(L.sd_plan_from_seed(plans[0].buf.data_ptr(), plans[0].R, plans[0].C, 1, 1, SEED,
                                        (rank << 40) + warmup + i, P_DROP, None, stream.cuda_stream))
         kept_dev += plans[0].header[0]
     kept = kept_dev.item()
@@ -425,7 +425,7 @@ def run_ours(args) -> None:
         sus_ms = s0.elapsed_time(s1)
         kept_dev.zero_()
         for i in range(n_sus):
-            _lib.check(L.sd_plan_from_seed(plans[0].buf.data_ptr(), plans[0].R, plans[0].C, 1, SEED,
+            _lib.check(L.sd_plan_from_seed(plans[0].buf.data_ptr(), plans[0].R, plans[0].C, 1, 1, SEED,
                                            (rank << 40) + 10_000 + i, P_DROP, None, stream.cuda_stream))
             kept_dev += plans[0].header[0]
         sus_tflops = useful_flops(kept_dev.item()) / (sus_ms * 1e-3) / 1e12
@@ -644,7 +644,7 @@ def measure_train(workload: str, variant: str, dev, world: int, rank: int, steps
         host_y = host_x
         name = "char-GPT 6 layers d=384 6 heads ctx 256 vocab 65, bf16 autocast, batch 64/GPU, p=0.2, AdamW"
         loss_of = lambda m, x, y: m(x)[1]
-    dp = FlatGradDataParallel(model, bucket_bytes=4 << 20)
+    dp = FlatGradDataParallel(model, bucket_bytes=4 << 20, fuse_wgrad=True)
     sd_random.manual_seed(SEED, subsequence=rank)
     x_dev, y_dev = host_x.to(dev), host_y.to(dev)
 

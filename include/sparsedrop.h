@@ -60,8 +60,9 @@ const char* sd_last_error(void);
  * Block plan = the drop mask plus every compacted kept-block index list the kernels walk.
  *
  * A plan describes an R x C grid of 128x128 tiles (R = ceil(M/128), C = ceil(K/128)).  The
- * logical dropout blocks may be larger: block_size = 128*rep, and tile (r, c) inherits the
- * decision of logical block (r / rep, c / rep).  True / 1 = dropped, as in
+ * logical dropout blocks may be larger, and need not be square: block_size = (128*rep_r, 128*rep_c) — the (m, k)
+ * pairs of eval/mlp/config.py:23-27 — and tile (r, c) inherits the decision of logical block
+ * (r / rep_r, c / rep_c).  True / 1 = dropped, as in
  * flash_dropout/functional/utils.py:11-16.
  *
  * The plan lives in ONE caller-allocated device buffer of sd_plan_bytes(R, C) bytes, laid out
@@ -91,12 +92,12 @@ int sd_plan_offsets(int R, int C, sd_plan_layout* out);
  * Replaces blockwise_dropout_mask (flash_dropout/functional/utils.py:11-16: torch.rand(...) < p)
  * and the index-list builders (utils.py:19-69 mask_to_increment_table;
  * blockwise_dropout_matmul_triton.py:48 torch.nonzero(~mask)).
- * Logical block (i, j) of the ceil(R/rep) x ceil(C/rep) grid is dropped iff
+ * Logical block (i, j) of the ceil(R/rep_r) x ceil(C/rep_c) grid (Cm = ceil(C/rep_c) columns) is dropped iff
  *   u < p,  u = float(philox4x32_10(key = seed, counter = (i*Cm + j, 0, offset_lo, offset_hi)).x >> 8) * 2^-24
  * compared in fp32.  mask_out (optional, may be NULL) receives the logical mask as
- * ceil(R/rep) x ceil(C/rep) bytes, row-major.
+ * ceil(R/rep_r) x ceil(C/rep_c) bytes, row-major.
  */
-int sd_plan_from_seed(void* plan, int R, int C, int rep, uint64_t seed, uint64_t offset, float p,
+int sd_plan_from_seed(void* plan, int R, int C, int rep_r, int rep_c, uint64_t seed, uint64_t offset, float p,
                       uint8_t* mask_out, void* stream);
 
 /*
@@ -105,15 +106,29 @@ int sd_plan_from_seed(void* plan, int R, int C, int rep, uint64_t seed, uint64_t
  * captured CUDA graph that contains this launch draws a fresh mask on every replay.  No counterpart in
  * the reference (its masks come from torch.rand on the host-controlled generator, utils.py:15).
  */
-int sd_plan_from_seed_counter(void* plan, int R, int C, int rep, uint64_t seed, uint64_t base_offset,
+int sd_plan_from_seed_counter(void* plan, int R, int C, int rep_r, int rep_c, uint64_t seed, uint64_t base_offset,
                               uint64_t* device_counter, float p, uint8_t* mask_out, void* stream);
+
+/*
+ * Several plans from ONE launch: plan i of n draws like sd_plan_from_seed_counter with offset base_offset + i +
+ * *device_counter, and the launch advances the shared counter by n, so the masks equal those of n single launches
+ * in that order.  The descriptors live in a caller-owned device buffer of sd_plan_batch_desc_bytes(n) bytes, zero
+ * initialised, 8-byte aligned: fill a host buffer of the same size entry by entry with sd_plan_batch_describe
+ * (which needs the device buffer's address), copy it to the device once, then call sd_plan_batch_launch every step.
+ * Each plan is at most 3072 x 32 tiles.  No counterpart in the reference (one torch.rand call per layer per step,
+ * flash_dropout/functional/utils.py:15).
+ */
+size_t sd_plan_batch_desc_bytes(int n);
+int sd_plan_batch_describe(void* host_desc, void* device_desc, int n, int i, void* plan, int R, int C, int rep_r, int rep_c,
+                           uint64_t seed, uint64_t base_offset, uint64_t* device_counter, float p, uint8_t* mask_out);
+int sd_plan_batch_launch(const void* device_desc, int n, void* stream);
 
 /*
  * Build the plan from a caller-supplied bool mask (1 byte per logical block, any two strides),
  * the form in which the reference passes masks to gemm_dsd / gemm_sdd
- * (flash_dropout/cuda/binding_gemm.py:29-47).  mask is ceil(R/rep) x ceil(C/rep).
+ * (flash_dropout/cuda/binding_gemm.py:29-47).  mask is ceil(R/rep_r) x ceil(C/rep_c).
  */
-int sd_plan_from_mask(void* plan, int R, int C, int rep, const uint8_t* mask,
+int sd_plan_from_mask(void* plan, int R, int C, int rep_r, int rep_c, const uint8_t* mask,
                       int64_t mask_row_stride, int64_t mask_col_stride, void* stream);
 
 /* ------------------------------------------------------------------------------------------

@@ -25,12 +25,13 @@ import torch
 import torch.nn.functional as F
 
 
-def _keep_matrix(mask, M: int, K: int, block_size: int) -> torch.Tensor:
-    """fp32 (M, K) matrix: 0 in dropped blocks, 1 elsewhere."""
+def _keep_matrix(mask, M: int, K: int, block_size) -> torch.Tensor:
+    """fp32 (M, K) matrix: 0 in dropped blocks, 1 elsewhere.  ``block_size``: an int or an (m, k) pair."""
+    bm, bk = (block_size if isinstance(block_size, (tuple, list)) else (block_size, block_size))
     m = torch.as_tensor(np.asarray(mask), dtype=torch.bool)
-    assert tuple(m.shape) == (ceil(M / block_size), ceil(K / block_size)), (m.shape, M, K, block_size)
+    assert tuple(m.shape) == (ceil(M / bm), ceil(K / bk)), (m.shape, M, K, block_size)
     keep = (~m).to(torch.float32)
-    keep = keep.repeat_interleave(block_size, 0).repeat_interleave(block_size, 1)
+    keep = keep.repeat_interleave(bm, 0).repeat_interleave(bk, 1)
     return keep[:M, :K]
 
 

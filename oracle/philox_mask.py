@@ -58,19 +58,27 @@ def uniform24(seed: int, offset: int, n: int) -> np.ndarray:
     return (x >> np.uint32(8)).astype(np.float32) * np.float32(2.0 ** -24)
 
 
-def block_mask(M: int, K: int, block_size: int, p: float, seed: int, offset: int = 0) -> np.ndarray:
-    """Drop mask (True = dropped) of shape (ceil(M/bs), ceil(K/bs)) — utils.py:11-16 with the Philox draw."""
+def block_pair(block_size) -> tuple:
+    """(rows, columns) of a logical block: an int, or an (m, k) pair as in eval/mlp/config.py:23-27."""
+    if isinstance(block_size, (tuple, list)):
+        return int(block_size[0]), int(block_size[1])
+    return int(block_size), int(block_size)
+
+
+def block_mask(M: int, K: int, block_size, p: float, seed: int, offset: int = 0) -> np.ndarray:
+    """Drop mask (True = dropped) of shape (ceil(M/bm), ceil(K/bk)) — utils.py:11-16 with the Philox draw."""
     assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
-    R, C = ceil(M / block_size), ceil(K / block_size)
+    bm, bk = block_pair(block_size)
+    R, C = ceil(M / bm), ceil(K / bk)
     u = uniform24(seed, offset, R * C).reshape(R, C)
     return u < np.float32(p)
 
 
-def expand_to_tiles(mask: np.ndarray, M: int, K: int, block_size: int, tile: int = 128) -> np.ndarray:
-    """Mask at `tile` granularity: tile (r, c) inherits logical block (r // rep, c // rep)."""
-    rep = block_size // tile
+def expand_to_tiles(mask: np.ndarray, M: int, K: int, block_size, tile: int = 128) -> np.ndarray:
+    """Mask at `tile` granularity: tile (r, c) inherits logical block (r // rep_r, c // rep_c)."""
+    bm, bk = block_pair(block_size)
     R, C = ceil(M / tile), ceil(K / tile)
-    return np.repeat(np.repeat(mask, rep, axis=0), rep, axis=1)[:R, :C]
+    return np.repeat(np.repeat(mask, bm // tile, axis=0), bk // tile, axis=1)[:R, :C]
 
 
 def kept_pairs(mask: np.ndarray) -> np.ndarray:

@@ -89,7 +89,7 @@ __device__ __forceinline__ void block_exclusive_scan_pair(int a, int b, unsigned
 
 struct PlanArgs {
     unsigned char* plan;
-    int R, C, rep;
+    int R, C, rep, rep_c;   // logical block = rep x rep_c tiles (rows x columns)
     int from_seed;
     unsigned long long seed, offset;
     unsigned long long* counter;   // optional device counter added to `offset`, incremented by this launch
@@ -97,6 +97,10 @@ struct PlanArgs {
     const unsigned char* mask_in;
     long long mask_rs, mask_cs;
     unsigned char* mask_out;
+    // one launch for several plans (plan_bits_batch_kernel): the CTAs share `counter`; plan j of n draws with
+    // offset + j + *counter, and the last CTA to arrive (counted in *batch_arrivals) advances the counter by n
+    unsigned int* batch_arrivals;
+    int batch_n;
 };
 
 __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
@@ -105,9 +109,9 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
     __shared__ int bins[kPlanThreads];
     __shared__ int s_max_row, s_max_col;
 
-    const int R = a.R, C = a.C, rep = a.rep;
+    const int R = a.R, C = a.C, rep = a.rep, rep_c = a.rep_c;
     const int RC = R * C;
-    const int Cm = (C + rep - 1) / rep;
+    const int Cm = (C + rep_c - 1) / rep_c;
     const sd_plan_layout L = plan_layout(R, C);
     int* header = reinterpret_cast<int*>(a.plan + L.header);
     int* row_ptr = reinterpret_cast<int*>(a.plan + L.row_ptr);
@@ -131,11 +135,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
     // ---- phase 0: the drop decision of every tile (1 = dropped)
     for (int i = threadIdx.x; i < RC; i += kPlanThreads) {
         const int r = i / C, c = i - r * C;
-        const int lr = r / rep, lc = c / rep;
+        const int lr = r / rep, lc = c / rep_c;
         bool drop;
         if (a.from_seed) {
             drop = philox_drop(a.seed, offset, (unsigned long long)lr * Cm + lc, a.p);
-            if (a.mask_out && r == lr * rep && c == lc * rep) a.mask_out[(long long)lr * Cm + lc] = drop;
+            if (a.mask_out && r == lr * rep && c == lc * rep_c) a.mask_out[(long long)lr * Cm + lc] = drop;
         } else {
             drop = a.mask_in[lr * a.mask_rs + lc * a.mask_cs] != 0;
         }
@@ -300,7 +304,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_kernel(PlanArgs a) {
 constexpr int kBitsMaxRows = 3072;
 
 
-__global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) {
+__device__ __forceinline__ void plan_bits_body(const PlanArgs& a) {
     __shared__ unsigned keepmask[kBitsMaxRows];
     __shared__ int s_row_ptr[kBitsMaxRows];
     __shared__ int s_item_ptr[kBitsMaxRows];
@@ -311,8 +315,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
     __shared__ int bins[40];
     __shared__ int s_max_row;
 
-    const int R = a.R, C = a.C, rep = a.rep;
-    const int Cm = (C + rep - 1) / rep;
+    const int R = a.R, C = a.C, rep = a.rep, rep_c = a.rep_c;
+    const int Cm = (C + rep_c - 1) / rep_c;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const sd_plan_layout L = plan_layout(R, C);
     int* header = reinterpret_cast<int*>(a.plan + L.header);
@@ -337,11 +341,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
     __syncthreads();
     for (int i = threadIdx.x; i < R * C; i += kPlanThreads) {
         const int r = i / C, c = i - r * C;
-        const int lr = r / rep, lc = c / rep;
+        const int lr = r / rep, lc = c / rep_c;
         bool drop;
         if (a.from_seed) {
             drop = philox_drop(a.seed, offset, (unsigned long long)lr * Cm + lc, a.p);
-            if (a.mask_out && r == lr * rep && c == lc * rep) a.mask_out[(long long)lr * Cm + lc] = drop;
+            if (a.mask_out && r == lr * rep && c == lc * rep_c) a.mask_out[(long long)lr * Cm + lc] = drop;
         } else {
             drop = a.mask_in[lr * a.mask_rs + lc * a.mask_cs] != 0;
         }
@@ -457,7 +461,19 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
             header[H_C] = C;
             header[H_MAX_ROW] = s_max_row;
             header[H_MAX_COL] = mxc;
-            if (a.counter) *a.counter = offset - a.offset + 1;   // every thread read it before the first barrier
+            if (a.counter) {                                      // every thread read it before the first barrier
+                const unsigned long long drawn = offset - a.offset;
+                if (!a.batch_arrivals) {
+                    *a.counter = drawn + 1;
+                } else {
+                    // every CTA of the batch read the counter before it arrives here; the last one moves it on
+                    __threadfence();
+                    if (atomicAdd(a.batch_arrivals, 1u) == unsigned(a.batch_n - 1)) {
+                        *a.counter = drawn + a.batch_n;
+                        *a.batch_arrivals = 0u;
+                    }
+                }
+            }
         }
     }
     __syncthreads();
@@ -512,6 +528,16 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) 
     }
 }
 
+__global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_kernel(PlanArgs a) { plan_bits_body(a); }
+
+// Several plans from one launch: CTA j builds the plan list[j] describes.  A training step draws one mask per
+// SparseDrop layer; as separate launches of a few microseconds each they add up to a visible share of a small model's
+// step, and nothing orders them among themselves, so they run side by side here.
+__global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_batch_kernel(const PlanArgs* __restrict__ list) {
+    const PlanArgs a = list[blockIdx.x];
+    plan_bits_body(a);
+}
+
 // The same plan from a cluster of kPlanClusterSize CTAs, for grids of thousands of tiles, where one SM is bound by
 // the instructions it has to issue (a Philox draw and three list entries per tile).  CTA g owns a contiguous slice
 // of the rows and does everything plan_bits_kernel does on that slice; what one slice must know of the others -
@@ -538,8 +564,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_cluster_kernel(Plan
 
     cg::cluster_group cluster = cg::this_cluster();
     const int G = int(cluster.num_blocks()), gi = int(cluster.block_rank());
-    const int R = a.R, C = a.C, rep = a.rep;
-    const int Cm = (C + rep - 1) / rep;
+    const int R = a.R, C = a.C, rep = a.rep, rep_c = a.rep_c;
+    const int Cm = (C + rep_c - 1) / rep_c;
     const int r_lo = int((long long)R * gi / G), r_hi = int((long long)R * (gi + 1) / G), Rn = r_hi - r_lo;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const sd_plan_layout L = plan_layout(R, C);
@@ -565,11 +591,11 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_cluster_kernel(Plan
     __syncthreads();
     for (int i = threadIdx.x; i < Rn * C; i += kPlanThreads) {
         const int rl = i / C, c = i - rl * C, r = r_lo + rl;
-        const int lr = r / rep, lc = c / rep;
+        const int lr = r / rep, lc = c / rep_c;
         bool drop;
         if (a.from_seed) {
             drop = philox_drop(a.seed, offset, (unsigned long long)lr * Cm + lc, a.p);
-            if (a.mask_out && r == lr * rep && c == lc * rep) a.mask_out[(long long)lr * Cm + lc] = drop;
+            if (a.mask_out && r == lr * rep && c == lc * rep_c) a.mask_out[(long long)lr * Cm + lc] = drop;
         } else {
             drop = a.mask_in[lr * a.mask_rs + lc * a.mask_cs] != 0;
         }
@@ -756,7 +782,7 @@ __global__ void __launch_bounds__(kPlanThreads, 1) plan_bits_cluster_kernel(Plan
 static int launch_plan(const PlanArgs& a, void* stream) {
     if (!a.plan) return fail(SD_ERR_INVALID_ARG, "plan buffer is null");
     if (a.R <= 0 || a.C <= 0) return fail(SD_ERR_INVALID_ARG, "plan grid must be positive (R=%d, C=%d)", a.R, a.C);
-    if (a.rep <= 0) return fail(SD_ERR_INVALID_ARG, "block_size must be a positive multiple of 128");
+    if (a.rep <= 0 || a.rep_c <= 0) return fail(SD_ERR_INVALID_ARG, "block_size must be a positive multiple of 128");
     if (int64_t(a.R) * a.C > (int64_t(1) << 26))
         return fail(SD_ERR_TOO_LARGE, "plan grid %d x %d exceeds 2^26 tiles", a.R, a.C);
     cudaLaunchConfig_t cfg = {};
@@ -812,25 +838,25 @@ int sd_plan_offsets(int R, int C, sd_plan_layout* out) {
     return SD_OK;
 }
 
-int sd_plan_from_seed(void* plan, int R, int C, int rep, uint64_t seed, uint64_t offset, float p,
+int sd_plan_from_seed(void* plan, int R, int C, int rep_r, int rep_c, uint64_t seed, uint64_t offset, float p,
                       uint8_t* mask_out, void* stream) {
     if (!(p >= 0.0f && p < 1.0f)) return sd::fail(SD_ERR_INVALID_ARG, "Dropout probability must be in [0, 1)");
     sd::PlanArgs a{};
     a.plan = static_cast<unsigned char*>(plan);
-    a.R = R; a.C = C; a.rep = rep;
+    a.R = R; a.C = C; a.rep = rep_r; a.rep_c = rep_c;
     a.from_seed = 1;
     a.seed = seed; a.offset = offset; a.p = p;
     a.mask_out = mask_out;
     return sd::launch_plan(a, stream);
 }
 
-int sd_plan_from_seed_counter(void* plan, int R, int C, int rep, uint64_t seed, uint64_t base_offset,
+int sd_plan_from_seed_counter(void* plan, int R, int C, int rep_r, int rep_c, uint64_t seed, uint64_t base_offset,
                               uint64_t* device_counter, float p, uint8_t* mask_out, void* stream) {
     if (!(p >= 0.0f && p < 1.0f)) return sd::fail(SD_ERR_INVALID_ARG, "Dropout probability must be in [0, 1)");
     if (!device_counter) return sd::fail(SD_ERR_INVALID_ARG, "device_counter is null");
     sd::PlanArgs a{};
     a.plan = static_cast<unsigned char*>(plan);
-    a.R = R; a.C = C; a.rep = rep;
+    a.R = R; a.C = C; a.rep = rep_r; a.rep_c = rep_c;
     a.from_seed = 1;
     a.seed = seed; a.offset = base_offset; a.p = p;
     a.counter = reinterpret_cast<unsigned long long*>(device_counter);
@@ -838,12 +864,53 @@ int sd_plan_from_seed_counter(void* plan, int R, int C, int rep, uint64_t seed, 
     return sd::launch_plan(a, stream);
 }
 
-int sd_plan_from_mask(void* plan, int R, int C, int rep, const uint8_t* mask, int64_t mask_row_stride,
+size_t sd_plan_batch_desc_bytes(int n) {
+    return n > 0 ? size_t(n) * sizeof(sd::PlanArgs) + 16 : 0;     // descriptors, then the arrival counter
+}
+
+int sd_plan_batch_describe(void* host_desc, void* device_desc, int n, int i, void* plan, int R, int C, int rep_r, int rep_c,
+                           uint64_t seed, uint64_t base_offset, uint64_t* device_counter, float p, uint8_t* mask_out) {
+    if (!host_desc || !device_desc || n <= 0 || i < 0 || i >= n) return sd::fail(SD_ERR_INVALID_ARG, "bad batch descriptor arguments");
+    if (!(p >= 0.0f && p < 1.0f)) return sd::fail(SD_ERR_INVALID_ARG, "Dropout probability must be in [0, 1)");
+    if (!plan || !device_counter) return sd::fail(SD_ERR_INVALID_ARG, "plan or device_counter is null");
+    if (R <= 0 || C <= 0 || rep_r <= 0 || rep_c <= 0) return sd::fail(SD_ERR_INVALID_ARG, "plan grid and block repeat must be positive");
+    if (C > 32 || R > sd::kBitsMaxRows)
+        return sd::fail(SD_ERR_TOO_LARGE, "a batched plan is at most %d x 32 tiles (got %d x %d)", sd::kBitsMaxRows, R, C);
+    sd::PlanArgs a{};
+    a.plan = static_cast<unsigned char*>(plan);
+    a.R = R; a.C = C; a.rep = rep_r; a.rep_c = rep_c;
+    a.from_seed = 1;
+    a.seed = seed; a.offset = base_offset + uint64_t(i); a.p = p;
+    a.counter = reinterpret_cast<unsigned long long*>(device_counter);
+    a.mask_out = mask_out;
+    a.batch_arrivals = reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(device_desc) + size_t(n) * sizeof(sd::PlanArgs));
+    a.batch_n = n;
+    static_cast<sd::PlanArgs*>(host_desc)[i] = a;
+    return SD_OK;
+}
+
+int sd_plan_batch_launch(const void* device_desc, int n, void* stream) {
+    if (!device_desc || n <= 0) return sd::fail(SD_ERR_INVALID_ARG, "bad batch launch arguments");
+    if (reinterpret_cast<uintptr_t>(device_desc) & 7) return sd::fail(SD_ERR_LAYOUT, "descriptors must be 8-byte aligned");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n);
+    cfg.blockDim = dim3(sd::kPlanThreads);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    SD_CUDA_TRY(cudaLaunchKernelEx(&cfg, sd::plan_bits_batch_kernel, static_cast<const sd::PlanArgs*>(device_desc)));
+    return SD_OK;
+}
+
+int sd_plan_from_mask(void* plan, int R, int C, int rep_r, int rep_c, const uint8_t* mask, int64_t mask_row_stride,
                       int64_t mask_col_stride, void* stream) {
     if (!mask) return sd::fail(SD_ERR_INVALID_ARG, "mask is null");
     sd::PlanArgs a{};
     a.plan = static_cast<unsigned char*>(plan);
-    a.R = R; a.C = C; a.rep = rep;
+    a.R = R; a.C = C; a.rep = rep_r; a.rep_c = rep_c;
     a.from_seed = 0;
     a.mask_in = mask;
     a.mask_rs = mask_row_stride; a.mask_cs = mask_col_stride;

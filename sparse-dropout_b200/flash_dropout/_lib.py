@@ -26,6 +26,7 @@ EXPORTS = (
     "sd_gemm_dsd_panels", "sd_gemm_sdd_kept_t_panels", "sd_selftest_bounded_wait", "sd_check_status",
     "sd_conv_fused_supported", "sd_conv_dsd_fwd", "sd_conv_dsd_dw",
     "sd_gemm_dsd_relu", "sd_gemm_dsd_f32", "sd_gemm_sdd_relu_mask",
+    "sd_plan_batch_desc_bytes", "sd_plan_batch_describe", "sd_plan_batch_launch",
 )
 
 
@@ -54,11 +55,17 @@ def lib() -> C.CDLL:
     L.sd_plan_offsets.restype = i32
     L.sd_plan_offsets.argtypes = [i32, i32, C.POINTER(PlanLayout)]
     L.sd_plan_from_seed.restype = i32
-    L.sd_plan_from_seed.argtypes = [vp, i32, i32, i32, u64, u64, f32, vp, vp]
+    L.sd_plan_from_seed.argtypes = [vp, i32, i32, i32, i32, u64, u64, f32, vp, vp]
     L.sd_plan_from_seed_counter.restype = i32
-    L.sd_plan_from_seed_counter.argtypes = [vp, i32, i32, i32, u64, u64, vp, f32, vp, vp]
+    L.sd_plan_from_seed_counter.argtypes = [vp, i32, i32, i32, i32, u64, u64, vp, f32, vp, vp]
+    L.sd_plan_batch_desc_bytes.restype = C.c_size_t
+    L.sd_plan_batch_desc_bytes.argtypes = [i32]
+    L.sd_plan_batch_describe.restype = i32
+    L.sd_plan_batch_describe.argtypes = [vp, vp, i32, i32, vp, i32, i32, i32, i32, u64, u64, vp, f32, vp]
+    L.sd_plan_batch_launch.restype = i32
+    L.sd_plan_batch_launch.argtypes = [vp, i32, vp]
     L.sd_plan_from_mask.restype = i32
-    L.sd_plan_from_mask.argtypes = [vp, i32, i32, i32, vp, i64, i64, vp]
+    L.sd_plan_from_mask.argtypes = [vp, i32, i32, i32, i32, vp, i64, i64, vp]
     mat = [vp, i64, i64]
     L.sd_gemm.restype = i32
     L.sd_gemm.argtypes = mat * 3 + [i32, i32, i32, f32, i32, vp, vp, vp]

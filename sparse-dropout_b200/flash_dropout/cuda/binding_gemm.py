@@ -32,15 +32,20 @@ def _check_operand(x: torch.Tensor, name: str) -> None:
         raise RuntimeError(f"{name} must be row or column major")
 
 
-def _rep(block_size: int) -> int:
+def _rep(block_size) -> tuple[int, int]:
+    """(rows, columns) of 128x128 tiles in one logical dropout block.  ``block_size`` is an int or an ``(m, k)`` pair
+    as the reference's model configs pass (eval/mlp/config.py:23-27); both must be multiples of 128."""
     if isinstance(block_size, (tuple, list)):
-        if len(block_size) != 2 or block_size[0] != block_size[1]:
-            raise ValueError(f"block_size must be an int or an (m, k) pair with equal entries, got {block_size}")
-        block_size = block_size[0]
-    if block_size <= 0 or block_size % TILE:
-        # flash_dropout/cuda/src/matmul_dsd.cuh:92-93
-        raise ValueError(f"block_size must be a positive multiple of {TILE}, got {block_size}")
-    return block_size // TILE
+        if len(block_size) != 2:
+            raise ValueError(f"block_size must be an int or an (m, k) pair, got {block_size}")
+        bm, bk = block_size
+    else:
+        bm = bk = block_size
+    for b in (bm, bk):
+        if b <= 0 or b % TILE:
+            # flash_dropout/cuda/src/matmul_dsd.cuh:92-93
+            raise ValueError(f"block_size must be a positive multiple of {TILE}, got {block_size}")
+    return bm // TILE, bk // TILE
 
 
 class BlockPlan:
@@ -61,12 +66,12 @@ class BlockPlan:
     def from_seed(cls, M: int, K: int, block_size: int, p: float, seed: int, offset: int,
                   device: torch.device) -> "BlockPlan":
         assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
-        rep = _rep(block_size)
+        rr, rc = _rep(block_size)
         plan = cls(ceil(M / TILE), ceil(K / TILE), device)
-        mask = torch.empty((ceil(plan.R / rep), ceil(plan.C / rep)), dtype=torch.bool, device=device)
+        mask = torch.empty((ceil(plan.R / rr), ceil(plan.C / rc)), dtype=torch.bool, device=device)
         with _on_device(device):
             _lib.check(_lib.lib().sd_plan_from_seed(
-                plan.buf.data_ptr(), plan.R, plan.C, rep, seed & (2**64 - 1), offset & (2**64 - 1), float(p),
+                plan.buf.data_ptr(), plan.R, plan.C, rr, rc, seed & (2**64 - 1), offset & (2**64 - 1), float(p),
                 mask.data_ptr(), _lib.stream_ptr(device)))
         plan.mask = mask
         return plan
@@ -76,12 +81,12 @@ class BlockPlan:
                             counter: torch.Tensor, device: torch.device) -> "BlockPlan":
         """Like ``from_seed`` with offset = base_offset + counter[0], read and incremented on the device."""
         assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
-        rep = _rep(block_size)
+        rr, rc = _rep(block_size)
         plan = cls(ceil(M / TILE), ceil(K / TILE), device)
-        mask = torch.empty((ceil(plan.R / rep), ceil(plan.C / rep)), dtype=torch.bool, device=device)
+        mask = torch.empty((ceil(plan.R / rr), ceil(plan.C / rc)), dtype=torch.bool, device=device)
         with _on_device(device):
             _lib.check(_lib.lib().sd_plan_from_seed_counter(
-                plan.buf.data_ptr(), plan.R, plan.C, rep, seed & (2**64 - 1), base_offset & (2**64 - 1),
+                plan.buf.data_ptr(), plan.R, plan.C, rr, rc, seed & (2**64 - 1), base_offset & (2**64 - 1),
                 counter.data_ptr(), float(p), mask.data_ptr(), _lib.stream_ptr(device)))
         plan.mask = mask
         return plan
@@ -90,6 +95,8 @@ class BlockPlan:
     def draw(cls, M: int, K: int, block_size: int, p: float, device: torch.device) -> "BlockPlan":
         """Next mask of the stream ``flash_dropout.random`` describes (host- or device-side counter)."""
         from flash_dropout import random as sd_random
+        if PlanBatch.active is not None:
+            return PlanBatch.active.request(M, K, block_size, p, device)
         counter = sd_random.device_counter(device)
         if counter is not None:
             seed, base = sd_random.seed_and_base()
@@ -103,14 +110,14 @@ class BlockPlan:
             raise RuntimeError("Mask must be bool")
         if not mask.is_cuda or mask.dim() != 2:
             raise RuntimeError("Mask must be a 2D CUDA tensor")
-        rep = _rep(block_size)
+        rr, rc = _rep(block_size)
         plan = cls(ceil(M / TILE), ceil(K / TILE), mask.device)
-        want = (ceil(plan.R / rep), ceil(plan.C / rep))
+        want = (ceil(plan.R / rr), ceil(plan.C / rc))
         if tuple(mask.shape) != want:
             raise RuntimeError(f"mask shape {tuple(mask.shape)} does not match {want} blocks of {block_size}")
         with torch.cuda.device(mask.device):
             _lib.check(_lib.lib().sd_plan_from_mask(
-                plan.buf.data_ptr(), plan.R, plan.C, rep, mask.data_ptr(), mask.stride(0), mask.stride(1),
+                plan.buf.data_ptr(), plan.R, plan.C, rr, rc, mask.data_ptr(), mask.stride(0), mask.stride(1),
                 _lib.stream_ptr(mask.device)))
         plan.mask = mask
         return plan
@@ -141,6 +148,86 @@ class BlockPlan:
     def sdd_items(self): return self._ints(self.layout.sdd_items, 3 * self.R * ((self.C + 1) // 2)).view(-1, 3)
     @property
     def tile_mask(self): return self.buf[self.layout.mask:self.layout.mask + self.R * self.C].view(self.R, self.C)
+
+
+class PlanBatch:
+    """All block plans of one pass over a model from ONE kernel launch.
+
+    A step draws one mask per SparseDrop layer, each a launch of a few microseconds.  A ``PlanBatch`` made the
+    ``PlanBatch.active`` one first records the ``BlockPlan.draw`` calls of a pass (they run as usual); after
+    ``finalize()``, ``launch()`` at the start of every later pass builds all of them side by side in one launch and
+    ``BlockPlan.draw`` hands them out in the recorded order.  The masks are the ones the single launches would draw
+    (plan i uses offset base + counter + i; the launch moves the device counter on by the number of plans).  Needs
+    the device-side counter of ``flash_dropout.random``; plans beyond 3072 x 32 tiles keep their own launch."""
+
+    active: "PlanBatch | None" = None
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.specs: list[tuple] = []
+        self.plans: list[BlockPlan] = []
+        self.batched: list[int] = []          # indices of the plans the batch launch builds
+        self.recording = True
+        self.pos = 0
+        self.desc = None
+
+    def request(self, M: int, K: int, block_size: int, p: float, device: torch.device) -> "BlockPlan":
+        from flash_dropout import random as sd_random
+        spec = (M, K, block_size if isinstance(block_size, int) else tuple(block_size), float(p))
+        if self.recording:
+            PlanBatch.active = None
+            try:
+                plan = BlockPlan.draw(M, K, block_size, p, device)
+            finally:
+                PlanBatch.active = self
+            self.specs.append(spec)
+            self.plans.append(plan)
+            return plan
+        if self.pos >= len(self.plans) or self.specs[self.pos] != spec:
+            raise RuntimeError("the pass asks for different block plans than the recorded one")
+        plan = self.plans[self.pos]
+        if self.pos not in self._batched_set:      # too large for the batch kernel: its own launch, same counter
+            counter = sd_random.device_counter(device)
+            seed, base = sd_random.seed_and_base()
+            with _on_device(device):
+                _lib.check(_lib.lib().sd_plan_from_seed_counter(
+                    plan.buf.data_ptr(), plan.R, plan.C, *_rep(block_size), seed & (2**64 - 1), base & (2**64 - 1),
+                    counter.data_ptr(), float(p), plan.mask.data_ptr(), _lib.stream_ptr(device)))
+        self.pos += 1
+        return plan
+
+    def finalize(self) -> None:
+        """Ends the recording pass: describes the recorded plans to the batch kernel."""
+        from flash_dropout import random as sd_random
+        self.recording = False
+        counter = sd_random.device_counter(self.device)
+        if counter is None:
+            raise RuntimeError("PlanBatch needs flash_dropout.random.enable_device_counter")
+        seed, base = sd_random.seed_and_base()
+        # the batch draws its plans first, at the start of the pass; larger plans follow with single launches
+        self.batched = [i for i, pl in enumerate(self.plans) if pl.C <= 32 and pl.R <= 3072]
+        self._batched_set = set(self.batched)
+        n = len(self.batched)
+        if n == 0:
+            return
+        L = _lib.lib()
+        nbytes = L.sd_plan_batch_desc_bytes(n)
+        host = (C.c_ubyte * nbytes)()
+        self.desc = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        for j, i in enumerate(self.batched):
+            pl = self.plans[i]
+            _lib.check(L.sd_plan_batch_describe(host, self.desc.data_ptr(), n, j, pl.buf.data_ptr(), pl.R, pl.C,
+                                                *_rep(self.specs[i][2]), seed & (2**64 - 1), base & (2**64 - 1),
+                                                counter.data_ptr(), self.specs[i][3], pl.mask.data_ptr()))
+        self.desc.copy_(torch.frombuffer(host, dtype=torch.uint8))
+
+    def launch(self) -> None:
+        """Start of a pass: one launch for every batched plan."""
+        self.pos = 0
+        if self.desc is not None:
+            with _on_device(self.device):
+                _lib.check(_lib.lib().sd_plan_batch_launch(self.desc.data_ptr(), len(self.batched),
+                                                           _lib.stream_ptr(self.device)))
 
 
 _workspaces: dict = {}

@@ -29,9 +29,25 @@ def _operand(x: torch.Tensor) -> torch.Tensor:
 
 
 class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
+    """forward(input, weight, block_size, p, plan, relu, input_relu, grad_premasked, wgrad)
+
+    The first four arguments are the reference's.  The others fuse the layer's elementwise neighbours into the
+    kernels' epilogues (all off by default):
+      relu            the result goes through ReLU in the forward epilogue (eval/mlp/model.py:33-38 applies it as a
+                      separate op after every layer);
+      input_relu      ``input`` is the output of a ReLU: the dX epilogue multiplies by its derivative (input > 0), so
+                      the gradient this layer returns is already the gradient of the ReLU's input;
+      grad_premasked  with ``relu``: the incoming gradient already carries this layer's ReLU derivative (its only
+                      consumer is a layer called with ``input_relu``), so backward does not apply it again;
+      wgrad           ``(fp32 tensor [out, in], accumulate, notify)``: the weight gradient is written (or added) in fp32
+                      straight into that tensor by the dW epilogue instead of being returned to autograd as a 16-bit
+                      tensor that is then cast and accumulated by two more kernels; ``notify()`` is called afterwards.
+    """
+
     @staticmethod
     def forward(ctx, input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
-                plan: BlockPlan | None = None):
+                plan: BlockPlan | None = None, relu: bool = False, input_relu: bool = False,
+                grad_premasked: bool = False, wgrad=None):
         assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
         if not (input.is_cuda and weight.is_cuda):
             # no CPU path: flash_dropout/cuda/src/gemm_binding.cu:19 raises the same way
@@ -44,28 +60,43 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
         if K % 8 or weight.size(0) % 8:
             raise RuntimeError("in_features and out_features must be multiples of 8 (16-byte TMA rows)")
         input, weight = _operand(input), _operand(weight)
+        if input_relu and input.stride(1) != 1:
+            input = input.contiguous()
         if plan is None:
             plan = BlockPlan.draw(M, K, block_size, p, input.device)
-        out = dsd(input, weight, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p))
-        ctx.save_for_backward(input, weight)
+        out = dsd(input, weight, plan, _lib.SD_PLAN_ROWS, 1.0 / (1.0 - p), relu=relu)
+        if relu and not grad_premasked:
+            ctx.save_for_backward(input, weight, out)
+        else:
+            ctx.save_for_backward(input, weight)
         ctx.plan = plan
         ctx.p = p
+        ctx.relu, ctx.input_relu, ctx.grad_premasked, ctx.wgrad = relu, input_relu, grad_premasked, wgrad
         return out
 
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor):
-        input, weight = ctx.saved_tensors
+        input, weight, *rest = ctx.saved_tensors
         plan, scale = ctx.plan, 1.0 / (1.0 - ctx.p)
-        dy = _operand(grad_output.to(input.dtype))
+        dy = grad_output.to(input.dtype)
+        if ctx.relu and not ctx.grad_premasked:
+            dy = torch.ops.aten.threshold_backward(dy, rest[0], 0)       # ReLU derivative, one kernel
+        dy = _operand(dy)
         grad_input = grad_weight = None
         if ctx.needs_input_grad[0]:
             # dx (M, K) = keep o (dy (M, N) . W (N, K)) * scale: B operand is W^T, a column-major view
-            grad_input = sdd(dy, weight.T, plan, scale)
-        if ctx.needs_input_grad[1]:
+            grad_input = sdd(dy, weight.T, plan, scale, relu_mask=input if ctx.input_relu else None)
+        if ctx.wgrad is not None:
+            # dW^T (K, N) in fp32, straight into the caller's gradient buffer
+            target, accumulate, notify = ctx.wgrad
+            dsd(input.T, dy.T, plan, _lib.SD_PLAN_COLS, scale, out=target.T, accumulate=accumulate)
+            if notify is not None:
+                notify()
+        elif ctx.needs_input_grad[1]:
             # dW^T (K, N) = (keep o x)^T (K, M) . dy (M, N) * scale, stored straight into dW (N, K)
             grad_weight = torch.empty_like(weight, memory_format=torch.contiguous_format)
             dsd(input.T, dy.T, plan, _lib.SD_PLAN_COLS, scale, out=grad_weight.T)
-        return grad_input, grad_weight, None, None, None
+        return grad_input, grad_weight, None, None, None, None, None, None, None
 
 
 _last_cast = {"key": None, "src": None, "ref": None}
@@ -95,14 +126,17 @@ def _autocast_input(input: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
 
 
 def blockwise_dropout_matmul(input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
-                             plan: BlockPlan | None = None) -> torch.Tensor:
+                             plan: BlockPlan | None = None, relu: bool = False, input_relu: bool = False,
+                             grad_premasked: bool = False, wgrad=None) -> torch.Tensor:
     """``y = (mask o input) . weight^T / (1 - p)`` with a fresh block mask (or the given plan).
 
     Under CUDA autocast both operands are cast to the autocast dtype (the reference casts to fp16,
-    blockwise_dropout_matmul_cuda.py:9); otherwise they must already be fp16 or bf16.
+    blockwise_dropout_matmul_cuda.py:9); otherwise they must already be fp16 or bf16.  The keyword arguments after
+    ``plan`` fuse elementwise neighbours into the kernels (see ``BlockwiseDropoutMatmulCUDA``).
     """
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
         input, weight = _autocast_input(input, dt), weight.to(dt)
     with torch.autocast("cuda", enabled=False):
-        return BlockwiseDropoutMatmulCUDA.apply(input, weight, block_size, p, plan)
+        return BlockwiseDropoutMatmulCUDA.apply(input, weight, block_size, p, plan, relu, input_relu, grad_premasked,
+                                                wgrad)

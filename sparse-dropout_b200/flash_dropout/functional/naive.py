@@ -16,10 +16,11 @@ def blockwise_dropout_matmul_mask(input: torch.Tensor, mask: torch.Tensor, block
     """``F.linear(keep o input / (1 - p), weight)`` with ``mask`` True = dropped (naive.py:8-25)."""
     assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
     M, K = input.shape
-    if tuple(mask.shape) != (ceil(M / block_size), ceil(K / block_size)):
+    bm, bk = block_size if isinstance(block_size, (tuple, list)) else (block_size, block_size)
+    if tuple(mask.shape) != (ceil(M / bm), ceil(K / bk)):
         raise RuntimeError(f"mask shape {tuple(mask.shape)} does not match input {tuple(input.shape)}")
     keep = (~mask).to(input.dtype) / (1 - p)
-    keep = keep.repeat_interleave(block_size, 0).repeat_interleave(block_size, 1)[:M, :K]
+    keep = keep.repeat_interleave(bm, 0).repeat_interleave(bk, 1)[:M, :K]
     return F.linear(input * keep, weight)
 
 

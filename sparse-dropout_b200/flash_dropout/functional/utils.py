@@ -9,17 +9,19 @@ from flash_dropout import random as sd_random
 
 
 def blockwise_dropout_mask(x: torch.Tensor, block_size: int, p: float) -> torch.Tensor:
-    """Bernoulli(p) drop mask (True = dropped) per ``block_size`` x ``block_size`` block of the last two dims.
+    """Bernoulli(p) drop mask (True = dropped) per ``block_size`` x ``block_size`` block of the last two dims
+    (``block_size`` may also be an ``(m, k)`` pair, the form of eval/mlp/config.py:23-27).
 
     Same shape rule and polarity as flash_dropout/functional/utils.py:11-16.  For a 2-D CUDA tensor the
     mask is drawn on the device by the Philox plan kernel; otherwise by ``torch.rand`` as in the reference.
     """
     *b, m, k = x.shape
-    if x.is_cuda and not b and block_size % 128 == 0:
+    bm, bk = block_size if isinstance(block_size, (tuple, list)) else (block_size, block_size)
+    if x.is_cuda and not b and bm % 128 == 0 and bk % 128 == 0:
         from flash_dropout.cuda.binding_gemm import BlockPlan
         seed, offset = sd_random.next_seed_offset()
         return BlockPlan.from_seed(m, k, block_size, p, seed, offset, x.device).mask
-    shape = (*b, ceil(m / block_size), ceil(k / block_size))
+    shape = (*b, ceil(m / bm), ceil(k / bk))
     return torch.rand(shape, device=x.device) < p
 
 

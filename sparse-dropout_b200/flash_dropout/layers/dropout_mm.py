@@ -11,14 +11,15 @@ import flash_dropout.functional as F
 VARIANTS = ("none", "vanilla", "blockwise[naive]", "blockwise[triton]", "blockwise[cuda]")
 
 
-def _block_size(kwargs: dict) -> int:
-    """``block_size`` keyword as an int; an (m, k) pair with equal entries is accepted because the
-    reference's model configs pass ``(128, 128)`` (eval/mlp/config.py:23-27)."""
+def _block_size(kwargs: dict):
+    """``block_size`` keyword: an int, or an ``(m, k)`` pair as the reference's model configs pass
+    (eval/mlp/config.py:23-27) — m rows by k columns of the layer's input per dropout decision.  A pair with equal
+    entries is returned as an int."""
     bs = kwargs["block_size"]
     if isinstance(bs, (tuple, list)):
-        if len(bs) != 2 or bs[0] != bs[1]:
-            raise ValueError(f"block_size pair must have equal entries, got {bs}")
-        bs = bs[0]
+        if len(bs) != 2 or int(bs[0]) <= 0 or int(bs[1]) <= 0:
+            raise ValueError(f"block_size must be an int or an (m, k) pair of positive ints, got {bs}")
+        return int(bs[0]) if bs[0] == bs[1] else (int(bs[0]), int(bs[1]))
     return int(bs)
 
 
@@ -42,7 +43,27 @@ class DropoutMM(nn.Module):
     def extra_repr(self) -> str:
         return f"{self.in_features}, {self.out_features}, p={self.p}, variant={self.variant!r}"
 
-    def forward(self, input: torch.Tensor) -> torch.Tensor:
+    def forward(self, input: torch.Tensor, activation: str | None = None, input_relu: bool = False,
+                grad_premasked: bool = False) -> torch.Tensor:
+        """``activation="relu"`` applies ReLU to the result.  On the CUDA variant it is fused into the forward kernel,
+        ``input_relu`` (the input is a ReLU's output) fuses that ReLU's derivative into the dX kernel, and
+        ``grad_premasked`` says the consumer of this layer's output does the same for this layer's ReLU; the other
+        variants apply a plain ReLU and ignore the two hints.  With no arguments: the reference's forward."""
+        if activation not in (None, "relu"):
+            raise ValueError(f"Unknown activation {activation}")
+        v = self.variant
+        if self.training and v in ("blockwise[cuda]", "blockwise[triton]"):
+            lead = input.shape[:-1]
+            x = input.reshape(-1, input.shape[-1])
+            wgrad = getattr(self.weight, "_sd_wgrad", None) if torch.is_grad_enabled() else None
+            out = F.cuda_blockwise_dropout_matmul(x, self.weight, _block_size(self.kwargs), self.p,
+                                                  relu=activation == "relu", input_relu=input_relu,
+                                                  grad_premasked=grad_premasked and activation == "relu", wgrad=wgrad)
+            return out.reshape(*lead, self.out_features)
+        out = self._forward_plain(input)
+        return torch.relu(out) if activation == "relu" else out
+
+    def _forward_plain(self, input: torch.Tensor) -> torch.Tensor:
         if not self.training:
             return nn.functional.linear(input, self.weight)
         lead = input.shape[:-1]

@@ -23,7 +23,7 @@ from flash_dropout import random as sd_random
 
 class FlatGradDataParallel:
     def __init__(self, module: torch.nn.Module, process_group=None, bucket_bytes: int = 16 << 20,
-                 broadcast_from: int | None = 0):
+                 broadcast_from: int | None = 0, fuse_wgrad: bool = False):
         self.module = module
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -75,6 +75,8 @@ class FlatGradDataParallel:
                     dist.broadcast(b.data, src=broadcast_from, group=self.group)
             for p in self.params:
                 p.register_post_accumulate_grad_hook(self._on_grad_ready)
+        if fuse_wgrad:
+            self._fuse_weight_gradients()
         sd_random.set_subsequence(self.rank)     # every rank draws its own masks from the shared seed
 
     # ------------------------------------------------------------------
@@ -97,6 +99,20 @@ class FlatGradDataParallel:
             except Exception:                           # noqa: BLE001 - any failure means: not available here
                 pass
         return torch.zeros(total, dtype=dtype, device=dev)
+
+    def _fuse_weight_gradients(self) -> None:
+        """Lets the dW kernel of every DropoutMM layer on the CUDA variant write its fp32 result straight into the
+        layer's slice of the flat buffer (overwriting: the step zeroes the buffer and runs one backward), instead of
+        returning a 16-bit gradient that autograd casts and accumulates with two more kernels per layer.  Autograd
+        then never sees a gradient for these weights, so the bucket bookkeeping is notified from the layer's backward.
+        Only for steps that run exactly one backward between ``zero_grad`` calls, without weight sharing."""
+        from flash_dropout.layers import DropoutMM
+        for m in self.module.modules():
+            if isinstance(m, DropoutMM) and m.variant in ("blockwise[cuda]", "blockwise[triton]"):
+                p = m.weight
+                if p in self._slices and p.dtype == torch.float32 and p.is_cuda:
+                    notify = (lambda p=p: self._on_grad_ready(p)) if self.world > 1 else None
+                    p._sd_wgrad = (p.grad, False, notify)
 
     defer_allreduce = False     # hooks stay quiet: the caller reduces the whole flat buffer itself
 
@@ -192,7 +208,8 @@ class GraphedTrainStep:
     """
 
     def __init__(self, model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torch.optim.Optimizer, loss_fn,
-                 inputs: tuple, autocast_dtype: torch.dtype | None = None, warmup: int = 3, whole_step: bool = True):
+                 inputs: tuple, autocast_dtype: torch.dtype | None = None, warmup: int = 3, whole_step: bool = True,
+                 batch_plans: bool = True):
         self.model, self.dp, self.optimizer = model, dp, optimizer
         self.inputs = inputs
         dev = dp.flat_grad.device
@@ -203,18 +220,32 @@ class GraphedTrainStep:
         self.whole_step = whole_step and self._make_capturable(optimizer)
         dp.defer_allreduce = not self.whole_step        # outside the graph: one flat all-reduce after the replay
 
+        from flash_dropout.cuda.binding_gemm import PlanBatch
+        self.plan_batch = PlanBatch(dev) if batch_plans else None
+
         def fwd_bwd():
             dp.zero_grad()
-            if autocast_dtype is not None:
-                with torch.autocast("cuda", dtype=autocast_dtype):
-                    loss = loss_fn(model, *inputs)
-            else:
-                loss = loss_fn(model, *inputs)
+            if self.plan_batch is not None:
+                PlanBatch.active = self.plan_batch
+                if not self.plan_batch.recording:
+                    self.plan_batch.launch()           # every layer's mask of this step, one launch
+            try:
+                loss = fwd_loss()
+            finally:
+                PlanBatch.active = None
+            if self.plan_batch is not None and self.plan_batch.recording:
+                self.plan_batch.finalize()
             loss.backward()
             if self.whole_step:
                 dp.finish()
                 optimizer.step()
             return loss.detach()
+
+        def fwd_loss():
+            if autocast_dtype is not None:
+                with torch.autocast("cuda", dtype=autocast_dtype):
+                    return loss_fn(model, *inputs)
+            return loss_fn(model, *inputs)
 
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))

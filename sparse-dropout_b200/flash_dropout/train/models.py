@@ -35,10 +35,12 @@ class BasicNet(nn.Module):
         self.act = nn.ReLU()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = self.act(self.in_proj(x.flatten(1)))
+        # Every ReLU sits between two DropoutMM layers and feeds only the next one, so on the CUDA variant it is fused:
+        # forward into the producing layer's epilogue, its derivative into the consuming layer's dX epilogue.
+        x = self.in_proj(x.flatten(1), activation="relu", grad_premasked=True)
         for layer in self.layers:
-            x = self.act(layer(x))
-        return self.out_proj(x)[..., : self.output_dim]
+            x = layer(x, activation="relu", input_relu=True, grad_premasked=True)
+        return self.out_proj(x, input_relu=True)[..., : self.output_dim]
 
 
 class CausalSelfAttention(nn.Module):

@@ -46,10 +46,10 @@ def test_argument_validation_without_a_gpu(built_lib):
     SD_ERR_INVALID_ARG, SD_ERR_LAYOUT = -1, -2
     buf = C.create_string_buffer(1 << 16)
     # p outside [0, 1): the reference asserts this in Python (blockwise_dropout_matmul_cuda.py:17)
-    assert built_lib.sd_plan_from_seed(buf, 4, 4, 1, 0, 0, 1.0, None, None) == SD_ERR_INVALID_ARG
+    assert built_lib.sd_plan_from_seed(buf, 4, 4, 1, 1, 0, 0, 1.0, None, None) == SD_ERR_INVALID_ARG
     assert b"[0, 1)" in built_lib.sd_last_error()
-    assert built_lib.sd_plan_from_seed(buf, 4, 4, 1, 0, 0, -0.1, None, None) == SD_ERR_INVALID_ARG
-    assert built_lib.sd_plan_from_mask(buf, 4, 4, 1, None, 4, 1, None) == SD_ERR_INVALID_ARG
+    assert built_lib.sd_plan_from_seed(buf, 4, 4, 1, 1, 0, 0, -0.1, None, None) == SD_ERR_INVALID_ARG
+    assert built_lib.sd_plan_from_mask(buf, 4, 4, 1, 1, None, 4, 1, None) == SD_ERR_INVALID_ARG
     # GEMM entry points reject bad sizes / dtypes / layouts before touching the device
     a = C.cast(buf, C.c_void_p)
     assert built_lib.sd_gemm(a, 128, 1, a, 128, 1, a, 128, 1, 0, 128, 128, 1.0, 0, None, None, None) == SD_ERR_INVALID_ARG

@@ -344,3 +344,28 @@ def test_fused_epilogues_against_oracle(built_lib, M, N, K, p, dtype):
     dW2 = torch.zeros((N, K), device=DEV, dtype=torch.float32)
     bg.dsd(A.T, dC.T, plan, _lib.SD_PLAN_COLS, s, out=dW2.T, ws=None)      # whole tiles, no workspace
     torch.testing.assert_close(dW2.cpu(), dw_ref, **tol32)
+
+
+@pytest.mark.parametrize("bs", [(128, 384), (256, 128), (512, 256)])
+def test_rectangular_block_sizes(built_lib, bs):
+    """block_size given as an (m, k) pair with m != k (eval/mlp/config.py:23-27 passes pairs): mask drawn on the
+    device bit-exact vs the oracle, and the three products of the layer against the masked-dense oracle."""
+    import flash_dropout.functional as F
+    from flash_dropout import random as sd_random
+    from flash_dropout.cuda.binding_gemm import BlockPlan
+    M, N, K, p = 1024, 384, 1152, 0.5
+    x, w, dy = _inputs(M, N, K, seed=51)
+    sd_random.manual_seed(61, subsequence=0)
+    plan = BlockPlan.draw(M, K, bs, p, DEV)
+    mask_np = pm.block_mask(M, K, bs, p, seed=61, offset=0)
+    assert np.array_equal(plan.mask.cpu().numpy(), mask_np)
+    assert np.array_equal(plan.tile_mask.cpu().numpy().astype(bool), pm.expand_to_tiles(mask_np, M, K, bs))
+    sd_random.manual_seed(61, subsequence=0)
+    xa, wa = x.to(DEV).requires_grad_(), w.to(DEV).requires_grad_()
+    y = F.cuda_blockwise_dropout_matmul(xa, wa, bs, p)
+    y.backward(dy.to(DEV))
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, bs, p, w, dy)
+    _close(y, y_ref, "y")
+    _close(xa.grad, dx_ref, "dx")
+    _close(wa.grad, dw_ref, "dw")
+    sd_random.follow_torch_seed()

@@ -160,3 +160,41 @@ def test_graphed_train_step_draws_fresh_masks(built_lib):
     assert final < 2.30
     sd_random.disable_device_counter()
     sd_random.follow_torch_seed()
+
+
+def test_fused_mlp_matches_unfused_composition(built_lib):
+    """BasicNet on the CUDA variant fuses every ReLU into the neighbouring kernels and (under the data-parallel wrapper
+    with fuse_wgrad) writes fp32 weight gradients straight into the flat buffer.  Same masks, same inputs: loss and
+    all gradients must equal those of the plain composition (separate ReLU ops, autograd-accumulated gradients)."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.train import BasicNet, FlatGradDataParallel
+    torch.manual_seed(0)
+    drop = dict(p=0.5, variant="blockwise[cuda]", block_size=(128, 128))
+    fused = BasicNet(784, 2, 512, 10, drop).to(DEV)
+    plain = BasicNet(784, 2, 512, 10, drop).to(DEV)
+    plain.load_state_dict(fused.state_dict())
+    x, y = torch.rand(256, 28, 28, device=DEV), torch.randint(0, 10, (256,), device=DEV)
+
+    def plain_forward(m, inp):                                # the reference's forward, op by op
+        h = torch.relu(m.in_proj(inp.flatten(1)))
+        for layer in m.layers:
+            h = torch.relu(layer(h))
+        return m.out_proj(h)[..., : m.output_dim]
+
+    dp = FlatGradDataParallel(fused, fuse_wgrad=True)
+    assert all(hasattr(m.weight, "_sd_wgrad") for m in (fused.in_proj, fused.out_proj, *fused.layers))
+    losses = []
+    for model, fwd in ((fused, lambda m, a: m(a)), (plain, plain_forward)):
+        sd_random.manual_seed(21, subsequence=0)              # both draw the same four masks
+        if model is fused:
+            dp.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = torch.nn.functional.cross_entropy(fwd(model, x).float(), y)
+        loss.backward()
+        losses.append(loss.item())
+    assert abs(losses[0] - losses[1]) < 1e-3
+    assert dp.grads_are_views()
+    for (n, a), (_, b) in zip(fused.named_parameters(), plain.named_parameters()):
+        # identical products; the fused path rounds dW once less (fp32 store instead of bf16), hence a loose bound
+        torch.testing.assert_close(a.grad, b.grad, rtol=2e-2, atol=2e-3, msg=lambda m, n=n: f"{n}: {m}")
+    sd_random.follow_torch_seed()

@@ -116,3 +116,43 @@ def test_device_counter_supplies_the_offset(built_lib):
         torch.cuda.synchronize()
         assert counter.item() == 6 + i
         assert np.array_equal(plan.mask.cpu().numpy(), pm.block_mask(1024, 2048, 128, 0.5, 77, base + 5 + i))
+
+
+def test_plan_batch_equals_single_launches(built_lib):
+    """One launch for several plans: masks and every list are what the single launches give, pass after pass."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.cuda.binding_gemm import BlockPlan, PlanBatch
+    dev = torch.device("cuda:0")
+    shapes = [(512, 784, 128, 0.5), (512, 1024, 128, 0.5), (16384, 384, 128, 0.2), (16384, 1536, 256, 0.2), (300, 136, 128, 0.9)]
+    sd_random.manual_seed(91, subsequence=2)
+    sd_random.enable_device_counter(dev)
+    counter = sd_random.device_counter(dev)
+    seed, base = sd_random.seed_and_base()
+    batch = PlanBatch(dev)
+    drawn = 0
+    try:
+        for step in range(3):
+            PlanBatch.active = batch
+            if not batch.recording:
+                batch.launch()
+            plans = [BlockPlan.draw(M, K, bs, p, dev) for M, K, bs, p in shapes]
+            PlanBatch.active = None
+            if batch.recording:
+                batch.finalize()
+            torch.cuda.synchronize()
+            for i, ((M, K, bs, p), plan) in enumerate(zip(shapes, plans)):
+                want = pm.block_mask(M, K, bs, p, seed, base + drawn + i)
+                assert np.array_equal(plan.mask.cpu().numpy(), want), (step, i)
+                ref = BlockPlan.from_mask(torch.from_numpy(want).to(dev), M, K, bs)
+                nnz, n_items, n_drop = (int(v) for v in ref.header[:3].tolist())
+                assert torch.equal(plan.header[:7], ref.header[:7]), (step, i)
+                for name, n in (("row_ptr", None), ("col_ptr", None), ("col_idx", nnz), ("row_idx", nnz),
+                                ("kept_pairs", nnz), ("drop_pairs", n_drop), ("sdd_items", n_items), ("row_order", None),
+                                ("col_order", None), ("tile_mask", None)):
+                    assert torch.equal(getattr(plan, name)[:n], getattr(ref, name)[:n]), (step, i, name)
+            drawn += len(shapes)
+            assert counter.item() == drawn
+    finally:
+        PlanBatch.active = None
+        sd_random.disable_device_counter()
+        sd_random.follow_torch_seed()

@@ -75,8 +75,10 @@ def test_dropout_mm_variants_on_cpu():
         torch.testing.assert_close(m(x), torch.nn.functional.linear(x, m.weight))
     with pytest.raises(ValueError):
         DropoutMM(256, 128, variant="bogus")(x)
+    rect = DropoutMM(256, 128, p=0.5, variant="blockwise[naive]", block_size=(64, 128))   # an (m, k) pair, m != k
+    assert tuple(rect(x).shape) == (4, 32, 128)
     with pytest.raises(ValueError):
-        DropoutMM(256, 128, variant="blockwise[naive]", block_size=(128, 64))(x)
+        DropoutMM(256, 128, variant="blockwise[naive]", block_size=(128, 64, 1))(x)
     none = DropoutMM(256, 128, p=0.9, variant="none")
     torch.testing.assert_close(none(x), torch.nn.functional.linear(x, none.weight))
 
