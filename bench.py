@@ -644,7 +644,7 @@ def measure_train(workload: str, variant: str, dev, world: int, rank: int, steps
         host_y = host_x
         name = "char-GPT 6 layers d=384 6 heads ctx 256 vocab 65, bf16 autocast, batch 64/GPU, p=0.2, AdamW"
         loss_of = lambda m, x, y: m(x)[1]
-    dp = FlatGradDataParallel(model, bucket_bytes=4 << 20, fuse_wgrad=True)
+    dp = FlatGradDataParallel(model, bucket_bytes=int(os.environ.get("SD_DP_BUCKET_MB", "16")) << 20, fuse_wgrad=True)
     sd_random.manual_seed(SEED, subsequence=rank)
     x_dev, y_dev = host_x.to(dev), host_y.to(dev)
 
