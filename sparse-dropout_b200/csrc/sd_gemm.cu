@@ -791,8 +791,15 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             constexpr uint64_t B_HI = B_MN ? make_smem_desc_hi(MN_ATOM_BYTES, 1024) : make_smem_desc_hi(16, 1024);
             constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32;   // bytes per 16-wide K step
             constexpr uint32_t B_KSTEP = B_MN ? 2048 : 32;
+            // This one thread feeds the tensor pipe, and every instruction it executes between two tcgen05.mma is time
+            // the pipe may sit idle (a lone thread issues a dependent instruction only every few cycles).  So the loop
+            // is kept as short as it can be: a descriptor is (high word: constant, low word: LBO | address >> 4), and
+            // moving to the next K step or ring slot is one add on the low word.
+            constexpr uint32_t A_HI32 = uint32_t(A_HI >> 32), B_HI32 = uint32_t(B_HI >> 32);
+            const uint32_t a_lo0 = uint32_t(A_HI) + (tiles >> 4), b_lo0 = uint32_t(B_HI) + ((tiles + A_BYTES) >> 4);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;             // descriptors of ring slot `stage`
             bool ok = true;
             WorkIter it;
             it.init(g, cta, n_ctas, tab);
@@ -807,19 +814,20 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 kit.init(w);
                 int kb;
                 while (ok && kit.next(kb)) {
-                    for (int h = 0; h < 2; ++h) {
-                        if (kb * 128 + h * BK >= g.KK) break;
+                    const int halves = kb * 128 + BK < g.KK ? 2 : 1;         // the last K tile may be only 64 wide
+                    for (int h = 0; h < halves; ++h) {
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
                         tc_fence_after();
-                        const uint32_t sA = tiles + stage * STAGE_BYTES, sB = sA + A_BYTES;
 #pragma unroll
                         for (int j = 0; j < BK / 16; ++j) {
-                            umma_f16(d, make_smem_desc(sA + j * A_KSTEP, A_HI), make_smem_desc(sB + j * B_KSTEP, B_HI),
-                                     idesc, accumulate);
-                            accumulate = 1;
+                            umma_f16_lohi(d, a_lo + j * (A_KSTEP >> 4), A_HI32, b_lo + j * (B_KSTEP >> 4), B_HI32, idesc,
+                                          j == 0 ? accumulate : 1u);
                         }
+                        accumulate = 1;
                         umma_commit(bar_empty + 8 * stage);
-                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                        a_lo += STAGE_BYTES >> 4;
+                        b_lo += STAGE_BYTES >> 4;
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
                     }
                 }
                 if (!ok) break;

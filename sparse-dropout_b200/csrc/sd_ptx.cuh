@@ -71,9 +71,10 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // never spins forever: every role leaves its loop and the CTA runs its normal teardown.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s; a whole launch is far below this
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The polling loop of mbar_wait, kept out of line: the callers' hot loops stay compact and only ever execute the
+// one try_wait of the fast path.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                            int code, uint64_t limit_ns) {
     uint64_t t0 = 0;
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -88,6 +89,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             }
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code, limit_ns);
 }
 
 // Bounded wait until a counter in global memory that another CTA increments reaches `target`.
@@ -201,6 +208,20 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
         :
         : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same with each 64-bit shared-memory descriptor given as its two 32-bit halves: the issuing thread then advances
+// a descriptor from stage to stage and K step to K step with one 32-bit add on the low half (the address field).
+__device__ __forceinline__ void umma_f16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}\n"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.

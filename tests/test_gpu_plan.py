@@ -147,9 +147,14 @@ def test_plan_batch_equals_single_launches(built_lib):
                 nnz, n_items, n_drop = (int(v) for v in ref.header[:3].tolist())
                 assert torch.equal(plan.header[:7], ref.header[:7]), (step, i)
                 for name, n in (("row_ptr", None), ("col_ptr", None), ("col_idx", nnz), ("row_idx", nnz),
-                                ("kept_pairs", nnz), ("drop_pairs", n_drop), ("sdd_items", n_items), ("row_order", None),
-                                ("col_order", None), ("tile_mask", None)):
+                                ("kept_pairs", nnz), ("drop_pairs", n_drop), ("sdd_items", n_items), ("tile_mask", None)):
                     assert torch.equal(getattr(plan, name)[:n], getattr(ref, name)[:n]), (step, i, name)
+                # the heaviest-first orders are permutations sorted by kept count (ties in any order)
+                keep = (plan.tile_mask == 0)
+                for order, counts in ((plan.row_order, keep.sum(1)), (plan.col_order, keep.sum(0))):
+                    o = order.long()
+                    assert torch.equal(torch.sort(o).values, torch.arange(o.numel(), device=dev)), (step, i)
+                    assert (counts[o][:-1] >= counts[o][1:]).all(), (step, i)
             drawn += len(shapes)
             assert counter.item() == drawn
     finally:
