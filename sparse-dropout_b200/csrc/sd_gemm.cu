@@ -70,7 +70,7 @@ constexpr int STAGING_BYTES = 8 * 4096;                  // TMA-store staging
 // Tile table: a CTA that runs several whole-tile passes resolves all of them once, in its prologue, into shared
 // memory (row block, column tile, keep bits of the row block's K tiles), so that no role pays the chain of
 // dependent index loads (order -> list bounds -> list entries) again for every tile.
-constexpr int TAB_MAX = 96;
+constexpr int TAB_MAX = 96, TAB_MIN = 8;
 constexpr int TAB_BYTES = TAB_MAX * 16;
 constexpr int GEMM_SMEM = TILE_SMEM + 1024 /*align*/ + 256 /*barriers*/ + STAGING_BYTES + TAB_BYTES;
 static_assert(GEMM_SMEM <= 227 * 1024, "over the shared memory of one CTA");
@@ -272,7 +272,9 @@ struct WorkIter {
         }
         n_entries = whole_entries + 2 * (n_tiles - whole_entries);
         passes = (n_entries + n_ctas - 1) / n_ctas;
-        if (g.use_table && !split && passes >= 2 && passes <= TAB_MAX) tab = table;
+        // the table costs a CTA-wide barrier and one chain of index loads up front: worth it from a handful of tiles per
+        // CTA on (the short tiles of a conv), not for the three or four long tiles of a large square product
+        if (g.use_table && !split && passes >= TAB_MIN && passes <= TAB_MAX) tab = table;
         if (!split || n_tiles == 0 || n_tiles > n_ctas) return;
         const int row_weight = 2 * g.n_col_tiles - (ragged ? 1 : 0);
         const unsigned total = work_before(g, n_tiles, row_weight);
@@ -791,15 +793,8 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
             constexpr uint64_t B_HI = B_MN ? make_smem_desc_hi(MN_ATOM_BYTES, 1024) : make_smem_desc_hi(16, 1024);
             constexpr uint32_t A_KSTEP = A_MN ? 2048 : 32;   // bytes per 16-wide K step
             constexpr uint32_t B_KSTEP = B_MN ? 2048 : 32;
-            // This one thread feeds the tensor pipe, and every instruction it executes between two tcgen05.mma is time
-            // the pipe may sit idle (a lone thread issues a dependent instruction only every few cycles).  So the loop
-            // is kept as short as it can be: a descriptor is (high word: constant, low word: LBO | address >> 4), and
-            // moving to the next K step or ring slot is one add on the low word.
-            constexpr uint32_t A_HI32 = uint32_t(A_HI >> 32), B_HI32 = uint32_t(B_HI >> 32);
-            const uint32_t a_lo0 = uint32_t(A_HI) + (tiles >> 4), b_lo0 = uint32_t(B_HI) + ((tiles + A_BYTES) >> 4);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
-            uint32_t a_lo = a_lo0, b_lo = b_lo0;             // descriptors of ring slot `stage`
             bool ok = true;
             WorkIter it;
             it.init(g, cta, n_ctas, tab);
@@ -814,20 +809,19 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 kit.init(w);
                 int kb;
                 while (ok && kit.next(kb)) {
-                    const int halves = kb * 128 + BK < g.KK ? 2 : 1;         // the last K tile may be only 64 wide
-                    for (int h = 0; h < halves; ++h) {
+                    for (int h = 0; h < 2; ++h) {
+                        if (kb * 128 + h * BK >= g.KK) break;
                         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, g.status, ST_MMA_FULL)) { ok = false; break; }
                         tc_fence_after();
+                        const uint32_t sA = tiles + stage * STAGE_BYTES, sB = sA + A_BYTES;
 #pragma unroll
                         for (int j = 0; j < BK / 16; ++j) {
-                            umma_f16_lohi(d, a_lo + j * (A_KSTEP >> 4), A_HI32, b_lo + j * (B_KSTEP >> 4), B_HI32, idesc,
-                                          j == 0 ? accumulate : 1u);
+                            umma_f16(d, make_smem_desc(sA + j * A_KSTEP, A_HI), make_smem_desc(sB + j * B_KSTEP, B_HI),
+                                     idesc, accumulate);
+                            accumulate = 1;
                         }
-                        accumulate = 1;
                         umma_commit(bar_empty + 8 * stage);
-                        a_lo += STAGE_BYTES >> 4;
-                        b_lo += STAGE_BYTES >> 4;
-                        if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
+                        if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
                 }
                 if (!ok) break;
@@ -1438,7 +1432,9 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         grid = int(tiles_upper);
     }
     // Whole-tile launches describe their tiles once per CTA in shared memory when a tile's kept K tiles fit a 32-bit mask
-    g.use_table = !g.split && (mode != MODE_DSD || k_tiles <= 32);
+    // (and only when a CTA gets enough tiles for the table to pay: see TAB_MIN; the bound below counts every tile
+    // that may exist, the kernel checks the tiles that do)
+    g.use_table = !g.split && (mode != MODE_DSD || k_tiles <= 32) && tiles_upper >= (long long)TAB_MIN * grid / 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Row-major result with 16-byte rows: written by TMA (clipped at the ragged edge); otherwise by the warps.
     CUtensorMap tc = ta;

@@ -71,10 +71,9 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // never spins forever: every role leaves its loop and the CTA runs its normal teardown.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s; a whole launch is far below this
 
-// The polling loop of mbar_wait, kept out of line: the callers' hot loops stay compact and only ever execute the
-// one try_wait of the fast path.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                            int code, uint64_t limit_ns) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -89,12 +88,6 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
             }
         }
     }
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, code, limit_ns);
 }
 
 // Bounded wait until a counter in global memory that another CTA increments reaches `target`.
