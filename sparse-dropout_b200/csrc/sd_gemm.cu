@@ -1099,6 +1099,25 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                         }
                         ++n_stores;
                     }
+                } else if (g.tma_store == 3) {
+                    // fp32 column-major result (a weight gradient written into the fp32 gradient buffer): one chunk =
+                    // 32 columns of 32 rows = 4 KiB, staged as [column][row] (128-byte rows of the transpose,
+                    // CU_TENSOR_MAP_SWIZZLE_128B) and stored by one TMA store
+                    const uint32_t buf = stage_base + (two_bufs ? ((n_stores & 1) << 12) : 0);
+                    wait_staging_free(two_bufs, n_stores, lane);
+                    const uint32_t piece = uint32_t(lane) >> 2, within = (uint32_t(lane) & 3u) << 2;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t addr = buf + j * 128 + ((piece ^ (uint32_t(j) & 7u)) << 4) + within;
+                        asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "f"(__uint_as_float(r[j]) * g.scale) : "memory");
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tmapC, buf, w.a_row + quad * 32, col);
+                        bulk_commit();
+                    }
+                    ++n_stores;
                 } else if (g.out_f32) {
                     store_chunk_f32(g, row, col, r);
                 } else {
@@ -1439,7 +1458,20 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     // Row-major result with 16-byte rows: written by TMA (clipped at the ragged edge); otherwise by the warps.
     CUtensorMap tc = ta;
     if (g.out_f32) {
-        // fp32 results are written by the epilogue warps directly
+        // an fp32 result that overwrites a column-major matrix with 16-byte aligned columns leaves by TMA; other
+        // fp32 results (row-major, accumulating, unaligned) are written by the epilogue warps directly
+        if (!g.out_acc && c_rs == 1 && (c_cs & 3) == 0 && c_cs >= M && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+            EncodeTiledFn enc = encode_tiled_fn();
+            cuuint64_t dims[2] = {cuuint64_t(M), cuuint64_t(N)};            // the transpose, row-major [N][M]
+            cuuint64_t strides[1] = {cuuint64_t(N > 1 ? c_cs * 4 : ((int64_t(M) * 4 + 15) & ~int64_t(15)))};
+            cuuint32_t box[2] = {32u, 32u};
+            cuuint32_t estr[2] = {1u, 1u};
+            CUresult r = enc(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C, dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(SD_ERR_CUDA, "cuTensorMapEncodeTiled(fp32 C^T) failed with CUresult %d", int(r));
+            g.tma_store = 3;
+        }
     } else if (c_panel_kg) {
         EncodeTiledFn enc = encode_tiled_fn();
         const long long all_rows = (long long)((N + 127) / 128) * c_panel_kg;
