@@ -986,11 +986,23 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                 zero_tile(g, vec_ok, vec_t_ok, etid, __ldg(g.zero_pairs + 2 * z) * 128, __ldg(g.zero_pairs + 2 * z + 1) * 128);
         } else if (g.mode == MODE_DSD) {
             // row blocks with nothing kept: their 128x128 output tiles are spread over all CTAs
-            const int ncol = (g.NN + 127) >> 7;
-            for (int z = epi_halves * cta + half; z < g.n_row_blocks * ncol; z += epi_halves * n_ctas) {
-                const int rb = z / ncol;
-                if (__ldg(g.list_ptr + rb + 1) == __ldg(g.list_ptr + rb))
-                    zero_tile(g, vec_ok, vec_t_ok, etid, rb * 128, (z - rb * ncol) * 128);
+            // Every warp of the group tests the same 32 candidates at a time, one per lane, so the index loads of a
+            // whole batch are in flight together; the ballot then gives all of them the same list of tiles to zero.
+            const int ncol = (g.NN + 127) >> 7, total = g.n_row_blocks * ncol;
+            const int z0 = epi_halves * cta + half, zstep = epi_halves * n_ctas;
+            for (int zb = z0; zb < total; zb += 32 * zstep) {
+                const int z = zb + lane * zstep;
+                bool empty = false;
+                if (z < total) {
+                    const int rb = z / ncol;
+                    empty = __ldg(g.list_ptr + rb + 1) == __ldg(g.list_ptr + rb);
+                }
+                unsigned found = __ballot_sync(0xffffffffu, empty);
+                while (found) {
+                    const int zz = zb + (__ffs(found) - 1) * zstep, rb = zz / ncol;
+                    found &= found - 1;
+                    zero_tile(g, vec_ok, vec_t_ok, etid, rb * 128, (zz - rb * ncol) * 128);
+                }
             }
         }
         WorkIter it;
