@@ -5,8 +5,6 @@ from math import ceil
 
 import torch
 
-from flash_dropout import random as sd_random
-
 
 def blockwise_dropout_mask(x: torch.Tensor, block_size: int, p: float) -> torch.Tensor:
     """Bernoulli(p) drop mask (True = dropped) per ``block_size`` x ``block_size`` block of the last two dims
@@ -19,8 +17,8 @@ def blockwise_dropout_mask(x: torch.Tensor, block_size: int, p: float) -> torch.
     bm, bk = block_size if isinstance(block_size, (tuple, list)) else (block_size, block_size)
     if x.is_cuda and not b and bm % 128 == 0 and bk % 128 == 0:
         from flash_dropout.cuda.binding_gemm import BlockPlan
-        seed, offset = sd_random.next_seed_offset()
-        return BlockPlan.from_seed(m, k, block_size, p, seed, offset, x.device).mask
+        # the next mask of the stream (host- or device-side counter, so that a captured step draws afresh on replay)
+        return BlockPlan.draw(m, k, block_size, p, x.device).mask
     shape = (*b, ceil(m / bm), ceil(k / bk))
     return torch.rand(shape, device=x.device) < p
 

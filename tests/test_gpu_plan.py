@@ -161,3 +161,33 @@ def test_plan_batch_equals_single_launches(built_lib):
         PlanBatch.active = None
         sd_random.disable_device_counter()
         sd_random.follow_torch_seed()
+
+
+def test_functional_mask_is_fresh_on_graph_replay(built_lib):
+    """``blockwise_dropout_mask`` inside a captured region reads the device-side counter: every replay of the graph
+    draws the next mask of the stream, not the one seen at capture."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.functional.utils import blockwise_dropout_mask
+    dev = torch.device("cuda:0")
+    sd_random.manual_seed(5, subsequence=1)
+    sd_random.enable_device_counter(dev)
+    seed, base = sd_random.seed_and_base()
+    try:
+        x = torch.empty(1024, 2048, device=dev, dtype=torch.float16)
+        out = torch.empty(8, 16, dtype=torch.bool, device=dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            out.copy_(blockwise_dropout_mask(x, 128, 0.5))                   # offset base + 0
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out.copy_(blockwise_dropout_mask(x, 128, 0.5))
+        for i in range(3):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(out.cpu().numpy(), pm.block_mask(1024, 2048, 128, 0.5, seed, base + 1 + i)), i
+    finally:
+        sd_random.disable_device_counter()
+        sd_random.follow_torch_seed()
