@@ -1,10 +1,12 @@
-"""The two models the reference trains with DropoutMM, restated (architecture, parameter names and
+"""The models the reference trains with DropoutMM, restated (architecture, parameter names and
 initialisation follow the reference so checkpoints stay interchangeable):
 
   BasicNet — eval/mlp/model.py:8-40: in_proj, `num_layers` hidden DropoutMM layers, out_proj whose width is
              padded to a multiple of 128 and sliced back, ReLU in between.
   GPT      — eval/llm/model.py:8-173: nanoGPT-style decoder; q/k/v/out projections and both MLP linears are
              DropoutMM, LayerNorm without bias, causal SDPA, untied lm_head, AdamW with decay on >=2-D params.
+  ViT      — eval/vit/model.py:8-124: patches grouped into blocks of neighbouring patches, fused qkv DropoutMM,
+             pre-norm feed-forward with GELU, mean pooling, linear head.
 """
 from __future__ import annotations
 
@@ -117,3 +119,79 @@ class GPT(nn.Module):
         if fused is None:
             fused = all(p.is_cuda for p in params)
         return torch.optim.AdamW(groups, lr=lr, fused=fused)
+
+
+class _BlockedPatches(nn.Module):
+    """Image -> sequence of flattened patches, ordered so that the patches of one (b1 x b2) block of neighbouring
+    patches are consecutive: the einops pattern "b c (h b1 p1) (w b2 p2) -> b (h w b1 b2) (p1 p2 c)" of
+    eval/vit/model.py:97-103, written with view / permute.  No parameters (it holds index 0 of the embedding
+    Sequential, as the reference's Rearrange layer does)."""
+
+    def __init__(self, block: tuple[int, int], patch: tuple[int, int]):
+        super().__init__()
+        self.block, self.patch = block, patch
+
+    def forward(self, img: torch.Tensor) -> torch.Tensor:
+        b, c, H, W = img.shape
+        (b1, b2), (p1, p2) = self.block, self.patch
+        h, w = H // (b1 * p1), W // (b2 * p2)
+        x = img.view(b, c, h, b1, p1, w, b2, p2)
+        x = x.permute(0, 2, 5, 3, 6, 4, 7, 1)                    # b h w b1 b2 p1 p2 c
+        return x.reshape(b, h * w * b1 * b2, p1 * p2 * c)
+
+
+class ViTSelfAttention(nn.Module):
+    def __init__(self, n_embed: int, n_head: int, dropout: dict):
+        super().__init__()
+        assert n_embed % n_head == 0
+        self.n_head, self.n_embed = n_head, n_embed
+        self.qkv_proj = DropoutMM(n_embed, 3 * n_embed, **dropout)
+        self.out_proj = DropoutMM(n_embed, n_embed, **dropout)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        q, k, v = self.qkv_proj(x).split(self.n_embed, dim=2)
+        b, s, d = q.shape
+        heads = lambda t: t.view(b, s, self.n_head, d // self.n_head).transpose(1, 2)
+        # the reference passes is_causal=True here as well (eval/vit/model.py:41)
+        y = F.scaled_dot_product_attention(heads(q), heads(k), heads(v), is_causal=True)
+        return self.out_proj(y.transpose(1, 2).reshape(b, s, d))
+
+
+class ViTTransformer(nn.Module):
+    def __init__(self, n_embed: int, n_layers: int, n_head: int, dropout: dict):
+        super().__init__()
+        self.norm = nn.LayerNorm(n_embed)
+        self.layers = nn.ModuleList(
+            nn.ModuleList([
+                ViTSelfAttention(n_embed, n_head, dropout),
+                nn.Sequential(nn.LayerNorm(n_embed), DropoutMM(n_embed, 4 * n_embed, **dropout), nn.GELU(),
+                              DropoutMM(4 * n_embed, n_embed, **dropout)),
+            ]) for _ in range(n_layers))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        for attn, ff in self.layers:
+            x = attn(x) + x
+            x = ff(x) + x
+        return self.norm(x)
+
+
+class ViT(nn.Module):
+    """``sample`` is an (images, labels) pair as in the reference (only the image shape is used), or the image shape."""
+
+    def __init__(self, sample, num_classes: int, patch_size: tuple[int, int], block_size: tuple[int, int],
+                 n_embed: int, n_head: int, n_layers: int, dropout: dict):
+        super().__init__()
+        shape = sample[0].shape if isinstance(sample, (tuple, list)) and torch.is_tensor(sample[0]) else tuple(sample)
+        _, c, h, w = shape
+        (ph, pw), (bh, bw) = patch_size, block_size
+        assert h % (bh * ph) == 0 and w % (bw * pw) == 0, "Image dimensions must be divisible by the patch size."
+        num_patches, patch_dim = (h // ph) * (w // pw), c * ph * pw
+        self.to_patch_embedding = nn.Sequential(_BlockedPatches((bh, bw), (ph, pw)), nn.LayerNorm(patch_dim),
+                                                nn.Linear(patch_dim, n_embed), nn.LayerNorm(n_embed))
+        self.pos_embedding = nn.Parameter(torch.randn(1, num_patches, n_embed))
+        self.transformer = ViTTransformer(n_embed, n_layers, n_head, dropout)
+        self.out = nn.Linear(n_embed, num_classes)
+
+    def forward(self, img: torch.Tensor) -> torch.Tensor:
+        x = self.to_patch_embedding(img) + self.pos_embedding
+        return self.out(self.transformer(x).mean(dim=1))

@@ -10,6 +10,7 @@ Imported from the reference (paths relative to its root):
     flash_dropout/functional/im2col_conv2d.py   im2col_conv2d
     eval/mlp/model.py                     BasicNet   (variant "none", reduced width)
     eval/llm/model.py                     GPT        (variant "none", reduced width)
+    eval/vit/model.py                     ViT        (variant "none", reduced width)
 Masks fed to the reference are drawn by oracle/philox_mask.py (the reference's tests also draw one mask
 and hand it to both implementations, test/test_cuda.py:34); inputs are stored in the file so the
 fixture does not depend on any RNG version.
@@ -136,6 +137,16 @@ def main(ref_root: str) -> None:
     out["gpt_param_names"] = np.array(list(gpt.state_dict().keys()))
     for k, v in gpt.state_dict().items():
         out["gpt_param/" + k] = v.numpy()
+    from eval.vit.model import ViT as RefViT
+    imgs = torch.rand(4, 1, 16, 16)
+    vit = RefViT((imgs, torch.zeros(4, dtype=torch.long)), num_classes=10, patch_size=(2, 2), block_size=(2, 2),
+                 n_embed=64, n_head=4, n_layers=2, dropout=dict(p=0.2, variant="none", block_size=(128, 128))).train()
+    out["vit_cfg"] = np.array([10, 2, 2, 2, 2, 64, 4, 2], dtype=np.int64)
+    out["vit_x"] = imgs.numpy()
+    out["vit_logits"] = vit(imgs).detach().numpy()
+    out["vit_param_names"] = np.array(list(vit.state_dict().keys()))
+    for k, v in vit.state_dict().items():
+        out["vit_param/" + k] = v.numpy()
     # which parameters AdamW decays (eval/llm/model.py:157-173): every tensor with 2 or more dimensions
     out["gpt_decay_names"] = np.array([n for n, q in gpt.named_parameters() if q.dim() >= 2])
 

@@ -182,3 +182,15 @@ def test_models_load_reference_checkpoints(golden):
     want = {str(n) for n in golden["gpt_decay_names"]}
     assert {n for n, q in gpt.named_parameters() if id(q) in decayed} == want
     assert opt.param_groups[0]["weight_decay"] == 0.1 and opt.param_groups[1]["weight_decay"] == 0.0
+
+
+def test_vit_loads_reference_checkpoint(golden):
+    """The restated ViT (eval/vit/model.py:73-124) takes the reference model's state_dict and reproduces its logits,
+    including the block-grouped patch order of its einops rearrangement."""
+    from flash_dropout.train import ViT
+    classes, p1, p2, b1, b2, n_embed, n_head, n_layers = (int(v) for v in golden["vit_cfg"])
+    x = torch.from_numpy(golden["vit_x"])
+    vit = ViT((x, None), classes, (p1, p2), (b1, b2), n_embed, n_head, n_layers,
+              dict(p=0.2, variant="none", block_size=(128, 128))).train()
+    _load_reference_params(vit, golden, "vit")
+    torch.testing.assert_close(vit(x), torch.from_numpy(golden["vit_logits"]), rtol=1e-4, atol=1e-5)
