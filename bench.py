@@ -20,7 +20,7 @@ The metric is useful TFLOP/s: 3 * 2 * 128^2 * N * (kept blocks of that step's ma
 * sub-records, appended last on the same JSON line and measured in the same process: `sustained` (>= 0.5 s of
   back-to-back steps with the clocks seen), `p_sweep` (p = 0 .. 0.9), `conv` (the 256x64x32x32 3x3 conv layer,
   forward + backward), `mlp` / `gpt` (training-step samples/s at this run's N, SparseDrop and vanilla dropout),
-  `c1_cpu` (the reference's 1024^3 fp32 forward on the host).
+  `model_sweep` (whole-MLP step time against p), `c1_cpu` (the reference's 1024^3 fp32 forward on the host).
 """
 from __future__ import annotations
 
@@ -180,13 +180,33 @@ def run_ours(args) -> None:
     scale = 1.0 / (1.0 - P_DROP)
     g = torch.Generator().manual_seed(SEED + 1000 * rank)
     sets = []
+    # With several ranks the weight-gradient buffers come from a memory pool registered with NCCL as user buffers, so the
+    # all-reduce can work on them in place (through the switch where the fabric offers it) with few of its own thread
+    # blocks competing with the GEMMs for SMs.
+    grad_pool, registered = None, False
+    if world > 1 and os.environ.get("SD_BENCH_REGISTER", "1") == "1":
+        try:
+            backend = dist.group.WORLD._get_backend(dev)
+            grad_pool = torch.cuda.MemPool(backend.mem_allocator)
+        except Exception:                                   # noqa: BLE001 - not offered by this torch / NCCL build
+            grad_pool = None
     for _ in range(N_SETS):
         x = (torch.randn(M, K, generator=g) * K ** -0.25).half().to(dev)
         w = (torch.randn(N, K, generator=g) * K ** -0.25).half().to(dev)
         dy = (torch.randn(M, N, generator=g) * N ** -0.25).half().to(dev)
+        if grad_pool is not None:
+            with torch.cuda.use_mem_pool(grad_pool):
+                dw_buf = torch.empty(N, K, device=dev, dtype=torch.float16)
+        else:
+            dw_buf = torch.empty(N, K, device=dev, dtype=torch.float16)
         sets.append((x, w, dy, torch.empty(M, N, device=dev, dtype=torch.float16),
-                     torch.empty(M, K, device=dev, dtype=torch.float16),
-                     torch.empty(N, K, device=dev, dtype=torch.float16)))
+                     torch.empty(M, K, device=dev, dtype=torch.float16), dw_buf))
+    if grad_pool is not None:
+        try:
+            backend.register_mem_pool(grad_pool)
+            registered = True
+        except Exception:                                   # noqa: BLE001
+            registered = False
     plans = [BlockPlan(M // BLOCK, K // BLOCK, dev) for _ in range(N_SETS)]
     L = _lib.lib()
     stream = torch.cuda.current_stream(dev)
@@ -460,6 +480,7 @@ def run_ours(args) -> None:
         plans.clear()
         torch.cuda.empty_cache()
         extra["conv"] = measure_conv(dev, max(10, min(steps, 30)), 3, extras=False)
+        extra["model_sweep"] = measure_model_sweep(dev)
         flash_dropout.check_status(dev)
 
     if rank == 0:
@@ -474,7 +495,8 @@ def run_ours(args) -> None:
             "config": {"workload": WORKLOAD, "parallelism": f"dp{world}" if world > 1 else "single GPU",
                        "l2": f"{N_SETS} rotating operand/result sets (768 MB > 126 MB L2), no flush kernel",
                        "step": "plan kernel (drawn one step ahead on a second stream) + DSD fwd + SDD dX + DSD dW"
-                               + (" + NCCL allreduce(dW)" if world > 1 else "")},
+                               + ((" + NCCL allreduce(dW)" + (" on registered user buffers" if registered else ""))
+                                  if world > 1 else "")},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
                          "kernel": "sparsedrop_gemm_kernel (3 launches per step: DSD fwd, SDD dX, DSD dW)",
@@ -497,7 +519,7 @@ def run_ours(args) -> None:
                 "sample": f"{r['passes']} full 4096^3 fwd+dX+dW passes, fp32 masked-dense (no block skipping), "
                           f"median {r['seconds_per_pass']:.3f} s; {info['cpu_model']}"}
         # sub-records last: a reader that keeps only the end of the line still sees them
-        for key in ("speedup_vs_p0", "sustained", "p_sweep", "conv"):
+        for key in ("speedup_vs_p0", "sustained", "p_sweep", "conv", "model_sweep"):
             if key in extra:
                 line[key] = extra[key]
         line.update(train)
@@ -735,6 +757,45 @@ def measure_train(workload: str, variant: str, dev, world: int, rank: int, steps
     # free the step's graph and model before the next measurement
     del graphed, dp, opt, model
     torch.cuda.synchronize()
+    return out
+
+
+def measure_model_sweep(dev, steps: int = 30) -> dict:
+    """Whole-model step time against the dropout rate, SparseDrop and vanilla dropout: the reference's model benchmark
+    (benchmark/model.py:36-60: MLP 1024-1024-1024-1024-10 on a 1024 x 1x32x32 batch, forward + backward) with the
+    optimizer step included, bf16 autocast, replayed from a CUDA graph."""
+    import torch
+
+    from flash_dropout import random as sd_random
+    from flash_dropout.train import BasicNet, FlatGradDataParallel, GraphedTrainStep
+
+    ps = [0.1, 0.3, 0.5, 0.7, 0.9]
+    x = torch.rand(1024, 1, 32, 32, device=dev)
+    y = torch.randint(0, 10, (1024,), device=dev)
+    out = {"p": ps, "workload": "MLP 1024-1024-1024-1024-10, batch 1024, bf16 autocast, zero_grad + fwd + bwd + AdamW, "
+                                "CUDA graph replay"}
+    for variant in ("blockwise[cuda]", "vanilla"):
+        ms = []
+        for p in ps:
+            torch.manual_seed(SEED)
+            sd_random.manual_seed(SEED, subsequence=0)
+            model = BasicNet(1024, 2, 1024, 10, dict(p=p, variant=variant, block_size=(128, 128))).to(dev)
+            opt = torch.optim.AdamW(model.parameters(), lr=1e-3, fused=True)
+            dp = FlatGradDataParallel(model, fuse_wgrad=True)
+            step = GraphedTrainStep(model, dp, opt, lambda m, a, b: torch.nn.functional.cross_entropy(m(a).float(), b),
+                                    (x, y), autocast_dtype=torch.bfloat16)
+            for _ in range(5):
+                step()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(round(e0.elapsed_time(e1) / steps, 4))
+            del step, dp, opt, model
+        out[variant + "_ms"] = ms
+    out["speedup_vs_vanilla"] = [round(v / b, 3) for v, b in zip(out["vanilla_ms"], out["blockwise[cuda]_ms"])]
     return out
 
 
