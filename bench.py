@@ -211,12 +211,24 @@ def run_ours(args) -> None:
     L = _lib.lib()
     stream = torch.cuda.current_stream(dev)
 
+    # Gradient exchange: the all-reduce of a step's dW is issued from a stream of its own, behind an event that the
+    # dW product records, and the compute stream waits for it only when the operand set comes round again.  Events on
+    # that stream bracket each all-reduce (its wait for NCCL's stream included), which gives the exchange's own time.
+    comm = torch.cuda.Stream(dev) if world > 1 else None
+    # The products' persistent grids leave SD_BENCH_SM_MARGIN SMs (default 32: NCCL runs 24 to 32 channels on this
+    # fabric) to the all-reduce that runs beside them; without that each all-reduce crawls behind the products for
+    # lack of SMs and, where it does get some, stretches the launch whose CTAs wait for them.
+    sm_margin = int(os.environ.get("SD_BENCH_SM_MARGIN", "32")) if world > 1 else 0
+    import flash_dropout
+    prev_margin = flash_dropout.set_sm_margin(sm_margin)
+    dw_done = [torch.cuda.Event() for _ in range(N_SETS)]
+    reduced = [torch.cuda.Event() for _ in range(N_SETS)]
     pending = [None] * N_SETS
 
     def drain():
-        for j, h in enumerate(pending):
-            if h is not None:
-                h.wait()
+        for j, ev in enumerate(pending):
+            if ev is not None:
+                stream.wait_event(ev)
                 pending[j] = None
 
     # The mask of step i + 1 does not depend on step i, so its plan kernel (one CTA, a few microseconds) is launched on
@@ -241,7 +253,7 @@ def run_ours(args) -> None:
         x, w, dy, y, dx, dw = sets[i % N_SETS]
         plan = plans[i % N_SETS]
         if pending[i % N_SETS] is not None:
-            pending[i % N_SETS].wait()
+            stream.wait_event(pending[i % N_SETS])
             pending[i % N_SETS] = None
         if i not in planned:
             launch_plan(i)
@@ -261,9 +273,19 @@ def run_ours(args) -> None:
             events[3].record()
         set_free[i % N_SETS].record(stream)
         if world > 1 and exchange:
-            # the gradient exchange runs on NCCL's stream while the next steps compute; it is waited for
-            # before this operand set is used again (and at the end of the timed region)
-            pending[i % N_SETS] = dist.all_reduce(dw, async_op=True)
+            # the gradient exchange runs while the next steps compute; it is waited for before this operand set is
+            # used again (and at the end of the timed region)
+            k = i % N_SETS
+            dw_done[k].record(stream)
+            with torch.cuda.stream(comm):
+                comm.wait_event(dw_done[k])
+                if events is not None:
+                    events[4].record(comm)
+                dist.all_reduce(dw)
+                if events is not None:
+                    events[5].record(comm)
+                reduced[k].record(comm)
+            pending[k] = reduced[k]
 
     def barrier():
         if world > 1:
@@ -276,7 +298,7 @@ def run_ours(args) -> None:
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0 = time.perf_counter()
@@ -296,8 +318,10 @@ def run_ours(args) -> None:
                                        (rank << 40) + warmup + i, P_DROP, None, stream.cuda_stream))
         kept_dev += plans[0].header[0]
     kept = kept_dev.item()
+    flash_dropout.set_sm_margin(prev_margin)        # the other measurements below use every SM
     gemm_ms = sum(ev[0].elapsed_time(ev[3]) for ev in evs)
     per_kernel_ms = [sum(ev[j].elapsed_time(ev[j + 1]) for ev in evs) / steps for j in range(3)]
+    exchange_ms = sum(ev[4].elapsed_time(ev[5]) for ev in evs) / steps if world > 1 else None
 
     # ---- end to end through the operator API from pinned host memory.  Three streams, two buffer sets: the
     # H2D copy of step i+1 and the D2H copy of step i-1 run while step i computes (PCIe is full duplex).
@@ -366,7 +390,6 @@ def run_ours(args) -> None:
     ms_total, e2e_ms, gemm_ms_max = stats.tolist()
     kept_all, e2e_kept_all = work.tolist()
     # the end of a timed region is where the host synchronises anyway: did any kernel give up on a wait?
-    import flash_dropout
     flash_dropout.check_status(dev)
 
     # ---- training-step workloads at this run's N (every rank takes part), SparseDrop and vanilla dropout
@@ -480,7 +503,8 @@ def run_ours(args) -> None:
         plans.clear()
         torch.cuda.empty_cache()
         extra["conv"] = measure_conv(dev, max(10, min(steps, 30)), 3, extras=False)
-        extra["model_sweep"] = measure_model_sweep(dev)
+        if world == 1:      # a single-GPU record (its training steps would issue collectives on this rank alone)
+            extra["model_sweep"] = measure_model_sweep(dev)
         flash_dropout.check_status(dev)
 
     if rank == 0:
@@ -509,6 +533,10 @@ def run_ours(args) -> None:
                            "H2D / compute / D2H of consecutive steps overlap on three streams"},
             "gpu_launches": 4 * steps, "clocks": clocks,
         }
+        if exchange_ms is not None:
+            line["exchange"] = {"allreduce_ms": exchange_ms, "bytes": N * K * 2, "sm_margin": sm_margin,
+                                "method": "CUDA events on the exchange's stream around each all-reduce of dW (rank 0), "
+                                          "queueing behind the previous one included"}
         if world == 1 and not args.no_extras:
             from oracle import cpu_path
             info = cpu_path.host_info()
@@ -530,6 +558,18 @@ def run_ours(args) -> None:
                               "ms": c1["ms"], "cores": c1["threads"], "kind": c1["kind"],
                               "dense_equivalent_gflops": c1["dense_equivalent_gflops"]}
         print(json.dumps(line))
+    # the registered pool hands its memory back through the communicator: release it while that still exists
+    sets.clear()
+    dw_buf = None
+    if grad_pool is not None:
+        torch.cuda.synchronize()
+        if registered:
+            try:
+                backend.deregister_mem_pool(grad_pool)
+            except Exception:                               # noqa: BLE001
+                pass
+        del grad_pool
+        torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

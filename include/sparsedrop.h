@@ -153,6 +153,15 @@ int sd_plan_from_mask(void* plan, int R, int C, int rep_r, int rep_c, const uint
 size_t sd_workspace_bytes(void);
 int sd_workspace_init(void* workspace, void* stream);
 
+/* SMs that every GEMM / conv launch made after this call leaves free (default 0, or the value of the environment
+ * variable SD_SM_MARGIN when the library is loaded); returns the previous value, or SD_ERR_INVALID_ARG for a
+ * negative one.  The kernels are persistent, one CTA per SM for the whole launch with tiles dealt out up front:
+ * when another kernel (a gradient all-reduce that overlaps the next step) occupies SMs, CTAs that have to wait for
+ * one stretch the launch by up to a whole pass, while the other kernel crawls for lack of SMs.  A margin of about
+ * as many SMs as that kernel has CTAs lets both run side by side; launches that do not fill the GPU anyway are
+ * unaffected.  Process-wide; no counterpart in the reference (one CTA per tile, flash_dropout/cuda/src/matmul_dsd.cuh:99-105). */
+int sd_set_sm_margin(int sms);
+
 /* Dense C = scale * A . B^T.  Replaces GEMM.gemm (flash_dropout/cuda/binding_gemm.py:26-27,
  * flash_dropout/cuda/src/gemm.cuh:143-167). */
 int sd_gemm(const void* A, int64_t a_rs, int64_t a_cs,

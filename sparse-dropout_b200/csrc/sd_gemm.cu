@@ -1291,6 +1291,13 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const CU
     return SD_OK;
 }
 
+// SMs that the persistent grids of this library leave free (sd_set_sm_margin); SD_SM_MARGIN gives the initial value.
+static std::atomic<int> g_sm_margin{[] {
+    const char* e = getenv("SD_SM_MARGIN");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 ? v : 0;
+}()};
+
 // Optional epilogue work of one launch (see the fields of the same names in GemmArgs).
 struct GemmExtras {
     int act = 0;
@@ -1402,7 +1409,11 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     int sms = 0;
     rc = sm_count_current_device(&sms);
     if (rc) return rc;
-    int grid = sms;
+    // SMs left to kernels that run beside this one (a gradient all-reduce overlapping the next step's products): a
+    // persistent CTA holds its SM for the whole launch, and with a static deal of tiles a CTA that has to wait for an
+    // SM another kernel occupies stretches the launch by up to a whole pass.
+    const int sm_margin = g_sm_margin.load(std::memory_order_relaxed);
+    int grid = sms > 2 * sm_margin ? sms - sm_margin : sms;
     if (mode == MODE_DSD) {
         const int kb = (K + 127) / 128;
         if (plan_side == SD_PLAN_ROWS) {
@@ -1721,6 +1732,11 @@ int sd_gemm_sdd_relu_mask(const void* A, int64_t a_rs, int64_t a_cs, const void*
     ex.mask_rs = x_rs;
     return sd::run_gemm(sd::MODE_SDD, A, a_rs, a_cs, B, b_rs, b_cs, C, c_rs, c_cs, M, N, K, plan, 0, scale, dtype,
                         workspace, status, stream, 0, true, false, 0, nullptr, 0, &ex);
+}
+
+int sd_set_sm_margin(int sms) {
+    if (sms < 0) return sd::fail(SD_ERR_INVALID_ARG, "the SM margin must not be negative (got %d)", sms);
+    return sd::g_sm_margin.exchange(sms, std::memory_order_relaxed);
 }
 
 size_t sd_workspace_bytes(void) {

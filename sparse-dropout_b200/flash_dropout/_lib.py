@@ -26,7 +26,7 @@ EXPORTS = (
     "sd_gemm_dsd_panels", "sd_gemm_sdd_kept_t_panels", "sd_selftest_bounded_wait", "sd_check_status",
     "sd_conv_fused_supported", "sd_conv_dsd_fwd", "sd_conv_dsd_dw",
     "sd_gemm_dsd_relu", "sd_gemm_dsd_f32", "sd_gemm_sdd_relu_mask",
-    "sd_plan_batch_desc_bytes", "sd_plan_batch_describe", "sd_plan_batch_launch",
+    "sd_plan_batch_desc_bytes", "sd_plan_batch_describe", "sd_plan_batch_launch", "sd_set_sm_margin",
 )
 
 
@@ -111,6 +111,8 @@ def lib() -> C.CDLL:
     L.sd_workspace_init.argtypes = [vp, vp]
     L.sd_check_status.restype = i32
     L.sd_check_status.argtypes = [vp, vp]
+    L.sd_set_sm_margin.restype = i32
+    L.sd_set_sm_margin.argtypes = [i32]
     return L
 
 

@@ -75,3 +75,7 @@ def test_argument_validation_without_a_gpu(built_lib):
     assert built_lib.sd_im2col_kept_panels(None, 1, 1, 8, 8, 3, 3, 1, 1, 1, 1, 1, 1, a, 64, None, None) == SD_ERR_INVALID_ARG
     assert built_lib.sd_check_status(None, None) == SD_ERR_INVALID_ARG
     assert built_lib.sd_workspace_init(None, None) == SD_ERR_INVALID_ARG
+    # SM margin: a process-wide setting, returns the previous value
+    assert built_lib.sd_set_sm_margin(-1) == SD_ERR_INVALID_ARG
+    prev = built_lib.sd_set_sm_margin(24)
+    assert prev >= 0 and built_lib.sd_set_sm_margin(prev) == 24

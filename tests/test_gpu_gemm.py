@@ -369,3 +369,34 @@ def test_rectangular_block_sizes(built_lib, bs):
     _close(xa.grad, dx_ref, "dx")
     _close(wa.grad, dw_ref, "dw")
     sd_random.follow_torch_seed()
+
+
+def test_sm_margin_changes_only_the_grid(built_lib):
+    """With SMs left free for a kernel running beside the products (flash_dropout.set_sm_margin) the three
+    products of a full-grid layer give bit-identical results: the margin only changes how many CTAs share the tiles."""
+    import flash_dropout
+    from flash_dropout import _lib
+    from flash_dropout.cuda.binding_gemm import BlockPlan, dsd, sdd
+    M = N = K = 2048
+    x, w, dy = _inputs(M, N, K, seed=71)
+    xd, wd, dyd = x.to(DEV), w.to(DEV), dy.to(DEV)
+    plan = BlockPlan.from_seed(M, K, 128, 0.5, 9, 0, DEV)
+
+    def products():
+        return (dsd(xd, wd, plan, _lib.SD_PLAN_ROWS, 2.0), sdd(dyd, wd.T, plan, 2.0),
+                dsd(xd.T, dyd.T, plan, _lib.SD_PLAN_COLS, 2.0))
+    base = products()
+    prev = flash_dropout.set_sm_margin(24)
+    try:
+        assert prev == 0
+        with_margin = products()
+    finally:
+        assert flash_dropout.set_sm_margin(prev) == 24
+    torch.cuda.synchronize()
+    for a, b, name in zip(base, with_margin, ("y", "dx", "dw")):
+        assert torch.equal(a, b), name
+    mask_np = pm.block_mask(M, K, 128, 0.5, seed=9, offset=0)
+    y_ref, dx_ref, dw_ref = md.forward_backward(x, mask_np, 128, 0.5, w, dy)
+    _close(with_margin[0], y_ref, "y")
+    _close(with_margin[1], dx_ref, "dx")
+    _close(with_margin[2].T, dw_ref, "dw")           # the third product is dW^T (K x N)
