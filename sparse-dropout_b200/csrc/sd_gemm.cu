@@ -140,7 +140,10 @@ struct GemmArgs {
     const int* items;                // SDD: (row block, col tile 0, col tile 1 or -1); with sdd_single: kept (row, col) pairs
     const int* n_items;
     int sdd_single;                  // SDD with one kept 128x128 tile per item: 1 = the plan's (row, col) is the result's
-                                     // tile (row, col); 2 = the plan describes the transposed result: tile (col, row)
+                                     // tile (row, col); 2 = the plan describes the transposed result: tile (col, row);
+                                     // 3 = transposed plan, two kept tiles of one plan column per item: item j of column
+                                     // c = entries 2j, 2j+1 of the column's kept-row list (list_ptr / list_idx), so two
+                                     // tiles of one result row block share the A tile and one 128x256 MMA
     const int* zero_pairs;           // SDD: dropped (row block, col tile) pairs
     const int* n_zero;
     int* status;
@@ -247,7 +250,12 @@ struct WorkIter {
         split = g.split != 0;
         tab = nullptr;
         nk_uniform = (g.KK + 127) >> 7;
-        n_tiles = g.mode == MODE_SDD ? __ldg(g.n_items) : g.n_row_blocks * g.n_col_tiles;
+        if (g.mode == MODE_SDD && g.sdd_single == 3) {
+            n_tiles = 0;
+            for (int c = 0; c < g.n_row_blocks; ++c) n_tiles += (count(g, c) + 1) >> 1;
+        } else {
+            n_tiles = g.mode == MODE_SDD ? __ldg(g.n_items) : g.n_row_blocks * g.n_col_tiles;
+        }
         t = cta;
         stride = n_ctas;
         pass = 0;
@@ -300,7 +308,21 @@ struct WorkIter {
     __device__ __forceinline__ void fill(const GemmArgs& g, Seg& s, int row_block, int n_tile) const {
         s.bits = 0;
         s.use_bits = false;
-        if (g.mode == MODE_SDD && g.sdd_single) {
+        if (g.mode == MODE_SDD && g.sdd_single == 3) {
+            int idx = row_block, c = 0, beg = 0, n = 0;
+            for (; c < g.n_row_blocks; ++c) {                    // which plan column the item falls into
+                beg = __ldg(g.list_ptr + c);
+                n = __ldg(g.list_ptr + c + 1) - beg;
+                const int items_c = (n + 1) >> 1;
+                if (idx < items_c) break;
+                idx -= items_c;
+            }
+            s.a_row = c * 128;
+            s.b_row0 = __ldg(g.list_idx + beg + 2 * idx) * 128;
+            s.b_row1 = 2 * idx + 1 < n ? __ldg(g.list_idx + beg + 2 * idx + 1) * 128 : -1;
+            s.nk = nk_uniform;
+            s.klist = nullptr;
+        } else if (g.mode == MODE_SDD && g.sdd_single) {
             const int pr = __ldg(g.items + 2 * row_block), pc = __ldg(g.items + 2 * row_block + 1);
             s.a_row = (g.sdd_single == 2 ? pc : pr) * 128;
             s.b_row0 = (g.sdd_single == 2 ? pr : pc) * 128;
@@ -1090,9 +1112,11 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
                         if (lane == 0) {
                             if (!g.c_panel_kg)
                                 tma_store_2d(&tmapC, buf, col - 32, w.a_row + quad * 32);
-                            else if (w.a_row + quad * 32 < g.MM)   // rows past the last k would land in the next panel
-                                tma_store_2d(&tmapC, buf, col - 32 - w.b_row0,
-                                             (w.b_row0 >> 7) * g.c_panel_kg + w.a_row + quad * 32);
+                            else if (w.a_row + quad * 32 < g.MM) { // rows past the last k would land in the next panel
+                                const int pix0 = c < 4 ? w.b_row0 : w.b_row1;     // the pixel block of this half
+                                tma_store_2d(&tmapC, buf, col - 32 - pix0,
+                                             (pix0 >> 7) * g.c_panel_kg + w.a_row + quad * 32);
+                            }
                             bulk_commit();
                         }
                         ++n_stores;
@@ -1430,6 +1454,12 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
         PlanView v = view_plan(plan, (N + 127) / 128, g.n_row_blocks);
         g.items = v.kept_pairs; g.n_items = v.header + H_NNZ;
         g.sdd_single = 2;
+        // few result row blocks (the conv's k blocks) with many kept tiles each: pair the tiles of a row block, which
+        // halves the number of tiles a CTA walks through and the A traffic
+        if (g.n_row_blocks <= 64 && (long long)g.n_row_blocks * ((N + 127) / 128) >= 4ll * sms) {
+            g.list_ptr = v.col_ptr; g.list_idx = v.row_idx;
+            g.sdd_single = 3;
+        }
     } else if (mode == MODE_SDD) {
         PlanView v = view_plan(plan, g.n_row_blocks, (N + 127) / 128);
         // paired items halve the A traffic; with so few of them that half the SMs would idle, one tile per item
