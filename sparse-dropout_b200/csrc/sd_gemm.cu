@@ -154,6 +154,10 @@ struct GemmArgs {
     int tma_store;                   // result written by TMA from a swizzled staging buffer: 1 row-major, 2 column-major
     float* ws_slots;
     int* ws_flags;
+    const unsigned char* direct_mask;   // DSD launches in which every CTA gets at most one tile: the plan's tile mask
+    int dm_stride_rb, dm_stride_k;      // (1 = dropped), byte (row block rb, K tile k) at rb * dm_stride_rb + k * dm_stride_k.
+                                        // A CTA then reads its row block's <= 32 mask bytes in one round trip instead of
+                                        // walking order -> list bounds -> list entries (three dependent loads)
     int use_table;                   // whole-tile schedule whose tiles can be described by the shared-memory table
     int all_halves;                  // whole-tile schedule of a launch that would leave most SMs idle: every tile is
                                      // handed out as two 128-wide halves, so twice as many SMs stream the operands
@@ -224,6 +228,7 @@ struct WorkIter {
     bool split, snake;
     const int4* tab;             // shared-memory tile table (see TAB_MAX), or null: resolve every tile from the plan
     int passes;                  // whole tiles: passes over the entry list this grid makes
+    bool direct;                 // DSD, one pass: tiles resolved from the plan's mask bytes (see GemmArgs::direct_mask)
 
     __device__ __forceinline__ int count(const GemmArgs& g, int r) const {
         return __ldg(g.list_ptr + r + 1) - __ldg(g.list_ptr + r);
@@ -259,9 +264,10 @@ struct WorkIter {
         t = cta;
         stride = n_ctas;
         pass = 0;
-        // alternate the direction only when row blocks differ in length; with equal tiles (dense, SDD, a mask that
-        // dropped nothing) plain round-robin keeps neighbouring CTAs on neighbouring tiles in every pass
-        snake = g.mode == MODE_DSD && __ldg(g.h_nnz) != g.n_row_blocks * __ldg(g.h_max);
+        // with equal tiles (dense, SDD, a mask that dropped nothing) plain round-robin keeps neighbouring CTAs on
+        // neighbouring tiles in every pass; see below for unequal row blocks
+        direct = false;
+        snake = false;
         sp_rb = sp_nt = sp_owner = sp_part = 0;
         sp_parts = 0;
         const bool ragged = (g.n_col_tiles - 1) * BN + 128 >= g.NN;
@@ -280,6 +286,9 @@ struct WorkIter {
         }
         n_entries = whole_entries + 2 * (n_tiles - whole_entries);
         passes = (n_entries + n_ctas - 1) / n_ctas;
+        direct = g.direct_mask != nullptr && !split && passes <= 1;
+        // alternate the direction only when row blocks differ in length (and there is more than one pass)
+        if (g.mode == MODE_DSD && passes > 1) snake = __ldg(g.h_nnz) != g.n_row_blocks * __ldg(g.h_max);
         // the table costs a CTA-wide barrier and one chain of index loads up front: worth it from a handful of tiles per
         // CTA on (the short tiles of a conv), not for the three or four long tiles of a large square product
         if (g.use_table && !split && passes >= TAB_MIN && passes <= TAB_MAX) tab = table;
@@ -368,7 +377,21 @@ struct WorkIter {
             int rbi, nt;
             if (tile < n_full) { rbi = tile / full_per_row; nt = tile - rbi * full_per_row; }
             else { rbi = tile - n_full; nt = g.n_col_tiles - 1; }
-            fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, nt);
+            if (direct) {
+                // one pass: the order of the tiles does not matter, and the kept K tiles come straight from the mask
+                const unsigned char* m = g.direct_mask + (long long)rbi * g.dm_stride_rb;
+                uint32_t bits = 0;
+                for (int j = 0; j < nk_uniform; ++j) bits |= uint32_t(__ldg(m + (long long)j * g.dm_stride_k) == 0) << j;
+                s.a_row = rbi * 128;
+                s.b_row0 = nt * BN;
+                s.b_row1 = (nt * BN + 128 < g.NN) ? nt * BN + 128 : -1;
+                s.klist = nullptr;
+                s.use_bits = true;
+                s.bits = bits;
+                s.nk = __popc(bits);
+            } else {
+                fill(g, s, g.order ? __ldg(g.order + rbi) : rbi, nt);
+            }
         }
         if (s.nk == 0) return false;          // empty row blocks are zero-filled by the epilogue warps
         if (half >= 0) {                      // one 128-wide half of a tile of the last wave
@@ -1332,6 +1355,7 @@ struct GemmExtras {
 
 struct PlanView {
     const int *header, *row_ptr, *col_idx, *col_ptr, *row_idx, *row_order, *col_order, *sdd_items, *drop_pairs, *kept_pairs;
+    const unsigned char* mask;
 };
 static PlanView view_plan(const void* plan, int R, int C) {
     const sd_plan_layout L = plan_layout(R, C);
@@ -1347,6 +1371,7 @@ static PlanView view_plan(const void* plan, int R, int C) {
     v.sdd_items = reinterpret_cast<const int*>(b + L.sdd_items);
     v.drop_pairs = reinterpret_cast<const int*>(b + L.drop_pairs);
     v.kept_pairs = reinterpret_cast<const int*>(b + L.kept_pairs);
+    v.mask = b + L.mask;
     return v;
 }
 
@@ -1444,10 +1469,12 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
             PlanView v = view_plan(plan, g.n_row_blocks, kb);
             g.list_ptr = v.row_ptr; g.list_idx = v.col_idx; g.order = v.row_order;
             g.h_nnz = v.header + H_NNZ; g.h_max = v.header + H_MAX_ROW;
+            if (kb <= 32) { g.direct_mask = v.mask; g.dm_stride_rb = kb; g.dm_stride_k = 1; }
         } else {
             PlanView v = view_plan(plan, kb, g.n_row_blocks);
             g.list_ptr = v.col_ptr; g.list_idx = v.row_idx; g.order = v.col_order;
             g.h_nnz = v.header + H_NNZ; g.h_max = v.header + H_MAX_COL;
+            if (kb <= 32) { g.direct_mask = v.mask; g.dm_stride_rb = 1; g.dm_stride_k = g.n_row_blocks; }
         }
     } else if (mode == MODE_SDD && sdd_t) {
         // the plan's grid is (N/128) x (M/128): the transpose of the result's; one item per kept pair

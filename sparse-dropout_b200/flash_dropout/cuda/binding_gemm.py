@@ -170,6 +170,7 @@ class PlanBatch:
         self.recording = True
         self.pos = 0
         self.desc = None
+        self._ready = None                    # event of a launch made on a side stream that the pass has not joined yet
 
     def request(self, M: int, K: int, block_size: int, p: float, device: torch.device) -> "BlockPlan":
         from flash_dropout import random as sd_random
@@ -185,6 +186,7 @@ class PlanBatch:
             return plan
         if self.pos >= len(self.plans) or self.specs[self.pos] != spec:
             raise RuntimeError("the pass asks for different block plans than the recorded one")
+        self.join(device)
         plan = self.plans[self.pos]
         if self.pos not in self._batched_set:      # too large for the batch kernel: its own launch, same counter
             counter = sd_random.device_counter(device)
@@ -221,13 +223,32 @@ class PlanBatch:
                                                 counter.data_ptr(), self.specs[i][3], pl.mask.data_ptr()))
         self.desc.copy_(torch.frombuffer(host, dtype=torch.uint8))
 
-    def launch(self) -> None:
-        """Start of a pass: one launch for every batched plan."""
+    def launch(self, side_stream: "torch.cuda.Stream | None" = None) -> None:
+        """Start of a pass: one launch for every batched plan.
+
+        With ``side_stream`` the launch goes there, behind everything the current stream holds so far (the previous
+        pass still reads the plans), and the current stream picks it up again at the pass's first ``BlockPlan.draw``
+        (or at ``join()``): whatever the pass does before its first SparseDrop layer runs beside the plan kernel."""
         self.pos = 0
-        if self.desc is not None:
+        if self.desc is None:
+            return
+        if side_stream is None:
             with _on_device(self.device):
                 _lib.check(_lib.lib().sd_plan_batch_launch(self.desc.data_ptr(), len(self.batched),
                                                            _lib.stream_ptr(self.device)))
+            return
+        side_stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side_stream):
+            _lib.check(_lib.lib().sd_plan_batch_launch(self.desc.data_ptr(), len(self.batched),
+                                                       _lib.stream_ptr(self.device)))
+            self._ready = torch.cuda.Event()
+            self._ready.record(side_stream)
+
+    def join(self, device: "torch.device | None" = None) -> None:
+        """The current stream waits for a launch made on a side stream (no-op otherwise)."""
+        if self._ready is not None:
+            torch.cuda.current_stream(device or self.device).wait_event(self._ready)
+            self._ready = None
 
 
 _workspaces: dict = {}

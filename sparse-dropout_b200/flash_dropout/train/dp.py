@@ -255,19 +255,24 @@ class GraphedTrainStep:
 
         from flash_dropout.cuda.binding_gemm import PlanBatch
         self.plan_batch = PlanBatch(dev) if batch_plans else None
+        self._plan_stream = torch.cuda.Stream(dev) if batch_plans else None
 
         def fwd_bwd():
-            dp.zero_grad()
             if self.plan_batch is not None:
                 PlanBatch.active = self.plan_batch
                 if not self.plan_batch.recording:
-                    self.plan_batch.launch()           # every layer's mask of this step, one launch
+                    # every layer's mask of this step from one launch, on a stream of its own: it runs beside the
+                    # zeroing of the gradients and whatever else precedes the first SparseDrop layer
+                    self.plan_batch.launch(self._plan_stream)
+            dp.zero_grad()
             try:
                 loss = fwd_loss()
             finally:
                 PlanBatch.active = None
-            if self.plan_batch is not None and self.plan_batch.recording:
-                self.plan_batch.finalize()
+            if self.plan_batch is not None:
+                self.plan_batch.join()                 # a pass that drew nothing still has to pick the launch up
+                if self.plan_batch.recording:
+                    self.plan_batch.finalize()
             loss.backward()
             if self.whole_step:
                 dp.finish()
