@@ -154,7 +154,7 @@ struct GemmArgs {
     int tma_store;                   // result written by TMA from a swizzled staging buffer: 1 row-major, 2 column-major
     float* ws_slots;
     int* ws_flags;
-    const unsigned char* direct_mask;   // DSD launches in which every CTA gets at most one tile: the plan's tile mask
+    const unsigned char* direct_mask;   // DSD launches in which a CTA gets only a few tiles: the plan's tile mask
     int dm_stride_rb, dm_stride_k;      // (1 = dropped), byte (row block rb, K tile k) at rb * dm_stride_rb + k * dm_stride_k.
                                         // A CTA then reads its row block's <= 32 mask bytes in one round trip instead of
                                         // walking order -> list bounds -> list entries (three dependent loads)
@@ -228,7 +228,7 @@ struct WorkIter {
     bool split, snake;
     const int4* tab;             // shared-memory tile table (see TAB_MAX), or null: resolve every tile from the plan
     int passes;                  // whole tiles: passes over the entry list this grid makes
-    bool direct;                 // DSD, one pass: tiles resolved from the plan's mask bytes (see GemmArgs::direct_mask)
+    bool direct;                 // DSD, few passes: tiles resolved from the plan's mask bytes (see GemmArgs::direct_mask)
 
     __device__ __forceinline__ int count(const GemmArgs& g, int r) const {
         return __ldg(g.list_ptr + r + 1) - __ldg(g.list_ptr + r);
@@ -286,7 +286,7 @@ struct WorkIter {
         }
         n_entries = whole_entries + 2 * (n_tiles - whole_entries);
         passes = (n_entries + n_ctas - 1) / n_ctas;
-        direct = g.direct_mask != nullptr && !split && passes <= 1;
+        direct = g.direct_mask != nullptr && !split && passes < TAB_MIN;
         // alternate the direction only when row blocks differ in length (and there is more than one pass)
         if (g.mode == MODE_DSD && passes > 1) snake = __ldg(g.h_nnz) != g.n_row_blocks * __ldg(g.h_max);
         // the table costs a CTA-wide barrier and one chain of index loads up front: worth it from a handful of tiles per
@@ -365,7 +365,7 @@ struct WorkIter {
     // blocks, forwards on even passes and backwards on odd ones, so the CTA that got the heaviest tile of one pass gets
     // the lightest of the next.
     __device__ bool resolve(const GemmArgs& g, int ps, Seg& s) const {
-        const int entry = ps * stride + ((snake && (ps & 1)) ? stride - 1 - t : t);
+        const int entry = ps * stride + (((ps & 1) && snake) ? stride - 1 - t : t);   // pass 0 does not wait for `snake`
         if (entry >= n_entries) return false;
         const int tile = entry < whole_entries ? entry : whole_entries + ((entry - whole_entries) >> 1);
         const int half = entry < whole_entries ? -1 : ((entry - whole_entries) & 1);
@@ -378,11 +378,13 @@ struct WorkIter {
             if (tile < n_full) { rbi = tile / full_per_row; nt = tile - rbi * full_per_row; }
             else { rbi = tile - n_full; nt = g.n_col_tiles - 1; }
             if (direct) {
-                // one pass: the order of the tiles does not matter, and the kept K tiles come straight from the mask
-                const unsigned char* m = g.direct_mask + (long long)rbi * g.dm_stride_rb;
+                // the kept K tiles come straight from the mask bytes of the row block (with one pass the order of the
+                // tiles does not matter either)
+                const int rb = (passes > 1 && g.order) ? __ldg(g.order + rbi) : rbi;
+                const unsigned char* m = g.direct_mask + (long long)rb * g.dm_stride_rb;
                 uint32_t bits = 0;
                 for (int j = 0; j < nk_uniform; ++j) bits |= uint32_t(__ldg(m + (long long)j * g.dm_stride_k) == 0) << j;
-                s.a_row = rbi * 128;
+                s.a_row = rb * 128;
                 s.b_row0 = nt * BN;
                 s.b_row1 = (nt * BN + 128 < g.NN) ? nt * BN + 128 : -1;
                 s.klist = nullptr;
