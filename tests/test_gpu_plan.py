@@ -129,12 +129,14 @@ def test_plan_batch_equals_single_launches(built_lib):
     counter = sd_random.device_counter(dev)
     seed, base = sd_random.seed_and_base()
     batch = PlanBatch(dev)
+    side = torch.cuda.Stream(dev)
     drawn = 0
     try:
-        for step in range(3):
+        for step in range(4):
             PlanBatch.active = batch
             if not batch.recording:
-                batch.launch()
+                # on the current stream, and (last pass) on a stream of its own that the first draw picks up again
+                batch.launch(side if step == 3 else None)
             plans = [BlockPlan.draw(M, K, bs, p, dev) for M, K, bs, p in shapes]
             PlanBatch.active = None
             if batch.recording:
