@@ -159,6 +159,7 @@ struct GemmArgs {
                                         // A CTA then reads its row block's <= 32 mask bytes in one round trip instead of
                                         // walking order -> list bounds -> list entries (three dependent loads)
     int use_table;                   // whole-tile schedule whose tiles can be described by the shared-memory table
+    int tab_min;                     // fewest passes of a CTA from which the table is used
     int all_halves;                  // whole-tile schedule of a launch that would leave most SMs idle: every tile is
                                      // handed out as two 128-wide halves, so twice as many SMs stream the operands
     int act;                         // epilogue: 1 = ReLU on the result (eval/mlp/model.py:33-38 applies it as a separate op)
@@ -286,12 +287,12 @@ struct WorkIter {
         }
         n_entries = whole_entries + 2 * (n_tiles - whole_entries);
         passes = (n_entries + n_ctas - 1) / n_ctas;
-        direct = g.direct_mask != nullptr && !split && passes < TAB_MIN;
+        direct = g.direct_mask != nullptr && !split && passes < g.tab_min;
         // alternate the direction only when row blocks differ in length (and there is more than one pass)
         if (g.mode == MODE_DSD && passes > 1) snake = __ldg(g.h_nnz) != g.n_row_blocks * __ldg(g.h_max);
         // the table costs a CTA-wide barrier and one chain of index loads up front: worth it from a handful of tiles per
         // CTA on (the short tiles of a conv), not for the three or four long tiles of a large square product
-        if (g.use_table && !split && passes >= TAB_MIN && passes <= TAB_MAX) tab = table;
+        if (g.use_table && !split && passes >= g.tab_min && passes <= TAB_MAX) tab = table;
         if (!split || n_tiles == 0 || n_tiles > n_ctas) return;
         const int row_weight = 2 * g.n_col_tiles - (ragged ? 1 : 0);
         const unsigned total = work_before(g, n_tiles, row_weight);
@@ -1544,7 +1545,15 @@ static int run_gemm(int mode, const void* A, int64_t a_rs, int64_t a_cs, const v
     // Whole-tile launches describe their tiles once per CTA in shared memory when a tile's kept K tiles fit a 32-bit mask
     // (and only when a CTA gets enough tiles for the table to pay: see TAB_MIN; the bound below counts every tile
     // that may exist, the kernel checks the tiles that do)
-    g.use_table = !g.split && (mode != MODE_DSD || k_tiles <= 32) && tiles_upper >= (long long)TAB_MIN * grid / 2;
+    // Short reductions (up to 16 K tiles) make a tile so short that resolving the next one between tiles shows: they get
+    // the table from five passes on ((16384, 1536, 384) forward: 25.3 -> 22.5 us); long ones only from TAB_MIN on, where
+    // the table's prologue would otherwise cost more than it saves (4096^3: +2.7 %).
+    static const int tab_min_short = [] {
+        const char* e = getenv("SD_TAB_MIN_SHORT");        // tuning knob: fewest passes that get the table, short reductions
+        return e ? atoi(e) : 5;
+    }();
+    g.tab_min = k_tiles <= 16 ? tab_min_short : TAB_MIN;
+    g.use_table = !g.split && (mode != MODE_DSD || k_tiles <= 32) && tiles_upper >= (long long)g.tab_min * grid / 2;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // Row-major result with 16-byte rows: written by TMA (clipped at the ragged edge); otherwise by the warps.
     CUtensorMap tc = ta;
