@@ -41,7 +41,8 @@ typedef enum sd_status {
 
 typedef enum sd_dtype {
     SD_F16 = 0,                /* IEEE half   (the only dtype of gemm_binding.cu:49-50) */
-    SD_BF16 = 1                /* bfloat16    (extension: the reference is fp16-only)   */
+    SD_BF16 = 1,               /* bfloat16    (extension: the reference is fp16-only)   */
+    SD_F32 = 2                 /* float: only as the output / gradient dtype of sd_layernorm_* */
 } sd_dtype;
 
 /* Side of the block plan a DSD product reduces over. */
@@ -354,6 +355,24 @@ int sd_conv_dsd_dw(const void* x, int N, int C, int H, int W, int R, int S,
                    const void* dY2d, int64_t dy_rs, int64_t dy_cs,
                    void* dW2d, int64_t dw_rs, int64_t dw_cs, int Ko,
                    const void* plan, float scale, int dtype, void* workspace, int* status, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * LayerNorm over the last dimension of x[rows, n] (fp32, contiguous, n a multiple of 4 and at most 1024), for the
+ * normalisations that sit in front of the SparseDrop layers of the transformer consumers.  The reference uses
+ * torch.nn.LayerNorm there (eval/llm/model.py:72-74,113; eval/vit/model.py:11,53,106-108), whose result autocast then
+ * casts to 16 bits for the DropoutMM that follows; no counterpart among the reference's own kernels.
+ *   forward : y = (x - mean) * rstd * gamma (+ beta, may be NULL), rstd = 1 / sqrt(var + eps), biased variance;
+ *             y is written as y_dtype (SD_F32, SD_BF16 or SD_F16); mean[rows] and rstd[rows] are kept for backward.
+ *   backward: dx[rows, n] (fp32), and dgamma[n] / dbeta[n] (dbeta may be NULL) overwritten or, with accumulate != 0,
+ *             added to; dy is read as dy_dtype.  workspace: sd_layernorm_bwd_workspace_bytes(rows, n) bytes,
+ *             16-byte aligned (per-CTA partial sums of the two parameter gradients).
+ * ------------------------------------------------------------------------------------------ */
+int sd_layernorm_fwd(const float* x, int rows, int n, const float* gamma, const float* beta, float eps, void* y,
+                     int y_dtype, float* mean, float* rstd, void* stream);
+size_t sd_layernorm_bwd_workspace_bytes(int rows, int n);
+int sd_layernorm_bwd(const float* x, const void* dy, int dy_dtype, const float* gamma, const float* mean,
+                     const float* rstd, int rows, int n, float* dx, float* dgamma, float* dbeta, int accumulate,
+                     void* workspace, void* stream);
 
 /*
  * Exercises the bounded device-side waits the kernels are built on, without a fault or a hang: a one-warp kernel

@@ -8,4 +8,4 @@ NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
 "$NVCC" -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a \
     -Xcompiler -fPIC -Xptxas -v --shared \
     -o "$out/libsparsedrop.so" \
-    "$here/sd_api.cu" "$here/sd_plan.cu" "$here/sd_gemm.cu" "$here/sd_conv.cu" "$here/sd_selftest.cu" "$@"
+    "$here/sd_api.cu" "$here/sd_plan.cu" "$here/sd_gemm.cu" "$here/sd_conv.cu" "$here/sd_norm.cu" "$here/sd_selftest.cu" "$@"

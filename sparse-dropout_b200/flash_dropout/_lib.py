@@ -15,7 +15,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libsparsedrop.so")
 
-SD_F16, SD_BF16 = 0, 1
+SD_F16, SD_BF16, SD_F32 = 0, 1, 2
 SD_PLAN_ROWS, SD_PLAN_COLS = 0, 1
 
 #: every symbol include/sparsedrop.h declares
@@ -27,6 +27,7 @@ EXPORTS = (
     "sd_conv_fused_supported", "sd_conv_dsd_fwd", "sd_conv_dsd_dw",
     "sd_gemm_dsd_relu", "sd_gemm_dsd_f32", "sd_gemm_sdd_relu_mask",
     "sd_plan_batch_desc_bytes", "sd_plan_batch_describe", "sd_plan_batch_launch", "sd_set_sm_margin",
+    "sd_layernorm_fwd", "sd_layernorm_bwd_workspace_bytes", "sd_layernorm_bwd",
 )
 
 
@@ -113,6 +114,12 @@ def lib() -> C.CDLL:
     L.sd_check_status.argtypes = [vp, vp]
     L.sd_set_sm_margin.restype = i32
     L.sd_set_sm_margin.argtypes = [i32]
+    L.sd_layernorm_fwd.restype = i32
+    L.sd_layernorm_fwd.argtypes = [vp, i32, i32, vp, vp, f32, vp, i32, vp, vp, vp]
+    L.sd_layernorm_bwd_workspace_bytes.restype = C.c_size_t
+    L.sd_layernorm_bwd_workspace_bytes.argtypes = [i32, i32]
+    L.sd_layernorm_bwd.restype = i32
+    L.sd_layernorm_bwd.argtypes = [vp, vp, i32, vp, vp, vp, i32, i32, vp, vp, vp, i32, vp, vp]
     return L
 
 

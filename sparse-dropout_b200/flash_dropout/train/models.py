@@ -15,6 +15,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from flash_dropout.layers import DropoutMM
+from flash_dropout.layers.norm import LayerNorm
 
 
 def next_multiple(x: int, base: int) -> int:
@@ -77,9 +78,9 @@ class MLP(nn.Module):
 class Block(nn.Module):
     def __init__(self, n_embed: int, n_head: int, dropout: dict):
         super().__init__()
-        self.ln_1 = nn.LayerNorm(n_embed, bias=False)
+        self.ln_1 = LayerNorm(n_embed, bias=False)
         self.attn = CausalSelfAttention(n_embed, n_head, dropout)
-        self.ln_2 = nn.LayerNorm(n_embed, bias=False)
+        self.ln_2 = LayerNorm(n_embed, bias=False)
         self.mlp = MLP(n_embed, dropout)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -95,7 +96,7 @@ class GPT(nn.Module):
             wte=nn.Embedding(vocab_size, n_embed),
             wpe=nn.Embedding(context_length, n_embed),
             h=nn.ModuleList(Block(n_embed, n_head, dropout) for _ in range(n_layer)),
-            ln_f=nn.LayerNorm(n_embed, bias=False),
+            ln_f=LayerNorm(n_embed, bias=False),
         ))
         self.lm_head = nn.Linear(n_embed, vocab_size, bias=False)
 
@@ -160,11 +161,11 @@ class ViTSelfAttention(nn.Module):
 class ViTTransformer(nn.Module):
     def __init__(self, n_embed: int, n_layers: int, n_head: int, dropout: dict):
         super().__init__()
-        self.norm = nn.LayerNorm(n_embed)
+        self.norm = LayerNorm(n_embed)
         self.layers = nn.ModuleList(
             nn.ModuleList([
                 ViTSelfAttention(n_embed, n_head, dropout),
-                nn.Sequential(nn.LayerNorm(n_embed), DropoutMM(n_embed, 4 * n_embed, **dropout), nn.GELU(),
+                nn.Sequential(LayerNorm(n_embed), DropoutMM(n_embed, 4 * n_embed, **dropout), nn.GELU(),
                               DropoutMM(4 * n_embed, n_embed, **dropout)),
             ]) for _ in range(n_layers))
 
@@ -186,8 +187,8 @@ class ViT(nn.Module):
         (ph, pw), (bh, bw) = patch_size, block_size
         assert h % (bh * ph) == 0 and w % (bw * pw) == 0, "Image dimensions must be divisible by the patch size."
         num_patches, patch_dim = (h // ph) * (w // pw), c * ph * pw
-        self.to_patch_embedding = nn.Sequential(_BlockedPatches((bh, bw), (ph, pw)), nn.LayerNorm(patch_dim),
-                                                nn.Linear(patch_dim, n_embed), nn.LayerNorm(n_embed))
+        self.to_patch_embedding = nn.Sequential(_BlockedPatches((bh, bw), (ph, pw)), LayerNorm(patch_dim),
+                                                nn.Linear(patch_dim, n_embed), LayerNorm(n_embed))
         self.pos_embedding = nn.Parameter(torch.randn(1, num_patches, n_embed))
         self.transformer = ViTTransformer(n_embed, n_layers, n_head, dropout)
         self.out = nn.Linear(n_embed, num_classes)

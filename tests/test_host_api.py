@@ -194,3 +194,15 @@ def test_vit_loads_reference_checkpoint(golden):
               dict(p=0.2, variant="none", block_size=(128, 128))).train()
     _load_reference_params(vit, golden, "vit")
     torch.testing.assert_close(vit(x), torch.from_numpy(golden["vit_logits"]), rtol=1e-4, atol=1e-5)
+
+
+def test_layernorm_module_is_torch_layernorm_on_cpu():
+    """The fused LayerNorm is nn.LayerNorm with another CUDA path: same parameters, same result on the CPU."""
+    import torch
+    from flash_dropout.layers.norm import LayerNorm
+    torch.manual_seed(0)
+    ours, ref = LayerNorm(48, bias=False), torch.nn.LayerNorm(48, bias=False)
+    assert isinstance(ours, torch.nn.LayerNorm) and list(ours.state_dict()) == list(ref.state_dict())
+    ref.load_state_dict(ours.state_dict())
+    x = torch.randn(5, 7, 48)
+    assert torch.equal(ours(x), ref(x))
