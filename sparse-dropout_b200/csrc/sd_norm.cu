@@ -15,6 +15,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "sd_common.h"
 
 namespace sd {
@@ -172,22 +174,32 @@ layernorm_bwd_kernel(const float* __restrict__ x, const void* __restrict__ dy, c
     for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) out[i] = acc[i];
 }
 
-// Column sums of partials[parts][2n]: thread (tx, ty) adds rows ty, ty + 8, ... of column blockIdx.x * 32 + tx.
-__global__ void __launch_bounds__(256)
+// Column sums of partials[parts][2n]: thread (tx, ty) adds rows ty, ty + 32, ... of column blockIdx.x * 32 + tx, four
+// rows at a time so that their loads are in flight together.
+__global__ void __launch_bounds__(1024)
 layernorm_bwd_reduce_kernel(const float* __restrict__ partials, int parts, int n, float* __restrict__ dgamma,
                             float* __restrict__ dbeta, int accumulate) {
-    __shared__ float red[8][33];
+    __shared__ float red[32][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int col = blockIdx.x * 32 + tx;
-    float s = 0.f;
-    if (col < 2 * n)
-        for (int p = ty; p < parts; p += 8) s += __ldg(partials + (long long)p * 2 * n + col);
-    red[ty][tx] = s;
+    const long long stride = 2ll * n;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (col < 2 * n) {
+        int p = ty;
+        for (; p + 96 < parts; p += 128) {
+            s0 += __ldg(partials + p * stride + col);
+            s1 += __ldg(partials + (p + 32) * stride + col);
+            s2 += __ldg(partials + (p + 64) * stride + col);
+            s3 += __ldg(partials + (p + 96) * stride + col);
+        }
+        for (; p < parts; p += 32) s0 += __ldg(partials + p * stride + col);
+    }
+    red[ty][tx] = (s0 + s1) + (s2 + s3);
     __syncthreads();
     if (ty == 0 && col < 2 * n) {
         float t = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) t += red[k][tx];
+        for (int k = 0; k < 32; ++k) t += red[k][tx];
         float* dst = col < n ? dgamma + col : (dbeta ? dbeta + (col - n) : nullptr);
         if (dst) *dst = accumulate ? *dst + t : t;
     }
@@ -220,6 +232,28 @@ static int norm_vpl(int n) {
         case 6: { constexpr int V = 6; CALL; } break;                      \
         default: { constexpr int V = 8; CALL; } break;                     \
     }
+
+// Backward launch: at most as many CTAs as are resident at once (a second, partly filled wave would run at a fraction
+// of the memory-level parallelism), never more than the workspace was sized for (`grid`, see norm_grid).
+template <int DYT, int V>
+static int launch_norm_bwd(int grid, cudaStream_t st, const float* x, const void* dy, const float* gamma, const float* mean,
+                           const float* rstd, float* dx, float* partials, int rows, int n, int* grid_used) {
+    static std::atomic<int> per_sm_cached{0};   // the same on every device this process sees (one GPU type per node)
+    int sms = 0;
+    const int rc = sm_count_current_device(&sms);
+    if (rc) return rc;
+    int per_sm = per_sm_cached.load(std::memory_order_relaxed);
+    if (per_sm == 0) {
+        int nb = 0;
+        SD_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, layernorm_bwd_kernel<DYT, V>, kNormThreads, 0));
+        per_sm = nb > 0 ? nb : 1;
+        per_sm_cached.store(per_sm, std::memory_order_relaxed);
+    }
+    if (grid > sms * per_sm) grid = sms * per_sm;
+    layernorm_bwd_kernel<DYT, V><<<grid, kNormThreads, 0, st>>>(x, dy, gamma, mean, rstd, dx, partials, rows, n);
+    *grid_used = grid;
+    return SD_OK;
+}
 
 static int check_norm_args(const void* x, int rows, int n) {
     if (!x) return fail(SD_ERR_INVALID_ARG, "x is null");
@@ -281,18 +315,20 @@ int sd_layernorm_bwd(const float* x, const void* dy, int dy_dtype, const float* 
     if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     float* partials = static_cast<float*>(workspace);
+    int parts = grid;
     const int vpl = sd::norm_vpl(n);
     if (dy_dtype == SD_F32) {
-        SD_NORM_DISPATCH_VPL(vpl, (sd::layernorm_bwd_kernel<SD_F32, V><<<grid, sd::kNormThreads, 0, st>>>(x, dy, gamma, mean, rstd, dx, partials, rows, n)))
+        SD_NORM_DISPATCH_VPL(vpl, (rc = sd::launch_norm_bwd<SD_F32, V>(grid, st, x, dy, gamma, mean, rstd, dx, partials, rows, n, &parts)))
     } else if (dy_dtype == SD_BF16) {
-        SD_NORM_DISPATCH_VPL(vpl, (sd::layernorm_bwd_kernel<SD_BF16, V><<<grid, sd::kNormThreads, 0, st>>>(x, dy, gamma, mean, rstd, dx, partials, rows, n)))
+        SD_NORM_DISPATCH_VPL(vpl, (rc = sd::launch_norm_bwd<SD_BF16, V>(grid, st, x, dy, gamma, mean, rstd, dx, partials, rows, n, &parts)))
     } else if (dy_dtype == SD_F16) {
-        SD_NORM_DISPATCH_VPL(vpl, (sd::layernorm_bwd_kernel<SD_F16, V><<<grid, sd::kNormThreads, 0, st>>>(x, dy, gamma, mean, rstd, dx, partials, rows, n)))
+        SD_NORM_DISPATCH_VPL(vpl, (rc = sd::launch_norm_bwd<SD_F16, V>(grid, st, x, dy, gamma, mean, rstd, dx, partials, rows, n, &parts)))
     } else {
         return sd::fail(SD_ERR_INVALID_ARG, "dy_dtype must be SD_F16, SD_BF16 or SD_F32");
     }
+    if (rc) return rc;
     SD_CUDA_TRY(cudaGetLastError());
-    sd::layernorm_bwd_reduce_kernel<<<(2 * n + 31) / 32, 256, 0, st>>>(partials, grid, n, dgamma, dbeta, accumulate);
+    sd::layernorm_bwd_reduce_kernel<<<(2 * n + 31) / 32, 1024, 0, st>>>(partials, parts, n, dgamma, dbeta, accumulate);
     SD_CUDA_TRY(cudaGetLastError());
     return SD_OK;
 }
