@@ -1076,7 +1076,9 @@ sparsedrop_gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_c
         while (alive && it.next(g, w)) {
             const bool partial = w.parts > 1;
             const bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, g.status, ST_EPILOGUE);
-            if (!epilogue_all(ok, epi_threads)) { alive = false; break; }     // uniform decision of all epilogue threads
+            // Split launches synchronise all epilogue warps later (the shared tile), so they decide together whether
+            // to go on; otherwise every warp decides for itself and no warp waits for the slowest one at every tile.
+            if (g.split ? !epilogue_all(ok, epi_threads) : !__all_sync(0xffffffffu, ok)) { alive = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quad * 32) << 16);
             const int row = w.a_row + etid;
