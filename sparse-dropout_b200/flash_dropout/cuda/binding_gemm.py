@@ -60,6 +60,7 @@ class BlockPlan:
         self.layout = _lib.plan_layout(self.R, self.C)
         self.buf = torch.empty(self.layout.total_bytes, dtype=torch.uint8, device=device)
         self.mask: torch.Tensor | None = None   # logical bool mask, True = dropped
+        self.origin: tuple | None = None        # (M, K, block_size, p, seed, offset) of a plan drawn from a host-side offset
 
     # ---- construction -------------------------------------------------------------------
     @classmethod
@@ -74,6 +75,7 @@ class BlockPlan:
                 plan.buf.data_ptr(), plan.R, plan.C, rr, rc, seed & (2**64 - 1), offset & (2**64 - 1), float(p),
                 mask.data_ptr(), _lib.stream_ptr(device)))
         plan.mask = mask
+        plan.origin = (M, K, block_size, float(p), seed, offset)     # enough to draw the same plan again
         return plan
 
     @classmethod

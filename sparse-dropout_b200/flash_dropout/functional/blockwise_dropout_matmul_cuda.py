@@ -29,7 +29,7 @@ def _operand(x: torch.Tensor) -> torch.Tensor:
 
 
 class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
-    """forward(input, weight, block_size, p, plan, relu, input_relu, grad_premasked, wgrad)
+    """forward(input, weight, block_size, p, plan, relu, input_relu, grad_premasked, wgrad, recompute_plan)
 
     The first four arguments are the reference's.  The others fuse the layer's elementwise neighbours into the
     kernels' epilogues (all off by default):
@@ -42,12 +42,16 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
       wgrad           ``(fp32 tensor [out, in], accumulate, notify)``: the weight gradient is written (or added) in fp32
                       straight into that tensor by the dW epilogue instead of being returned to autograd as a 16-bit
                       tensor that is then cast and accumulated by two more kernels; ``notify()`` is called afterwards.
+      recompute_plan  keep only (seed, offset) of the mask between forward and backward and draw the plan again there
+                      (one more plan launch per layer in backward; the plan buffer, 4 bytes per tile and list entry, is
+                      not kept alive).  Applies to plans drawn from a host-side offset; a plan whose offset was read
+                      from the device-side counter (CUDA-graph mode, where plan buffers are static anyway) is kept.
     """
 
     @staticmethod
     def forward(ctx, input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
                 plan: BlockPlan | None = None, relu: bool = False, input_relu: bool = False,
-                grad_premasked: bool = False, wgrad=None):
+                grad_premasked: bool = False, wgrad=None, recompute_plan: bool = False):
         assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
         if not (input.is_cuda and weight.is_cuda):
             # no CPU path: flash_dropout/cuda/src/gemm_binding.cu:19 raises the same way
@@ -69,7 +73,8 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
             ctx.save_for_backward(input, weight, out)
         else:
             ctx.save_for_backward(input, weight)
-        ctx.plan = plan
+        ctx.origin = plan.origin if recompute_plan else None
+        ctx.plan = None if ctx.origin is not None else plan
         ctx.p = p
         ctx.relu, ctx.input_relu, ctx.grad_premasked, ctx.wgrad = relu, input_relu, grad_premasked, wgrad
         return out
@@ -78,6 +83,8 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
     def backward(ctx, grad_output: torch.Tensor):
         input, weight, *rest = ctx.saved_tensors
         plan, scale = ctx.plan, 1.0 / (1.0 - ctx.p)
+        if plan is None:
+            plan = BlockPlan.from_seed(*ctx.origin, input.device)    # the same mask and lists, drawn again
         dy = grad_output.to(input.dtype)
         if ctx.relu and not ctx.grad_premasked:
             dy = torch.ops.aten.threshold_backward(dy, rest[0], 0)       # ReLU derivative, one kernel
@@ -96,7 +103,7 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
             # dW^T (K, N) = (keep o x)^T (K, M) . dy (M, N) * scale, stored straight into dW (N, K)
             grad_weight = torch.empty_like(weight, memory_format=torch.contiguous_format)
             dsd(input.T, dy.T, plan, _lib.SD_PLAN_COLS, scale, out=grad_weight.T)
-        return grad_input, grad_weight, None, None, None, None, None, None, None
+        return grad_input, grad_weight, None, None, None, None, None, None, None, None
 
 
 _last_cast = {"key": None, "src": None, "ref": None}
@@ -127,7 +134,7 @@ def _autocast_input(input: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
 
 def blockwise_dropout_matmul(input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
                              plan: BlockPlan | None = None, relu: bool = False, input_relu: bool = False,
-                             grad_premasked: bool = False, wgrad=None) -> torch.Tensor:
+                             grad_premasked: bool = False, wgrad=None, recompute_plan: bool = False) -> torch.Tensor:
     """``y = (mask o input) . weight^T / (1 - p)`` with a fresh block mask (or the given plan).
 
     Under CUDA autocast both operands are cast to the autocast dtype (the reference casts to fp16,
@@ -139,4 +146,4 @@ def blockwise_dropout_matmul(input: torch.Tensor, weight: torch.Tensor, block_si
         input, weight = _autocast_input(input, dt), weight.to(dt)
     with torch.autocast("cuda", enabled=False):
         return BlockwiseDropoutMatmulCUDA.apply(input, weight, block_size, p, plan, relu, input_relu, grad_premasked,
-                                                wgrad)
+                                                wgrad, recompute_plan)

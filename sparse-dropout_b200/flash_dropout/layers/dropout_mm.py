@@ -25,7 +25,9 @@ def _block_size(kwargs: dict):
 
 class DropoutMM(nn.Module):
     """``y = dropout(x) @ W.T``; in eval mode a plain linear.  Same constructor as the reference
-    (dropout_mm.py:15-35): weight ``(out_features, in_features)``, kaiming-uniform(a=sqrt(5)), no bias."""
+    (dropout_mm.py:15-35): weight ``(out_features, in_features)``, kaiming-uniform(a=sqrt(5)), no bias.
+    Extra keyword for the CUDA variant: ``recompute_plan=True`` keeps only the mask's (seed, offset) between forward
+    and backward and draws the block plan again there instead of keeping its buffer alive."""
 
     __constants__ = ["in_features", "out_features"]
 
@@ -58,7 +60,8 @@ class DropoutMM(nn.Module):
             wgrad = getattr(self.weight, "_sd_wgrad", None) if torch.is_grad_enabled() else None
             out = F.cuda_blockwise_dropout_matmul(x, self.weight, _block_size(self.kwargs), self.p,
                                                   relu=activation == "relu", input_relu=input_relu,
-                                                  grad_premasked=grad_premasked and activation == "relu", wgrad=wgrad)
+                                                  grad_premasked=grad_premasked and activation == "relu", wgrad=wgrad,
+                                                  recompute_plan=bool(self.kwargs.get("recompute_plan", False)))
             return out.reshape(*lead, self.out_features)
         out = self._forward_plain(input)
         return torch.relu(out) if activation == "relu" else out

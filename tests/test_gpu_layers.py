@@ -263,3 +263,32 @@ def test_convergence_smoke_on_synthetic_data(built_lib):
     # both SparseDrop paths draw the same mask stream, fresh on every replay: with whole 128-sample blocks dropped
     # their training loss stays noisy where a mask frozen into the graph would let it collapse to ~0
     assert last["blockwise[naive]"] > 0.05 and last["blockwise[cuda]"] > 0.05, last
+
+
+def test_recompute_plan_gives_the_same_gradients(built_lib):
+    """With ``recompute_plan`` the layer keeps only (seed, offset) of its mask and draws the plan again in backward:
+    output and gradients are bit-identical to keeping the plan, and the autograd node holds no plan."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.layers import DropoutMM
+    sd_random.disable_device_counter()         # host-side offsets: the mode in which a plan can be drawn again
+    torch.manual_seed(3)
+    x = torch.randn(640, 1024, device=DEV, dtype=torch.float16)
+    dy = torch.randn(640, 768, device=DEV, dtype=torch.float16)
+    outs = []
+    for recompute in (False, True):
+        sd_random.manual_seed(77, subsequence=0)
+        torch.manual_seed(4)
+        layer = DropoutMM(1024, 768, p=0.5, variant="blockwise[cuda]", block_size=128, recompute_plan=recompute).to(DEV).half()
+        xa = x.clone().requires_grad_()
+        y = layer(xa)
+        node = y.grad_fn
+        while node is not None and not hasattr(node, "plan"):
+            node = node.next_functions[0][0] if node.next_functions else None
+        assert node is not None and (node.plan is None) == recompute
+        if recompute:
+            assert node.origin[4:] == (77, 0) and node.origin[:2] == (640, 1024)
+        y.backward(dy)
+        outs.append((y.detach(), xa.grad, layer.weight.grad))
+    sd_random.follow_torch_seed()
+    for a, b, name in zip(outs[0], outs[1], ("y", "dx", "dw")):
+        assert torch.equal(a, b), name
