@@ -29,7 +29,7 @@ def _operand(x: torch.Tensor) -> torch.Tensor:
 
 
 class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
-    """forward(input, weight, block_size, p, plan, relu, input_relu, grad_premasked, wgrad, recompute_plan)
+    """forward(input, weight, block_size, p, plan, relu, input_relu, grad_premasked, wgrad, recompute_plan, anchor)
 
     The first four arguments are the reference's.  The others fuse the layer's elementwise neighbours into the
     kernels' epilogues (all off by default):
@@ -46,12 +46,14 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
                       (one more plan launch per layer in backward; the plan buffer, 4 bytes per tile and list entry, is
                       not kept alive).  Applies to plans drawn from a host-side offset; a plan whose offset was read
                       from the device-side counter (CUDA-graph mode, where plan buffers are static anyway) is kept.
+      anchor          a tensor that ties the result into the autograd graph when ``weight`` is a 16-bit copy made outside
+                      autograd (see ``blockwise_dropout_matmul(weight_lowp=...)``); it receives no gradient.
     """
 
     @staticmethod
     def forward(ctx, input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
                 plan: BlockPlan | None = None, relu: bool = False, input_relu: bool = False,
-                grad_premasked: bool = False, wgrad=None, recompute_plan: bool = False):
+                grad_premasked: bool = False, wgrad=None, recompute_plan: bool = False, anchor=None):
         assert 0 <= p < 1, "Dropout probability must be in [0, 1)"
         if not (input.is_cuda and weight.is_cuda):
             # no CPU path: flash_dropout/cuda/src/gemm_binding.cu:19 raises the same way
@@ -103,7 +105,7 @@ class BlockwiseDropoutMatmulCUDA(torch.autograd.Function):
             # dW^T (K, N) = (keep o x)^T (K, M) . dy (M, N) * scale, stored straight into dW (N, K)
             grad_weight = torch.empty_like(weight, memory_format=torch.contiguous_format)
             dsd(input.T, dy.T, plan, _lib.SD_PLAN_COLS, scale, out=grad_weight.T)
-        return grad_input, grad_weight, None, None, None, None, None, None, None, None
+        return grad_input, grad_weight, None, None, None, None, None, None, None, None, None
 
 
 _last_cast = {"key": None, "src": None, "ref": None}
@@ -134,16 +136,25 @@ def _autocast_input(input: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
 
 def blockwise_dropout_matmul(input: torch.Tensor, weight: torch.Tensor, block_size: int, p: float,
                              plan: BlockPlan | None = None, relu: bool = False, input_relu: bool = False,
-                             grad_premasked: bool = False, wgrad=None, recompute_plan: bool = False) -> torch.Tensor:
+                             grad_premasked: bool = False, wgrad=None, recompute_plan: bool = False,
+                             weight_lowp: torch.Tensor | None = None) -> torch.Tensor:
     """``y = (mask o input) . weight^T / (1 - p)`` with a fresh block mask (or the given plan).
 
     Under CUDA autocast both operands are cast to the autocast dtype (the reference casts to fp16,
     blockwise_dropout_matmul_cuda.py:9); otherwise they must already be fp16 or bf16.  The keyword arguments after
-    ``plan`` fuse elementwise neighbours into the kernels (see ``BlockwiseDropoutMatmulCUDA``).
+    ``plan`` fuse elementwise neighbours into the kernels (see ``BlockwiseDropoutMatmulCUDA``).  ``weight_lowp`` is an
+    up-to-date copy of ``weight`` in the autocast dtype that the caller keeps (a training step that casts all weights
+    with one launch): it is used instead of casting again, which needs ``wgrad`` (the copy is outside autograd, so
+    the weight gradient has to leave through the fused store).
     """
+    anchor = None
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
-        input, weight = _autocast_input(input, dt), weight.to(dt)
+        input = _autocast_input(input, dt)
+        if weight_lowp is not None and wgrad is not None and weight_lowp.dtype == dt and weight_lowp.shape == weight.shape:
+            anchor, weight = weight, weight_lowp
+        else:
+            weight = weight.to(dt)
     with torch.autocast("cuda", enabled=False):
         return BlockwiseDropoutMatmulCUDA.apply(input, weight, block_size, p, plan, relu, input_relu, grad_premasked,
-                                                wgrad, recompute_plan)
+                                                wgrad, recompute_plan, anchor)

@@ -58,7 +58,10 @@ class DropoutMM(nn.Module):
             lead = input.shape[:-1]
             x = input.reshape(-1, input.shape[-1])
             wgrad = getattr(self.weight, "_sd_wgrad", None) if torch.is_grad_enabled() else None
-            out = F.cuda_blockwise_dropout_matmul(x, self.weight, _block_size(self.kwargs), self.p,
+            # a 16-bit copy of the weight kept by the training step, valid while the weight has not changed since
+            lowp = getattr(self.weight, "_sd_w16", None)
+            lowp = lowp[0] if (lowp is not None and wgrad is not None and lowp[1] == self.weight._version) else None
+            out = F.cuda_blockwise_dropout_matmul(x, self.weight, _block_size(self.kwargs), self.p, weight_lowp=lowp,
                                                   relu=activation == "relu", input_relu=input_relu,
                                                   grad_premasked=grad_premasked and activation == "relu", wgrad=wgrad,
                                                   recompute_plan=bool(self.kwargs.get("recompute_plan", False)))

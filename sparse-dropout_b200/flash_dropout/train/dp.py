@@ -15,6 +15,8 @@ Works with any backend torch.distributed offers (NCCL on GPUs, gloo for the CPU 
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -75,6 +77,8 @@ class FlatGradDataParallel:
                     dist.broadcast(b.data, src=broadcast_from, group=self.group)
             for p in self.params:
                 p.register_post_accumulate_grad_hook(self._on_grad_ready)
+        self._shadow_params: list = []
+        self._shadows = None
         if fuse_wgrad:
             self._fuse_weight_gradients()
         sd_random.set_subsequence(self.rank)     # every rank draws its own masks from the shared seed
@@ -134,8 +138,26 @@ class FlatGradDataParallel:
                 if p in self._slices and p.dtype == torch.float32 and p.is_cuda:
                     notify = (lambda p=p: self._on_grad_ready(p)) if self.world > 1 else None
                     p._sd_wgrad = (p.grad, False, notify)
+                    self._shadow_params.append(p)
+
+    def refresh_weight_shadows(self, dtype: torch.dtype | None) -> None:
+        """Casts the weights of all layers with a fused weight gradient to ``dtype`` with one multi-tensor launch and
+        hands the copies to the layers, which then skip their own cast under autocast.  Call it once per step, after
+        the optimizer has updated the weights and before the forward pass; a layer ignores a copy that is older than
+        its weight (``_version``)."""
+        # the multi-tensor launch costs about as much as four casts: it pays for models with many layers (char-GPT:
+        # 36 layers, step 4.41 -> 4.29 ms), not for the four layers of the MLP (0.215 -> 0.219 ms)
+        if dtype is None or len(self._shadow_params) < self.shadow_min_layers:
+            return
+        if self._shadows is None or self._shadows[0].dtype != dtype:
+            self._shadows = [torch.empty_like(p, dtype=dtype) for p in self._shadow_params]
+        with torch.no_grad():
+            torch._foreach_copy_(self._shadows, [p.detach() for p in self._shadow_params])
+        for p, sh in zip(self._shadow_params, self._shadows):
+            p._sd_w16 = (sh, p._version)
 
     defer_allreduce = False     # hooks stay quiet: the caller reduces the whole flat buffer itself
+    shadow_min_layers = 8       # fewest fused layers from which refresh_weight_shadows() makes its copies
 
     def _reduce_bucket(self, b: int) -> None:
         """Starts the reduction of bucket b without blocking the stream that computes."""
@@ -211,6 +233,8 @@ def train_step(model: torch.nn.Module, dp: FlatGradDataParallel, optimizer: torc
     _maybe_check_status(dp.flat_grad.device, check_every)
     dp.zero_grad()
     dev_type = dp.flat_grad.device.type
+    if dev_type == "cuda":
+        dp.refresh_weight_shadows(autocast_dtype)
     if autocast_dtype is not None:
         with torch.autocast(dev_type, dtype=autocast_dtype):
             loss = loss_fn(model)
@@ -265,6 +289,7 @@ class GraphedTrainStep:
                     # zeroing of the gradients and whatever else precedes the first SparseDrop layer
                     self.plan_batch.launch(self._plan_stream)
             dp.zero_grad()
+            dp.refresh_weight_shadows(autocast_dtype)     # one launch instead of a cast per layer
             try:
                 loss = fwd_loss()
             finally:

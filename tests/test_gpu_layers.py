@@ -292,3 +292,39 @@ def test_recompute_plan_gives_the_same_gradients(built_lib):
     sd_random.follow_torch_seed()
     for a, b, name in zip(outs[0], outs[1], ("y", "dx", "dw")):
         assert torch.equal(a, b), name
+
+
+def test_weight_shadows_equal_per_layer_casts_and_are_ignored_when_stale(built_lib):
+    """One multi-tensor cast of all SparseDrop weights per step (``refresh_weight_shadows``) trains exactly like a
+    cast per layer, and a layer whose weight changed after the copy was made goes back to casting for itself."""
+    from flash_dropout import random as sd_random
+    from flash_dropout.train import BasicNet, FlatGradDataParallel
+    from flash_dropout.train.dp import train_step
+    sd_random.disable_device_counter()
+    g = torch.Generator().manual_seed(12)
+    x = torch.rand(512, 784, generator=g).to(DEV)
+    y = torch.randint(0, 10, (512,), generator=g).to(DEV)
+    models = []
+    for use_shadows in (False, True):
+        torch.manual_seed(21)
+        sd_random.manual_seed(31, subsequence=0)
+        model = BasicNet(784, 2, 512, 10, dict(p=0.5, variant="blockwise[cuda]", block_size=128)).to(DEV)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+        dp = FlatGradDataParallel(model, fuse_wgrad=True)
+        dp.shadow_min_layers = 1 if use_shadows else 10 ** 6      # the MLP has fewer layers than the default threshold
+        for _ in range(3):
+            train_step(model, dp, opt, lambda m: torch.nn.functional.cross_entropy(m(x).float(), y),
+                       autocast_dtype=torch.bfloat16)
+        models.append(model)
+    for (na, pa), (nb, pb) in zip(models[0].named_parameters(), models[1].named_parameters()):
+        assert torch.equal(pa, pb), na
+    # the optimizer's last update made every copy stale: the layers must not use them
+    stale = [p for p in models[1].parameters() if hasattr(p, "_sd_w16")]
+    assert stale and all(p._sd_w16[1] != p._version for p in stale)
+    outs = []
+    for model in models:
+        sd_random.manual_seed(41, subsequence=0)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            outs.append(model(x))
+    assert torch.equal(outs[0], outs[1])
+    sd_random.follow_torch_seed()
